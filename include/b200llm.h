@@ -1,0 +1,152 @@
+/*
+ * b200llm.h — C ABI of the B200 (sm_100a) kernels behind the continuous-batching
+ * prefill/decode step of the nano-vLLM-style engine in ZenoAFfectionate/LLM_from_Scratch.
+ *
+ * The reference engine has no native layer: its attention layer (the part that would call a
+ * store_kvcache kernel, a varlen prefill attention and a paged decode attention) is missing from
+ * the repository.  What the reference does define is the contract those kernels must honour —
+ * the metadata tensors built by engine/model_runner.py (prepare_prefill :202-249, prepare_decode
+ * :253-278), the KV pool layout of allocate_kv_cache (:162-190) and the padding conventions of
+ * the CUDA-graph replay (:295-310).  Every entry point below cites the part of that contract it
+ * implements.
+ *
+ * Conventions
+ *   - every pointer is a BORROWED device pointer unless its name ends in _host; the library never
+ *     allocates, frees or retains memory;
+ *   - `stream` is a cudaStream_t passed as void*; a call only enqueues work on that stream and
+ *     never synchronises the host, so every call can be captured in a CUDA graph;
+ *   - metadata dtypes are exactly the reference's: slot_mapping and context_lens int64,
+ *     block_tables and cu_seqlens int32; -1 is legal padding in slot_mapping and block_tables;
+ *   - return value: 0 on success, a negative B200_ERR_* code for argument / launch errors that
+ *     are detected on the host.  Faults detected on the device (a block id or slot outside the
+ *     pool) never dereference the bad address: the access is skipped and a B200_ERR_* code is
+ *     stored to `status` (a caller-owned device int32, may be NULL); read it with
+ *     b200_read_status at the next host sync point;
+ *   - dtype: B200_DTYPE_F32 or B200_DTYPE_BF16 is the element type of q/k/v/caches/outputs.
+ *     Arithmetic is always accumulated in fp32.
+ */
+#ifndef B200LLM_H_
+#define B200LLM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+#define B200_DTYPE_F32 0
+#define B200_DTYPE_BF16 1
+
+#define B200_OK 0
+#define B200_ERR_ARG (-1)          /* null pointer, negative size, inconsistent head counts */
+#define B200_ERR_ALIGN (-2)        /* pointer or stride not aligned as the kernel requires   */
+#define B200_ERR_UNSUPPORTED (-3)  /* shape / dtype outside what the kernels implement       */
+#define B200_ERR_LAUNCH (-4)       /* the CUDA runtime refused the launch                    */
+#define B200_ERR_WORKSPACE (-5)    /* workspace smaller than *_workspace_bytes asks for      */
+#define B200_ERR_BOUNDS (-6)       /* device-side: block id or slot outside the pool         */
+#define B200_ERR_NO_DEVICE (-7)    /* no usable CUDA device                                  */
+
+int b200_abi_version(void);
+const char* b200_strerror(int code);
+
+/* Number of SMs of the current device (148 on B200); <0 on error. */
+int b200_sm_count(void);
+
+/* Copies the device status word to the host (synchronises `stream`) and clears it. */
+int b200_read_status(int32_t* status, int32_t* status_host, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * XXH64 of a byte string with seed 0, and the chained block hash built on it.
+ * Replaces BlockManager.compute_hash (engine/block_manager.py:45-57), which calls the third-party
+ * xxhash package: hash = XXH64( [8-byte little-endian prefix hash, if prefix != -1] ||
+ * int32-little-endian token ids ).  Host-only; no GPU work.
+ * ------------------------------------------------------------------------------------------- */
+uint64_t b200_xxh64(const void* data_host, size_t len, uint64_t seed);
+uint64_t b200_block_hash(const int32_t* token_ids_host, int32_t num_tokens, uint64_t prefix_hash,
+                         int32_t has_prefix);
+
+/* ---------------------------------------------------------------------------------------------
+ * store_kvcache: k_cache[slot_mapping[t], :, :] = k[t, :, :] (same for v); slot < 0 is skipped.
+ * Contract: engine/model_runner.py:184-190 (pool [num_blocks, block_size, Hkv, D] per layer, so a
+ * slot is one row of [num_slots, Hkv*D]), :226-230 (prefill slots), :261 (decode slot) and
+ * :300-301 (-1 padding under graph replay).
+ *   k, v            [num_tokens, Hkv, D]; rows Hkv*D contiguous, token stride given in ELEMENTS
+ *                   (k/v may be column slices of a fused qkv projection)
+ *   k_cache,v_cache [num_slots, Hkv, D] contiguous
+ * ------------------------------------------------------------------------------------------- */
+int b200_store_kvcache(const void* k, const void* v, int64_t k_token_stride,
+                       int64_t v_token_stride, void* k_cache, void* v_cache,
+                       const int64_t* slot_mapping, int32_t num_tokens, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t num_slots, int32_t dtype, int32_t* status,
+                       void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Paged GQA decode attention: one query token per sequence attends to its whole context through
+ * block_tables.  Arithmetic = GroupedQueryAttention.forward cache branch
+ * (model/attention/GQA.py:105-130) with the dense cache replaced by the paged pool; metadata =
+ * prepare_decode (engine/model_runner.py:253-278).
+ *   q, out        [batch, Hq, D] contiguous
+ *   k_cache       [num_blocks, block_size, Hkv, D]
+ *   block_tables  [batch, bt_stride] int32, entries beyond ceil(context_len/block_size) are
+ *                 never read (-1 or stale values are fine)
+ *   context_lens  [batch] int64, includes the token being decoded; <= 0 writes a zero row
+ *   workspace     b200_paged_decode_gqa_workspace_bytes(...) bytes, 256-byte aligned; holds
+ *                 split-context partial results, no state survives the call
+ * ------------------------------------------------------------------------------------------- */
+size_t b200_paged_decode_gqa_workspace_bytes(int32_t batch, int32_t num_q_heads,
+                                             int32_t num_kv_heads, int32_t head_dim,
+                                             int32_t dtype);
+int b200_paged_decode_gqa(const void* q, const void* k_cache, const void* v_cache, void* out,
+                          const int32_t* block_tables, int64_t bt_stride,
+                          const int64_t* context_lens, int32_t batch, int32_t num_q_heads,
+                          int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
+                          int64_t num_blocks, float scale, void* workspace, size_t workspace_bytes,
+                          int32_t dtype, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Ragged (varlen) causal prefill attention over sequences packed with cu_seqlens.
+ * Arithmetic = scaled_dot_product_attention (model/attention/utils.py:51-63) per sequence with
+ * the causal mask of TransformerLM.forward (model/transformer.py:174-176), bottom-right aligned
+ * when seqlen_k > seqlen_q (GQA.py:108-113), KV heads shared as GQA.py:118-125; metadata =
+ * prepare_prefill (engine/model_runner.py:202-249).
+ *   q   [total_q, Hq, Dqk]   token stride q_token_stride (elements), heads contiguous
+ *   k   [total_k, Hkv, Dqk], v [total_k, Hkv, Dv]: the new tokens' keys/values when
+ *       block_tables == NULL (then cu_seqlens_k must equal cu_seqlens_q);
+ *   when block_tables != NULL (some prefix is cached, model_runner.py:231-237) keys/values are
+ *       read from k_cache/v_cache through block_tables [num_seqs, bt_stride] and k/v are ignored
+ *       (the caller has already stored the new tokens with b200_store_kvcache);
+ *   out [total_q, Hq, Dv] contiguous.
+ * ------------------------------------------------------------------------------------------- */
+int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
+                        int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                        int32_t num_seqs, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                        int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
+                        int32_t head_dim_v, float scale, const void* k_cache, const void* v_cache,
+                        const int32_t* block_tables, int64_t bt_stride, int32_t block_size,
+                        int64_t num_blocks, int32_t dtype, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * MLA latent-cache decode (absorbed form).  Arithmetic = MultiHeadLatentAttention.forward cache
+ * branch (model/attention/MLA.py:153-178) between the two weight einsums:
+ *   score = (q_abs . c^T + q_rope . pe^T) * scale ; P = softmax(score) ; out_latent = P . c
+ * with c/pe read from a paged latent pool whose rows are [kv_lora_rank | rope_dim].
+ *   q_abs [batch, H, r], q_rope [batch, H, dr], out_latent [batch, H, r] contiguous
+ *   latent_cache [num_blocks, block_size, r + dr]
+ * ------------------------------------------------------------------------------------------- */
+size_t b200_mla_decode_workspace_bytes(int32_t batch, int32_t num_heads, int32_t kv_lora_rank,
+                                       int32_t rope_dim, int32_t dtype);
+int b200_mla_decode(const void* q_abs, const void* q_rope, const void* latent_cache,
+                    void* out_latent, const int32_t* block_tables, int64_t bt_stride,
+                    const int64_t* context_lens, int32_t batch, int32_t num_heads,
+                    int32_t kv_lora_rank, int32_t rope_dim, int32_t block_size,
+                    int64_t num_blocks, float scale, void* workspace, size_t workspace_bytes,
+                    int32_t dtype, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200LLM_H_ */

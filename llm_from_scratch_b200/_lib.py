@@ -1,0 +1,63 @@
+"""ctypes binding of ``libb200llm.so`` (the C ABI declared in ``include/b200llm.h``).
+
+There is no fallback: if the library has not been built, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libb200llm.so"
+
+DTYPE_F32 = 0
+DTYPE_BF16 = 1
+
+ERR_BOUNDS = -6
+
+_vp, _i32, _i64, _f32, _sz, _u64 = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t, C.c_uint64
+
+# name -> (restype, argtypes); mirrors include/b200llm.h declaration by declaration
+SIGNATURES = {
+    "b200_abi_version": (_i32, []),
+    "b200_strerror": (C.c_char_p, [_i32]),
+    "b200_sm_count": (_i32, []),
+    "b200_read_status": (_i32, [_vp, _vp, _vp]),
+    "b200_xxh64": (_u64, [_vp, _sz, _u64]),
+    "b200_block_hash": (_u64, [_vp, _i32, _u64, _i32]),
+    "b200_store_kvcache": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i64,
+                                  _i32, _vp, _vp]),
+    "b200_paged_decode_gqa_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),
+    "b200_paged_decode_gqa": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32,
+                                     _i32, _i64, _f32, _vp, _sz, _i32, _vp, _vp]),
+    "b200_prefill_varlen": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
+                                   _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _i64, _i32,
+                                   _i64, _i32, _vp, _vp]),
+    "b200_mla_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),
+    "b200_mla_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32,
+                               _i64, _f32, _vp, _sz, _i32, _vp, _vp]),
+}
+
+
+def load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build the CUDA library first "
+            "(python -m llm_from_scratch_b200._build); there is no CPU fallback")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = load()
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise B200Error(f"{what}: {lib.b200_strerror(rc).decode()} ({rc})")

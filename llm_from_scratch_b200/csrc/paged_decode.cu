@@ -1,0 +1,636 @@
+// Paged GQA decode attention.
+//
+// Fast path (bf16, block_size 16, head_dim 32/64/128, group size <= 16, Hkv <= 16)
+// ---------------------------------------------------------------------------------------------
+// The work is the flat list of all KV blocks of all sequences, in (sequence, block) order.  It is
+// cut into gridDim.x equal contiguous ranges, one per persistent CTA, so every CTA streams the
+// same number of bytes whatever the mix of context lengths ("split-K" falls out of the cut: a
+// sequence that crosses a cut is finished by the combine kernel).  Each CTA recomputes the cut
+// from context_lens itself, so the launch needs no host-side knowledge of the lengths and can be
+// captured in a CUDA graph.
+//
+// A CTA has one warp per KV head; the warps of a CTA walk the same blocks, so between them they
+// read each 16-token block of the pool as one contiguous Hkv*D*16*2-byte segment of K and one of
+// V.  Every warp owns a private 3-stage ring of (K tile, V tile) in shared memory that it fills
+// with 16-byte cp.async.cg copies (coalesced 256-byte rows, XOR-swizzled so ldmatrix is free of
+// bank conflicts) and drains with no CTA-wide barrier.  The G query heads that share the KV head
+// are the N dimension of mma.sync m16n8k16: S^T[token, head] = K . Q^T and O^T[d, head] =
+// V^T . P^T, so each K/V byte is read from HBM exactly once and used for all G heads.  Softmax is
+// the online form in fp32 in the log2 domain; column statistics are reduced with warp shuffles.
+//
+// Generic path (any dtype / head_dim <= 256 / block size): one CTA per (sequence, query head),
+// fp32 FMA arithmetic.  It is the path the fp32 engine configuration uses.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kTok = 16;    // tokens per KV block on the fast path
+constexpr int kStages = 3;  // (K,V) tiles in flight per warp
+constexpr int kMaxFastThreads = 512;
+
+struct DecodeArgs {
+  const void* q;
+  const void* kc;
+  const void* vc;
+  void* out;
+  const int32_t* bt;
+  int64_t bt_stride;
+  const int64_t* lens;
+  int batch, Hq, Hkv, D, bs;
+  int64_t num_blocks;
+  float scale_log2;  // softmax scale * log2(e)
+  float* part_o;     // [grid][2][Hq][D]   unnormalised partial outputs
+  float* part_ml;    // [grid][2][Hq][2]   running max (log2 domain) and sum
+  int32_t* seq_info; // [batch][2]         first / last CTA of a split sequence, or -1
+  int32_t* status;
+};
+
+__device__ __forceinline__ int num_kv_blocks(int64_t len, int64_t bt_stride, int bs) {
+  if (len <= 0) return 0;
+  int64_t n = (len + bs - 1) / bs;
+  return static_cast<int>(n < bt_stride ? n : bt_stride);
+}
+
+// inclusive scan over the CTA; `scratch` holds one int per warp
+__device__ __forceinline__ int block_inclusive_scan(int v, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  int x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) scratch[warp] = x;
+  __syncthreads();
+  int add = 0, tot = 0;
+  for (int w = 0; w < nw; ++w) {
+    int s = scratch[w];
+    if (w < warp) add += s;
+    tot += s;
+  }
+  __syncthreads();
+  *total = tot;
+  return x + add;
+}
+
+struct Cursor {
+  int seq, blk, nblk, len;
+};
+
+template <int D>
+__device__ __forceinline__ int swizzle_chunk(int c, int t) {
+  constexpr int CPR = D / 8;
+  if (CPR >= 8) return c ^ (t & 7);
+  return c ^ ((t >> 1) & (CPR - 1));  // CPR == 4: two rows share a 128-byte line
+}
+
+template <int D, int NT>
+__global__ void __launch_bounds__(kMaxFastThreads)
+paged_decode_bf16_kernel(const DecodeArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_scan[32];
+  __shared__ int s_start_seq, s_start_off;
+
+  constexpr int ROWB = D * 2;         // bytes per token row of one head
+  constexpr int TILEB = kTok * ROWB;  // one K (or V) tile
+  constexpr int CPR = D / 8;          // 16-byte chunks per row
+  constexpr int KS = D / 16;          // k-steps of QK^T == m-tiles of PV
+  constexpr int LOADS = (kTok * CPR) / 32;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int B = a.batch;
+  const int G = a.Hq / a.Hkv;
+  const int p = blockIdx.x, P = gridDim.x;
+
+  // ---- plan: total block count, then the (sequence, block) where this CTA's range starts ----
+  int local = 0;
+  for (int i = threadIdx.x; i < B; i += blockDim.x)
+    local += num_kv_blocks(a.lens[i], a.bt_stride, kTok);
+  int T;
+  block_inclusive_scan(local, s_scan, &T);
+  const int Q = (T + P - 1) / P;
+  const int start = p * Q;
+  if (Q == 0 || start >= T) return;
+  const int cnt = min(Q, T - start);
+  {
+    int carry = 0;
+    for (int base = 0; base < B; base += blockDim.x) {
+      const int i = base + threadIdx.x;
+      const int v = i < B ? num_kv_blocks(a.lens[i], a.bt_stride, kTok) : 0;
+      int tot;
+      const int incl = block_inclusive_scan(v, s_scan, &tot) + carry;
+      const int excl = incl - v;
+      if (v > 0 && excl <= start && start < incl) {
+        s_start_seq = i;
+        s_start_off = start - excl;
+      }
+      carry += tot;
+    }
+    __syncthreads();
+  }
+
+  auto load_seq = [&](Cursor& c) {
+    const int64_t len = a.lens[c.seq];
+    c.nblk = num_kv_blocks(len, a.bt_stride, kTok);
+    const int64_t cap = static_cast<int64_t>(c.nblk) * kTok;
+    if (len > cap) report(a.status, B200_ERR_BOUNDS);  // table row too short for the context
+    c.len = static_cast<int>(len < cap ? len : cap);
+  };
+  auto advance = [&](Cursor& c) {
+    if (++c.blk < c.nblk) return;
+    c.blk = 0;
+    do {
+      if (++c.seq >= B) {
+        c.nblk = INT_MAX;
+        c.len = 0;
+        c.seq = B - 1;
+        return;
+      }
+      load_seq(c);
+    } while (c.nblk == 0);
+  };
+
+  Cursor L, C;
+  L.seq = C.seq = s_start_seq;
+  L.blk = C.blk = s_start_off;
+  load_seq(L);
+  C.nblk = L.nblk;
+  C.len = L.len;
+  int next_id = a.bt[static_cast<int64_t>(L.seq) * a.bt_stride + L.blk];
+
+  const int h = warp;  // KV head of this warp
+  const uint32_t ring = smem_u32(smem) + warp * (kStages * 2 * TILEB);
+  const int64_t row_stride = static_cast<int64_t>(a.Hkv) * ROWB;  // bytes between tokens
+  const uint8_t* kbase = static_cast<const uint8_t*>(a.kc) + static_cast<int64_t>(h) * ROWB;
+  const uint8_t* vbase = static_cast<const uint8_t*>(a.vc) + static_cast<int64_t>(h) * ROWB;
+
+  auto issue = [&](int stage) {
+    const int id = next_id;
+    const int valid = L.len - L.blk * kTok;  // tokens of this block inside the context
+    const bool ok = static_cast<uint64_t>(static_cast<int64_t>(id)) <
+                    static_cast<uint64_t>(a.num_blocks);
+    if (!ok) report(a.status, B200_ERR_BOUNDS);
+    const int64_t blk_off = ok ? static_cast<int64_t>(id) * kTok * row_stride : 0;
+    const uint32_t kdst = ring + stage * (2 * TILEB), vdst = kdst + TILEB;
+#pragma unroll
+    for (int j = 0; j < LOADS; ++j) {
+      const int idx = lane + 32 * j;
+      const int t = idx / CPR, c = idx % CPR;
+      const int bytes = (ok && t < valid) ? 16 : 0;
+      const int64_t off = blk_off + (bytes ? t * row_stride + c * 16 : 0);
+      const uint32_t d = t * ROWB + swizzle_chunk<D>(c, t) * 16;
+      cp_async16(kdst + d, kbase + off, bytes);
+      cp_async16(vdst + d, vbase + off, bytes);
+    }
+  };
+
+  float o[NT][KS][4];
+  float mrow[NT][2], lrow[NT][2];
+  uint32_t qf[NT][KS][2];
+  int seg_first = 0;
+  bool fresh = true;
+
+  int issued = 0;
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (issued < cnt) {
+      issue(s);
+      if (++issued < cnt) {
+        advance(L);
+        next_id = a.bt[static_cast<int64_t>(L.seq) * a.bt_stride + L.blk];
+      }
+    }
+    cp_async_commit();
+  }
+
+  for (int j = 0; j < cnt; ++j) {
+    if (issued < cnt) {
+      issue((j + kStages - 1) % kStages);
+      if (++issued < cnt) {
+        advance(L);
+        next_id = a.bt[static_cast<int64_t>(L.seq) * a.bt_stride + L.blk];
+      }
+    }
+    cp_async_commit();
+
+    if (fresh) {
+      fresh = false;
+      seg_first = C.blk;
+      const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) +
+                                (static_cast<int64_t>(C.seq) * a.Hq + h * G) * D;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int head = nt * 8 + g;
+        mrow[nt][0] = mrow[nt][1] = -INFINITY;
+        lrow[nt][0] = lrow[nt][1] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          o[nt][ks][0] = o[nt][ks][1] = o[nt][ks][2] = o[nt][ks][3] = 0.f;
+          uint32_t b0 = 0, b1 = 0;
+          if (head < G) {
+            const uint32_t* src =
+                reinterpret_cast<const uint32_t*>(qp + head * D + ks * 16 + tq * 2);
+            b0 = __ldg(src);
+            b1 = __ldg(src + 4);
+          }
+          qf[nt][ks][0] = b0;
+          qf[nt][ks][1] = b1;
+        }
+      }
+    }
+
+    cp_async_wait<kStages - 1>();
+    __syncwarp();
+
+    const uint32_t kt = ring + (j % kStages) * (2 * TILEB), vt = kt + TILEB;
+    const int valid = C.len - C.blk * kTok;
+
+    // ---- S^T[token, head] = K . Q^T ----
+    float s[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    {
+      const int t = (lane & 7) + ((lane >> 3) & 1) * 8;  // matrices 0,2: tokens 0-7; 1,3: 8-15
+      const int chalf = lane >> 4;                       // matrices 2,3: upper 8 of the k-step
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t af[4];
+        ldmatrix_x4(af, kt + t * ROWB + swizzle_chunk<D>(2 * ks + chalf, t) * 16);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(s[nt], af, qf[nt][ks]);
+      }
+    }
+
+    // ---- online softmax over the token axis (rows g and g+8 of the tile) ----
+    uint32_t pb[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float x0 = s[nt][0] * a.scale_log2, x1 = s[nt][1] * a.scale_log2;
+      float x2 = s[nt][2] * a.scale_log2, x3 = s[nt][3] * a.scale_log2;
+      if (g >= valid) x0 = x1 = -INFINITY;
+      if (g + 8 >= valid) x2 = x3 = -INFINITY;
+      float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float mn0 = fmaxf(mrow[nt][0], mx0), mn1 = fmaxf(mrow[nt][1], mx1);
+      const float al0 = fast_exp2(mrow[nt][0] - mn0), al1 = fast_exp2(mrow[nt][1] - mn1);
+      mrow[nt][0] = mn0;
+      mrow[nt][1] = mn1;
+      const float p0 = fast_exp2(x0 - mn0), p1 = fast_exp2(x1 - mn1);
+      const float p2 = fast_exp2(x2 - mn0), p3 = fast_exp2(x3 - mn1);
+      lrow[nt][0] = lrow[nt][0] * al0 + p0 + p2;
+      lrow[nt][1] = lrow[nt][1] * al1 + p1 + p3;
+      pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
+      pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
+#pragma unroll
+      for (int mt = 0; mt < KS; ++mt) {
+        o[nt][mt][0] *= al0;
+        o[nt][mt][1] *= al1;
+        o[nt][mt][2] *= al0;
+        o[nt][mt][3] *= al1;
+      }
+    }
+
+    // ---- O^T[d, head] += V^T . P^T ----
+    {
+      const int t = (lane & 7) + (lane >> 4) * 8;  // matrices 0,1: tokens 0-7; 2,3: tokens 8-15
+      const int chalf = (lane >> 3) & 1;           // matrices 1,3: upper 8 of the 16 d values
+#pragma unroll
+      for (int mt = 0; mt < KS; ++mt) {
+        uint32_t af[4];
+        ldmatrix_x4_trans(af, vt + t * ROWB + swizzle_chunk<D>(2 * mt + chalf, t) * 16);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(o[nt][mt], af, pb[nt]);
+      }
+    }
+    __syncwarp();  // the stage may be refilled by the next trip
+
+    const bool seq_end = (C.blk == C.nblk - 1);
+    if (seq_end || j == cnt - 1) {
+      fresh = true;
+      const bool whole = seq_end && seg_first == 0;
+      const int slot = seg_first > 0 ? 0 : 1;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float l0 = lrow[nt][0], l1 = lrow[nt][1];
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+          l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+        }
+        const int head0 = nt * 8 + tq * 2;
+        if (whole) {
+          const float i0 = 1.f / l0, i1 = 1.f / l1;
+          __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) +
+                              (static_cast<int64_t>(C.seq) * a.Hq + h * G) * D;
+#pragma unroll
+          for (int mt = 0; mt < KS; ++mt) {
+            const int d = mt * 16 + g;
+            if (head0 < G) {
+              op[head0 * D + d] = __float2bfloat16_rn(o[nt][mt][0] * i0);
+              op[head0 * D + d + 8] = __float2bfloat16_rn(o[nt][mt][2] * i0);
+            }
+            if (head0 + 1 < G) {
+              op[(head0 + 1) * D + d] = __float2bfloat16_rn(o[nt][mt][1] * i1);
+              op[(head0 + 1) * D + d + 8] = __float2bfloat16_rn(o[nt][mt][3] * i1);
+            }
+          }
+        } else {
+          const int64_t pslot = static_cast<int64_t>(p) * 2 + slot;
+          float* po = a.part_o + (pslot * a.Hq + h * G) * D;
+          float* pml = a.part_ml + (pslot * a.Hq + h * G) * 2;
+#pragma unroll
+          for (int mt = 0; mt < KS; ++mt) {
+            const int d = mt * 16 + g;
+            if (head0 < G) {
+              po[head0 * D + d] = o[nt][mt][0];
+              po[head0 * D + d + 8] = o[nt][mt][2];
+            }
+            if (head0 + 1 < G) {
+              po[(head0 + 1) * D + d] = o[nt][mt][1];
+              po[(head0 + 1) * D + d + 8] = o[nt][mt][3];
+            }
+          }
+          if (g == 0) {
+            if (head0 < G) {
+              pml[head0 * 2] = mrow[nt][0];
+              pml[head0 * 2 + 1] = l0;
+            }
+            if (head0 + 1 < G) {
+              pml[(head0 + 1) * 2] = mrow[nt][1];
+              pml[(head0 + 1) * 2 + 1] = l1;
+            }
+          }
+        }
+      }
+      if (seq_end && warp == 0 && lane == 0) {
+        const int seq_start_flat = start + j - C.blk;
+        a.seq_info[2 * C.seq] = whole ? -1 : seq_start_flat / Q;
+        a.seq_info[2 * C.seq + 1] = whole ? -1 : p;
+      }
+    }
+    if (j + 1 < cnt) advance(C);
+  }
+  cp_async_wait<0>();
+}
+
+// Merges the partial results of sequences that were cut across CTAs; zero-fills rows whose
+// context is empty.  One CTA per sequence.
+__global__ void __launch_bounds__(256) paged_decode_combine_kernel(const DecodeArgs a) {
+  const int i = blockIdx.x;
+  const int n = a.Hq * a.D;
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + static_cast<int64_t>(i) * n;
+  if (a.lens[i] <= 0) {
+    for (int e = threadIdx.x; e < n; e += blockDim.x) op[e] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int first = a.seq_info[2 * i], last = a.seq_info[2 * i + 1];
+  if (first < 0) return;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int head = e / a.D;
+    float M = -INFINITY;
+    for (int p = first; p <= last; ++p) {
+      const int64_t ps = static_cast<int64_t>(p) * 2 + (p == first ? 1 : 0);
+      M = fmaxf(M, a.part_ml[(ps * a.Hq + head) * 2]);
+    }
+    float acc = 0.f, Lsum = 0.f;
+    for (int p = first; p <= last; ++p) {
+      const int64_t ps = static_cast<int64_t>(p) * 2 + (p == first ? 1 : 0);
+      const float w = exp2f(a.part_ml[(ps * a.Hq + head) * 2] - M);
+      Lsum += w * a.part_ml[(ps * a.Hq + head) * 2 + 1];
+      acc += w * a.part_o[ps * n + e];
+    }
+    op[e] = __float2bfloat16_rn(acc / Lsum);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic path: grid (batch, Hq), 4 warps; warp w takes tokens w, w+4, ...; a lane owns the
+// head-dim elements lane, lane+32, ...
+// ---------------------------------------------------------------------------------------------
+constexpr int kSimpleWarps = 4;
+constexpr int kSimpleMaxPerLane = 8;  // head_dim <= 256
+
+template <typename T>
+__global__ void __launch_bounds__(kSimpleWarps * 32) paged_decode_simple_kernel(const DecodeArgs a) {
+  __shared__ float s_m[kSimpleWarps], s_l[kSimpleWarps];
+  __shared__ float s_acc[kSimpleWarps][kSimpleMaxPerLane * 32];
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int D = a.D, G = a.Hq / a.Hkv, kvh = head / G;
+  T* op = static_cast<T*>(a.out) + (static_cast<int64_t>(seq) * a.Hq + head) * D;
+  int64_t len64 = a.lens[seq];
+  if (len64 <= 0) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) op[d] = from_float<T>(0.f);
+    return;
+  }
+  const int64_t cap = a.bt_stride * a.bs;
+  if (len64 > cap) {
+    report(a.status, B200_ERR_BOUNDS);
+    len64 = cap;
+  }
+  const int len = static_cast<int>(len64);
+  const T* qp = static_cast<const T*>(a.q) + (static_cast<int64_t>(seq) * a.Hq + head) * D;
+  float qv[kSimpleMaxPerLane], acc[kSimpleMaxPerLane];
+#pragma unroll
+  for (int k = 0; k < kSimpleMaxPerLane; ++k) {
+    const int d = lane + 32 * k;
+    qv[k] = d < D ? to_float<T>(qp[d]) : 0.f;
+    acc[k] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  const T* kc = static_cast<const T*>(a.kc);
+  const T* vc = static_cast<const T*>(a.vc);
+  for (int t = warp; t < len; t += kSimpleWarps) {
+    const int id = a.bt[static_cast<int64_t>(seq) * a.bt_stride + t / a.bs];
+    if (static_cast<uint64_t>(static_cast<int64_t>(id)) >= static_cast<uint64_t>(a.num_blocks)) {
+      report(a.status, B200_ERR_BOUNDS);
+      continue;
+    }
+    const int64_t row = ((static_cast<int64_t>(id) * a.bs + t % a.bs) * a.Hkv + kvh) * D;
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < kSimpleMaxPerLane; ++k) {
+      const int d = lane + 32 * k;
+      if (d < D) dot += qv[k] * to_float<T>(kc[row + d]);
+    }
+    dot = warp_sum(dot) * a.scale_log2;
+    const float mn = fmaxf(m, dot);
+    const float al = exp2f(m - mn), pw = exp2f(dot - mn);
+    l = l * al + pw;
+#pragma unroll
+    for (int k = 0; k < kSimpleMaxPerLane; ++k) {
+      const int d = lane + 32 * k;
+      if (d < D) acc[k] = acc[k] * al + pw * to_float<T>(vc[row + d]);
+    }
+    m = mn;
+  }
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_l[warp] = l;
+  }
+#pragma unroll
+  for (int k = 0; k < kSimpleMaxPerLane; ++k) s_acc[warp][lane + 32 * k] = acc[k];
+  __syncthreads();
+  float M = -INFINITY;
+  for (int w = 0; w < kSimpleWarps; ++w) M = fmaxf(M, s_m[w]);
+  float Lsum = 0.f;
+  float wgt[kSimpleWarps];
+  for (int w = 0; w < kSimpleWarps; ++w) {
+    wgt[w] = s_m[w] == -INFINITY ? 0.f : exp2f(s_m[w] - M);
+    Lsum += wgt[w] * s_l[w];
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = 0.f;
+    for (int w = 0; w < kSimpleWarps; ++w) v += wgt[w] * s_acc[w][d];
+    op[d] = from_float<T>(Lsum > 0.f ? v / Lsum : 0.f);
+  }
+}
+
+struct FastPlan {
+  bool ok;
+  int nt;
+  int threads;
+  size_t smem;
+  int ctas_per_sm;
+};
+
+FastPlan fast_plan(int Hq, int Hkv, int D, int bs, int dtype) {
+  FastPlan pl{};
+  pl.ok = false;
+  if (dtype != B200_DTYPE_BF16 || bs != kTok) return pl;
+  if (D != 32 && D != 64 && D != 128) return pl;
+  if (Hkv <= 0 || Hkv > kMaxFastThreads / 32 || Hq % Hkv != 0) return pl;
+  const int G = Hq / Hkv;
+  if (G > 16) return pl;
+  pl.nt = G > 8 ? 2 : 1;
+  pl.threads = Hkv * 32;
+  pl.smem = static_cast<size_t>(Hkv) * kStages * 2 * kTok * D * 2;
+  const size_t budget = 220 * 1024;
+  if (pl.smem > budget) return pl;
+  int c = static_cast<int>(budget / (pl.smem + 1024));
+  const int by_threads = 2048 / pl.threads;
+  if (c > by_threads) c = by_threads;
+  if (c > 8) c = 8;
+  if (c < 1) c = 1;
+  pl.ctas_per_sm = c;
+  pl.ok = true;
+  return pl;
+}
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+template <int D, int NT>
+int launch_fast(const DecodeArgs& a, const FastPlan& pl, int grid, cudaStream_t s) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(paged_decode_bf16_kernel<D, NT>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             220 * 1024) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    configured[dev] = true;
+  }
+  paged_decode_bf16_kernel<D, NT><<<grid, pl.threads, pl.smem, s>>>(a);
+  return launch_result();
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" size_t b200_paged_decode_gqa_workspace_bytes(int32_t batch, int32_t num_q_heads,
+                                                        int32_t num_kv_heads, int32_t head_dim,
+                                                        int32_t dtype) {
+  using namespace b200;
+  if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
+  const FastPlan pl = fast_plan(num_q_heads, num_kv_heads, head_dim, kTok, dtype);
+  if (!pl.ok) return 256;
+  int sms = sm_count_cached();
+  if (sms <= 0) sms = 148;
+  const size_t grid = static_cast<size_t>(sms) * pl.ctas_per_sm;
+  size_t bytes = align256(grid * 2 * num_q_heads * head_dim * sizeof(float));
+  bytes += align256(grid * 2 * num_q_heads * 2 * sizeof(float));
+  bytes += align256(static_cast<size_t>(batch) * 2 * sizeof(int32_t));
+  return bytes;
+}
+
+extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const void* v_cache,
+                                     void* out, const int32_t* block_tables, int64_t bt_stride,
+                                     const int64_t* context_lens, int32_t batch,
+                                     int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                     int32_t block_size, int64_t num_blocks, float scale,
+                                     void* workspace, size_t workspace_bytes, int32_t dtype,
+                                     int32_t* status, void* stream) {
+  using namespace b200;
+  if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || block_size <= 0 ||
+      num_blocks < 0 || bt_stride <= 0)
+    return B200_ERR_ARG;
+  if (num_q_heads % num_kv_heads != 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (batch == 0) return B200_OK;
+  if (!q || !out || !block_tables || !context_lens) return B200_ERR_ARG;
+  if (num_blocks > 0 && (!k_cache || !v_cache)) return B200_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  DecodeArgs a{};
+  a.q = q;
+  a.kc = k_cache;
+  a.vc = v_cache;
+  a.out = out;
+  a.bt = block_tables;
+  a.bt_stride = bt_stride;
+  a.lens = context_lens;
+  a.batch = batch;
+  a.Hq = num_q_heads;
+  a.Hkv = num_kv_heads;
+  a.D = head_dim;
+  a.bs = block_size;
+  a.num_blocks = num_blocks;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+
+  const FastPlan pl = fast_plan(num_q_heads, num_kv_heads, head_dim, block_size, dtype);
+  const bool fast = pl.ok && aligned16(q) && aligned16(k_cache) && aligned16(v_cache);
+  if (fast) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return B200_ERR_NO_DEVICE;
+    const size_t need = b200_paged_decode_gqa_workspace_bytes(batch, num_q_heads, num_kv_heads,
+                                                              head_dim, dtype);
+    if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
+    const size_t grid = static_cast<size_t>(sms) * pl.ctas_per_sm;
+    uint8_t* w = static_cast<uint8_t*>(workspace);
+    a.part_o = reinterpret_cast<float*>(w);
+    w += align256(grid * 2 * num_q_heads * head_dim * sizeof(float));
+    a.part_ml = reinterpret_cast<float*>(w);
+    w += align256(grid * 2 * num_q_heads * 2 * sizeof(float));
+    a.seq_info = reinterpret_cast<int32_t*>(w);
+    int rc;
+    const int gi = static_cast<int>(grid);
+    if (head_dim == 128)
+      rc = pl.nt == 1 ? launch_fast<128, 1>(a, pl, gi, s) : launch_fast<128, 2>(a, pl, gi, s);
+    else if (head_dim == 64)
+      rc = pl.nt == 1 ? launch_fast<64, 1>(a, pl, gi, s) : launch_fast<64, 2>(a, pl, gi, s);
+    else
+      rc = pl.nt == 1 ? launch_fast<32, 1>(a, pl, gi, s) : launch_fast<32, 2>(a, pl, gi, s);
+    if (rc != B200_OK) return rc;
+    paged_decode_combine_kernel<<<batch, 256, 0, s>>>(a);
+    return launch_result();
+  }
+
+  if (head_dim > kSimpleMaxPerLane * 32) return B200_ERR_UNSUPPORTED;
+  dim3 grid(batch, num_q_heads);
+  if (dtype == B200_DTYPE_F32)
+    paged_decode_simple_kernel<float><<<grid, kSimpleWarps * 32, 0, s>>>(a);
+  else
+    paged_decode_simple_kernel<__nv_bfloat16><<<grid, kSimpleWarps * 32, 0, s>>>(a);
+  return launch_result();
+}

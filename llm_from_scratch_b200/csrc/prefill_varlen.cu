@@ -1,0 +1,182 @@
+// Ragged (varlen) causal prefill attention over cu_seqlens-packed sequences.
+//
+// Generic path: one warp per (sequence, query token, query head); a lane owns the head-dim
+// elements lane, lane+32, ...; keys are visited in order with an fp32 online softmax.  Keys and
+// values come either from the packed k/v tensors of the step or, when a cached prefix exists,
+// from the paged pool through block_tables (bottom-right aligned causal mask).
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+struct PrefillArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  int64_t q_stride, k_stride, v_stride;  // token strides, elements
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int num_seqs, Hq, Hkv, Dqk, Dv;
+  float scale_log2;
+  const void* kc;
+  const void* vc;
+  const int32_t* bt;
+  int64_t bt_stride;
+  int bs;
+  int64_t num_blocks;
+  int32_t* status;
+};
+
+constexpr int kWarps = 4;
+constexpr int kMaxPerLane = 8;  // head dims <= 256
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) prefill_simple_kernel(const PrefillArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s = blockIdx.z, head = blockIdx.y;
+  const int qi = blockIdx.x * kWarps + warp;
+  const int q0 = a.cu_q[s], q_len = a.cu_q[s + 1] - q0;
+  const int k0 = a.cu_k[s], k_len = a.cu_k[s + 1] - k0;
+  if (qi >= q_len) return;
+  const int G = a.Hq / a.Hkv, kvh = head / G;
+  const int nkeys = k_len - q_len + qi + 1;  // causal, bottom-right aligned
+  const T* qp = static_cast<const T*>(a.q) + static_cast<int64_t>(q0 + qi) * a.q_stride +
+                static_cast<int64_t>(head) * a.Dqk;
+  float qv[kMaxPerLane], acc[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    qv[i] = d < a.Dqk ? to_float<T>(qp[d]) : 0.f;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int j = 0; j < nkeys; ++j) {
+    const T* kp;
+    const T* vp;
+    if (a.bt == nullptr) {
+      kp = static_cast<const T*>(a.k) + static_cast<int64_t>(k0 + j) * a.k_stride +
+           static_cast<int64_t>(kvh) * a.Dqk;
+      vp = static_cast<const T*>(a.v) + static_cast<int64_t>(k0 + j) * a.v_stride +
+           static_cast<int64_t>(kvh) * a.Dv;
+    } else {
+      const int blk = j / a.bs;
+      if (blk >= a.bt_stride) {
+        report(a.status, B200_ERR_BOUNDS);
+        break;
+      }
+      const int id = a.bt[static_cast<int64_t>(s) * a.bt_stride + blk];
+      if (static_cast<uint64_t>(static_cast<int64_t>(id)) >= static_cast<uint64_t>(a.num_blocks)) {
+        report(a.status, B200_ERR_BOUNDS);
+        continue;
+      }
+      const int64_t row = (static_cast<int64_t>(id) * a.bs + j % a.bs) * a.Hkv + kvh;
+      kp = static_cast<const T*>(a.kc) + row * a.Dqk;
+      vp = static_cast<const T*>(a.vc) + row * a.Dv;
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < a.Dqk) dot += qv[i] * to_float<T>(kp[d]);
+    }
+    dot = warp_sum(dot) * a.scale_log2;
+    const float mn = fmaxf(m, dot);
+    const float al = exp2f(m - mn), pw = exp2f(dot - mn);
+    l = l * al + pw;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < a.Dv) acc[i] = acc[i] * al + pw * to_float<T>(vp[d]);
+    }
+    m = mn;
+  }
+  T* op = static_cast<T*>(a.out) + (static_cast<int64_t>(q0 + qi) * a.Hq + head) * a.Dv;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    if (d < a.Dv) op[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+}  // namespace
+
+// fast bf16 tensor-core path, defined in prefill_mma.cu; returns B200_ERR_UNSUPPORTED when the
+// shape is outside what it implements
+int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
+                       int64_t k_stride, int64_t v_stride, const int32_t* cu_q,
+                       const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv,
+                       int Dqk, int Dv, float scale, const void* kc, const void* vc,
+                       const int32_t* bt, int64_t bt_stride, int bs, int64_t num_blocks,
+                       int32_t* status, cudaStream_t s);
+
+}  // namespace b200
+
+extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
+                                   int64_t q_token_stride, int64_t k_token_stride,
+                                   int64_t v_token_stride, const int32_t* cu_seqlens_q,
+                                   const int32_t* cu_seqlens_k, int32_t num_seqs,
+                                   int32_t max_seqlen_q, int32_t max_seqlen_k,
+                                   int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
+                                   int32_t head_dim_v, float scale, const void* k_cache,
+                                   const void* v_cache, const int32_t* block_tables,
+                                   int64_t bt_stride, int32_t block_size, int64_t num_blocks,
+                                   int32_t dtype, int32_t* status, void* stream) {
+  using namespace b200;
+  if (num_seqs < 0 || max_seqlen_q < 0 || max_seqlen_k < 0 || num_q_heads <= 0 ||
+      num_kv_heads <= 0 || head_dim_qk <= 0 || head_dim_v <= 0)
+    return B200_ERR_ARG;
+  if (num_q_heads % num_kv_heads != 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (num_seqs == 0 || max_seqlen_q == 0) return B200_OK;
+  if (!q || !out || !cu_seqlens_q || !cu_seqlens_k) return B200_ERR_ARG;
+  if (block_tables == nullptr) {
+    if (!k || !v) return B200_ERR_ARG;
+  } else {
+    if (!k_cache || !v_cache || block_size <= 0 || bt_stride <= 0 || num_blocks <= 0)
+      return B200_ERR_ARG;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (dtype == B200_DTYPE_BF16) {
+    const int rc = prefill_mma_launch(q, k, v, out, q_token_stride, k_token_stride,
+                                      v_token_stride, cu_seqlens_q, cu_seqlens_k, num_seqs,
+                                      max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk,
+                                      head_dim_v, scale, k_cache, v_cache, block_tables, bt_stride,
+                                      block_size, num_blocks, status, s);
+    if (rc != B200_ERR_UNSUPPORTED) return rc;
+  }
+
+  if (head_dim_qk > kMaxPerLane * 32 || head_dim_v > kMaxPerLane * 32) return B200_ERR_UNSUPPORTED;
+  if (num_seqs > 65535 || num_q_heads > 65535) return B200_ERR_UNSUPPORTED;
+  PrefillArgs a{};
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.out = out;
+  a.q_stride = q_token_stride;
+  a.k_stride = k_token_stride;
+  a.v_stride = v_token_stride;
+  a.cu_q = cu_seqlens_q;
+  a.cu_k = cu_seqlens_k;
+  a.num_seqs = num_seqs;
+  a.Hq = num_q_heads;
+  a.Hkv = num_kv_heads;
+  a.Dqk = head_dim_qk;
+  a.Dv = head_dim_v;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.kc = k_cache;
+  a.vc = v_cache;
+  a.bt = block_tables;
+  a.bt_stride = bt_stride;
+  a.bs = block_size;
+  a.num_blocks = num_blocks;
+  a.status = status;
+  dim3 grid((max_seqlen_q + kWarps - 1) / kWarps, num_q_heads, num_seqs);
+  if (dtype == B200_DTYPE_F32)
+    prefill_simple_kernel<float><<<grid, kWarps * 32, 0, s>>>(a);
+  else
+    prefill_simple_kernel<__nv_bfloat16><<<grid, kWarps * 32, 0, s>>>(a);
+  return launch_result();
+}

@@ -1,0 +1,230 @@
+"""Tensor-level wrappers over the C ABI: the calls the attention layers of the engine make.
+
+Every function takes CUDA tensors, checks shapes/dtypes on the host, and enqueues the kernel on
+the current CUDA stream.  Nothing here computes on the CPU; a CPU tensor is an error.
+"""
+from __future__ import annotations
+
+import array
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
+
+_status: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, str], torch.Tensor] = {}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; the kernels take float32 or bfloat16") from None
+
+
+def _cuda(*ts: torch.Tensor | None) -> torch.device:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("b200 ops take CUDA tensors only (there is no CPU path)")
+        if dev is not None and t.device != dev:
+            raise ValueError("all tensors must be on the same device")
+        dev = t.device
+    return dev
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 that kernels set when they skip an out-of-pool block id or slot."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronises the current stream, raises if a kernel reported a device-side fault."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    st = status_word(device)
+    host = array.array("i", [0])
+    addr, _ = host.buffer_info()
+    check(lib.b200_read_status(st.data_ptr(), addr, _stream()), "read_status")
+    if host[0] != 0:
+        check(host[0], "device-side check")
+
+
+def workspace(device: torch.device, nbytes: int, tag: str) -> torch.Tensor:
+    """Grow-only scratch buffer per (device, op); allocated outside any graph capture."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, tag)
+    w = _workspaces.get(key)
+    if w is None or w.numel() < nbytes:
+        w = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = w
+    return w
+
+
+def store_kvcache(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  slot_mapping: torch.Tensor) -> None:
+    """k_cache[slot_mapping[t]] = k[t], v likewise; slots < 0 are skipped.
+
+    k, v: [T, Hkv, D] (rows contiguous, token stride free); caches: [..., Hkv, D] contiguous.
+    """
+    dev = _cuda(k, v, k_cache, v_cache, slot_mapping)
+    T, Hkv, D = k.shape
+    if v.shape != k.shape or k.dtype != v.dtype or k_cache.dtype != k.dtype or v_cache.dtype != k.dtype:
+        raise ValueError("k/v/cache shape or dtype mismatch")
+    if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != T or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous int64 tensor with one entry per token")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("caches must be contiguous")
+    if k.stride(2) != 1 or k.stride(1) != D or v.stride(2) != 1 or v.stride(1) != D:
+        raise ValueError("k/v rows (Hkv*D) must be contiguous")
+    if k_cache.shape[-2:] != (Hkv, D) or v_cache.shape != k_cache.shape:
+        raise ValueError("cache trailing dims must be (Hkv, D)")
+    num_slots = k_cache.numel() // (Hkv * D)
+    check(lib.b200_store_kvcache(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
+                                 k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(),
+                                 T, Hkv, D, num_slots, _dt(k), status_word(dev).data_ptr(),
+                                 _stream()), "store_kvcache")
+
+
+def paged_decode_gqa(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_tables: torch.Tensor, context_lens: torch.Tensor, scale: float,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """One query token per sequence over a paged KV pool.
+
+    q: [B, Hq, D]; caches: [num_blocks, block_size, Hkv, D]; block_tables: [B, maxb] int32;
+    context_lens: [B] int64.  Returns out [B, Hq, D].
+    """
+    dev = _cuda(q, k_cache, v_cache, block_tables, context_lens, out)
+    B, Hq, D = q.shape
+    nb, bs, Hkv, Dc = k_cache.shape
+    if Dc != D or v_cache.shape != k_cache.shape or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("cache shape/dtype does not match q")
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int64:
+        raise ValueError("block_tables must be int32 and context_lens int64")
+    if block_tables.dim() != 2 or block_tables.shape[0] != B or block_tables.stride(1) != 1:
+        raise ValueError("block_tables must be [B, maxb] with contiguous rows")
+    if context_lens.numel() != B or not context_lens.is_contiguous():
+        raise ValueError("context_lens must be a contiguous [B] tensor")
+    if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("q and caches must be contiguous")
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must match q")
+    need = lib.b200_paged_decode_gqa_workspace_bytes(B, Hq, Hkv, D, _dt(q))
+    ws = workspace(dev, need, "decode")
+    check(lib.b200_paged_decode_gqa(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                    out.data_ptr(), block_tables.data_ptr(),
+                                    block_tables.stride(0), context_lens.data_ptr(), B, Hq, Hkv, D,
+                                    bs, nb, float(scale), ws.data_ptr(), ws.numel(), _dt(q),
+                                    status_word(dev).data_ptr(), _stream()), "paged_decode_gqa")
+    return out
+
+
+def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None,
+                   cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int,
+                   max_seqlen_k: int, scale: float, k_cache: torch.Tensor | None = None,
+                   v_cache: torch.Tensor | None = None, block_tables: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention over packed ragged sequences.
+
+    q: [Tq, Hq, Dqk].  Without ``block_tables``: k [Tk, Hkv, Dqk], v [Tk, Hkv, Dv] are the packed
+    keys/values.  With ``block_tables`` (a cached prefix exists) keys/values are read from the
+    paged caches [num_blocks, block_size, Hkv, D*].  Returns out [Tq, Hq, Dv].
+    """
+    dev = _cuda(q, k, v, cu_seqlens_q, cu_seqlens_k, k_cache, v_cache, block_tables, out)
+    Tq, Hq, Dqk = q.shape
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
+        raise ValueError("cu_seqlens must be int32")
+    num_seqs = cu_seqlens_q.numel() - 1
+    if cu_seqlens_k.numel() != num_seqs + 1:
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must have the same length")
+    if q.stride(2) != 1 or q.stride(1) != Dqk:
+        raise ValueError("q heads must be contiguous")
+    if block_tables is None:
+        if k is None or v is None:
+            raise ValueError("k and v are required without block_tables")
+        Hkv, Dv = v.shape[1], v.shape[2]
+        if k.shape[1] != Hkv or k.shape[2] != Dqk or k.dtype != q.dtype or v.dtype != q.dtype:
+            raise ValueError("k/v shape or dtype mismatch")
+        if k.stride(2) != 1 or k.stride(1) != Dqk or v.stride(2) != 1 or v.stride(1) != Dv:
+            raise ValueError("k/v heads must be contiguous")
+        kp, vp, ks, vs = k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0)
+        kcp = vcp = btp = 0
+        bts = bs = nb = 0
+    else:
+        if k_cache is None or v_cache is None:
+            raise ValueError("paged prefill needs k_cache and v_cache")
+        nb, bs, Hkv, Dk = k_cache.shape
+        Dv = v_cache.shape[3]
+        if Dk != Dqk or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+            raise ValueError("cache shape/dtype does not match q")
+        if block_tables.dtype != torch.int32 or block_tables.shape[0] != num_seqs or block_tables.stride(1) != 1:
+            raise ValueError("block_tables must be int32 [num_seqs, maxb]")
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise ValueError("caches must be contiguous")
+        kp = vp = 0
+        ks = vs = 0
+        kcp, vcp, btp, bts = k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(), block_tables.stride(0)
+    if out is None:
+        out = torch.empty((Tq, Hq, Dv), dtype=q.dtype, device=q.device)
+    elif out.shape != (Tq, Hq, Dv) or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [Tq, Hq, Dv] tensor")
+    check(lib.b200_prefill_varlen(q.data_ptr(), kp, vp, out.data_ptr(), q.stride(0), ks, vs,
+                                  cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
+                                  int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, Dqk, Dv,
+                                  float(scale), kcp, vcp, btp, bts, bs, nb, _dt(q),
+                                  status_word(dev).data_ptr(), _stream()), "prefill_varlen")
+    return out
+
+
+def mla_decode(q_abs: torch.Tensor, q_rope: torch.Tensor, latent_cache: torch.Tensor,
+               block_tables: torch.Tensor, context_lens: torch.Tensor, scale: float,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """Absorbed MLA decode over a paged latent pool.
+
+    q_abs: [B, H, r]; q_rope: [B, H, dr]; latent_cache: [num_blocks, block_size, r + dr];
+    returns the attention-weighted latent [B, H, r].
+    """
+    dev = _cuda(q_abs, q_rope, latent_cache, block_tables, context_lens, out)
+    B, H, r = q_abs.shape
+    dr = q_rope.shape[2]
+    nb, bs, row = latent_cache.shape
+    if row != r + dr or q_rope.shape[:2] != (B, H):
+        raise ValueError("latent row must be kv_lora_rank + rope_dim wide")
+    if latent_cache.dtype != q_abs.dtype or q_rope.dtype != q_abs.dtype:
+        raise ValueError("dtype mismatch")
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int64:
+        raise ValueError("block_tables must be int32 and context_lens int64")
+    if block_tables.shape[0] != B or block_tables.stride(1) != 1 or context_lens.numel() != B:
+        raise ValueError("metadata batch mismatch")
+    if not (q_abs.is_contiguous() and q_rope.is_contiguous() and latent_cache.is_contiguous()):
+        raise ValueError("inputs must be contiguous")
+    if out is None:
+        out = torch.empty_like(q_abs)
+    need = lib.b200_mla_decode_workspace_bytes(B, H, r, dr, _dt(q_abs))
+    ws = workspace(dev, need, "mla")
+    check(lib.b200_mla_decode(q_abs.data_ptr(), q_rope.data_ptr(), latent_cache.data_ptr(),
+                              out.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+                              context_lens.data_ptr(), B, H, r, dr, bs, nb, float(scale),
+                              ws.data_ptr(), ws.numel(), _dt(q_abs), status_word(dev).data_ptr(),
+                              _stream()), "mla_decode")
+    return out
+
+
+def block_hash(token_ids, prefix: int = -1) -> int:
+    """Chained XXH64 block hash; same value as BlockManager.compute_hash of the reference."""
+    buf = array.array("i", token_ids)
+    addr, n = buf.buffer_info()
+    return int(lib.b200_block_hash(addr, n, 0 if prefix == -1 else prefix, 0 if prefix == -1 else 1))

@@ -1,0 +1,76 @@
+"""Seeded synthetic workloads with the shapes and value distributions of the benchmark configs.
+
+No public dataset is involved: token ids are uniform over the vocabulary, q/K/V are N(0,1), and
+lengths follow the distribution each configuration names.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+
+@dataclass
+class PagedDecodeCase:
+    """Metadata of a paged-decode batch (host side, numpy)."""
+    context_lens: np.ndarray   # [B] int64
+    block_tables: np.ndarray   # [B, maxb] int32, -1 padded
+    slot_mapping: np.ndarray   # [B] int64: slot of the last token of every sequence
+    num_blocks: int
+    block_size: int
+
+    @property
+    def batch(self) -> int:
+        return int(self.context_lens.shape[0])
+
+    @property
+    def total_tokens(self) -> int:
+        return int(self.context_lens.sum())
+
+
+def deal_blocks(context_lens, block_size: int, rng: np.random.Generator, pad_blocks: int = 0,
+                pad_value: int = -1) -> PagedDecodeCase:
+    """Physical pool = random permutation of block ids, dealt to the sequences in order."""
+    lens = np.asarray(context_lens, dtype=np.int64)
+    nblk = (lens + block_size - 1) // block_size
+    total = int(nblk.sum()) + pad_blocks
+    perm = rng.permutation(total).astype(np.int32)
+    maxb = max(1, int(nblk.max()) if len(nblk) else 1)
+    tables = np.full((len(lens), maxb), pad_value, dtype=np.int32)
+    slots = np.full(len(lens), -1, dtype=np.int64)
+    pos = 0
+    for i, n in enumerate(nblk):
+        n = int(n)
+        tables[i, :n] = perm[pos:pos + n]
+        pos += n
+        if lens[i] > 0:
+            last = int(lens[i]) - 1
+            slots[i] = int(tables[i, last // block_size]) * block_size + last % block_size
+    return PagedDecodeCase(lens, tables, slots, max(total, 1), block_size)
+
+
+def c2_decode_case(batch: int = 256, lo: int = 128, hi: int = 8192, block_size: int = 16,
+                   seed: int = 1) -> PagedDecodeCase:
+    """Paged GQA decode microbenchmark metadata: context lengths log-uniform in [lo, hi]."""
+    rng = np.random.default_rng(seed)
+    lens = np.rint(np.exp(rng.uniform(math.log(lo), math.log(hi), size=batch))).astype(np.int64)
+    lens = np.clip(lens, lo, hi)
+    return deal_blocks(lens, block_size, rng, pad_blocks=8)
+
+
+def decode_algorithmic_bytes(case: PagedDecodeCase, num_q_heads: int, num_kv_heads: int,
+                             head_dim: int, itemsize: int) -> int:
+    """Bytes one paged-decode call must move: every K and V row of every live context once, the
+    block-table entries and context lengths it walks, q in and out."""
+    lens = case.context_lens
+    kv = int(lens.sum()) * 2 * num_kv_heads * head_dim * itemsize
+    meta = int(((lens + case.block_size - 1) // case.block_size).sum()) * 4 + 8 * case.batch
+    qo = case.batch * 2 * num_q_heads * head_dim * itemsize
+    return kv + meta + qo
+
+
+def randn_bf16_pool(shape, seed: int, device) -> torch.Tensor:
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn(shape, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)

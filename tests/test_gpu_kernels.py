@@ -1,0 +1,304 @@
+"""Parity of the CUDA kernels (through the C ABI) against the CPU oracle on seeded inputs.
+
+Tolerances: fp32 kernels 2e-5 max-abs; bf16 kernels 2e-2 max-abs and 1e-2 mean-relative error
+against the fp32 oracle evaluated on the same bf16-rounded inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from llm_from_scratch_b200.workloads import deal_blocks
+
+pytestmark = pytest.mark.gpu
+
+BF16_MAX_ABS = 2e-2
+BF16_MEAN_REL = 1e-2
+F32_MAX_ABS = 2e-5
+
+
+def _ops():
+    from llm_from_scratch_b200 import ops
+    return ops
+
+
+def _oracle():
+    from oracle import attention
+    return attention
+
+
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype):
+    got = got.float().cpu()
+    want = want.float().cpu()
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    if dtype == torch.float32:
+        assert err.max().item() <= F32_MAX_ABS, err.max().item()
+    else:
+        assert err.max().item() <= BF16_MAX_ABS, err.max().item()
+        rel = err.sum().item() / max(want.abs().sum().item(), 1e-30)
+        assert rel <= BF16_MEAN_REL, rel
+
+
+def _randn(shape, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g).to(dtype)
+
+
+# ----------------------------------------------------------------------------- store_kvcache
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("T,Hkv,D,bs", [(1, 1, 32, 16), (37, 4, 32, 16), (300, 8, 128, 16),
+                                        (64, 4, 64, 256), (5, 3, 20, 4)])
+def test_store_kvcache_bit_exact(dtype, T, Hkv, D, bs):
+    ops, orc = _ops(), _oracle()
+    nb = (T + bs - 1) // bs + 3
+    k, v = _randn((T, Hkv, D), 1, dtype), _randn((T, Hkv, D), 2, dtype)
+    rng = np.random.default_rng(2)
+    slots = torch.from_numpy(rng.permutation(nb * bs)[:T].astype(np.int64))
+    if T > 3:
+        slots[1] = -1  # graph-replay padding
+    kc0, vc0 = _randn((nb, bs, Hkv, D), 3, dtype), _randn((nb, bs, Hkv, D), 4, dtype)
+    kc_ref, vc_ref = kc0.clone(), vc0.clone()
+    orc.store_kvcache(k, v, kc_ref, vc_ref, slots)
+    kc, vc = kc0.cuda(), vc0.cuda()
+    ops.store_kvcache(k.cuda(), v.cuda(), kc, vc, slots.cuda())
+    ops.check_status()
+    assert torch.equal(kc.cpu(), kc_ref) and torch.equal(vc.cpu(), vc_ref)
+
+
+def test_store_kvcache_strided_views_of_fused_qkv():
+    ops, orc = _ops(), _oracle()
+    T, Hq, Hkv, D, bs, nb = 50, 8, 2, 64, 16, 8
+    qkv = _randn((T, (Hq + 2 * Hkv) * D), 5, torch.bfloat16)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    slots = torch.from_numpy(np.random.default_rng(0).permutation(nb * bs)[:T].astype(np.int64))
+    kc_ref, vc_ref = torch.zeros(nb, bs, Hkv, D, dtype=torch.bfloat16), torch.zeros(nb, bs, Hkv, D, dtype=torch.bfloat16)
+    orc.store_kvcache(k, v, kc_ref, vc_ref, slots)
+    qkv_d = qkv.cuda()
+    kd = qkv_d[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    vd = qkv_d[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    kc, vc = torch.zeros_like(kc_ref).cuda(), torch.zeros_like(vc_ref).cuda()
+    ops.store_kvcache(kd, vd, kc, vc, slots.cuda())
+    assert torch.equal(kc.cpu(), kc_ref) and torch.equal(vc.cpu(), vc_ref)
+
+
+def test_store_kvcache_out_of_pool_slot_is_skipped_and_reported():
+    ops = _ops()
+    from llm_from_scratch_b200._lib import B200Error
+    k = _randn((4, 2, 32), 1, torch.bfloat16).cuda()
+    kc = torch.zeros(2, 16, 2, 32, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    slots = torch.tensor([0, 1, 2, 10 ** 9], dtype=torch.int64, device="cuda")
+    ops.store_kvcache(k, k, kc, vc, slots)
+    with pytest.raises(B200Error):
+        ops.check_status()
+    ops.check_status()  # cleared by the read
+    assert torch.equal(kc.view(-1, 2, 32)[:3], k[:3])
+
+
+def test_store_kvcache_round_trip_full_size():
+    """Size-independent property at the ragged-prefill stress size: scatter through a shuffled
+    slot mapping, gather back through the same mapping, bit-identical."""
+    ops = _ops()
+    T, Hkv, D, bs = 262144, 8, 128, 16
+    g = torch.Generator(device="cuda").manual_seed(2)
+    k = torch.randn(T, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    slots = torch.randperm(T, generator=g, device="cuda")
+    kc = torch.zeros(T // bs, bs, Hkv, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    ops.store_kvcache(k, v, kc, vc, slots)
+    ops.check_status()
+    assert torch.equal(kc.view(T, Hkv, D)[slots], k)
+    assert torch.equal(vc.view(T, Hkv, D)[slots], v)
+
+
+# ----------------------------------------------------------------------------- paged decode
+def _decode_case(lens, Hq, Hkv, D, bs, dtype, seed=0, pad_value=-1):
+    rng = np.random.default_rng(seed)
+    case = deal_blocks(lens, bs, rng, pad_blocks=2, pad_value=pad_value)
+    B = len(lens)
+    q = _randn((B, Hq, D), seed + 10, dtype)
+    kc = _randn((case.num_blocks, bs, Hkv, D), seed + 11, dtype)
+    vc = _randn((case.num_blocks, bs, Hkv, D), seed + 12, dtype)
+    return case, q, kc, vc
+
+
+def _run_decode(case, q, kc, vc, scale):
+    ops = _ops()
+    bt = torch.from_numpy(case.block_tables).cuda()
+    cl = torch.from_numpy(case.context_lens).cuda()
+    out = ops.paged_decode_gqa(q.cuda(), kc.cuda(), vc.cuda(), bt, cl, scale)
+    ops.check_status()
+    return out
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (16, 4, 64), (16, 4, 32), (8, 8, 128),
+                                      (16, 2, 64), (16, 1, 128), (32, 2, 128), (12, 4, 64)])
+def test_paged_decode_bf16_matches_oracle(Hq, Hkv, D):
+    lens = [1, 15, 16, 17, 31, 32, 33, 100, 0, 257, 1000, 64, 5, 2049]
+    case, q, kc, vc = _decode_case(lens, Hq, Hkv, D, 16, torch.bfloat16, seed=Hq + D)
+    scale = D ** -0.5
+    want = _oracle().paged_decode_gqa(q, kc, vc, case.block_tables, case.context_lens, scale)
+    got = _run_decode(case, q, kc, vc, scale)
+    assert_close(got, want, torch.bfloat16)
+    assert (got[8] == 0).all()  # empty context -> zero row
+
+
+def test_paged_decode_bf16_long_sequence_split_across_ctas():
+    lens = [6000, 3, 16 * 148 + 7, 129]
+    case, q, kc, vc = _decode_case(lens, 32, 8, 128, 16, torch.bfloat16, seed=7)
+    scale = 128 ** -0.5
+    want = _oracle().paged_decode_gqa(q, kc, vc, case.block_tables, case.context_lens, scale)
+    got = _run_decode(case, q, kc, vc, scale)
+    assert_close(got, want, torch.bfloat16)
+
+
+def test_paged_decode_bf16_single_short_sequence_and_stale_table_entries():
+    # entries past ceil(len/16) hold stale ids outside the pool: they must never be read
+    case, q, kc, vc = _decode_case([20], 32, 8, 128, 16, torch.bfloat16, seed=3)
+    bt = np.full((1, 40), 2 ** 30, dtype=np.int32)
+    bt[0, :2] = case.block_tables[0, :2]
+    case.block_tables = bt
+    scale = 128 ** -0.5
+    want = _oracle().paged_decode_gqa(q, kc, vc, case.block_tables, case.context_lens, scale)
+    got = _run_decode(case, q, kc, vc, scale)
+    assert_close(got, want, torch.bfloat16)
+
+
+def test_paged_decode_rejects_block_id_outside_pool_without_reading_it():
+    from llm_from_scratch_b200._lib import B200Error
+    ops = _ops()
+    case, q, kc, vc = _decode_case([40, 40], 32, 8, 128, 16, torch.bfloat16, seed=4)
+    case.block_tables[1, 1] = case.num_blocks + 5
+    bt = torch.from_numpy(case.block_tables).cuda()
+    cl = torch.from_numpy(case.context_lens).cuda()
+    ops.paged_decode_gqa(q.cuda(), kc.cuda(), vc.cuda(), bt, cl, 128 ** -0.5)
+    with pytest.raises(B200Error):
+        ops.check_status()
+
+
+def test_paged_decode_is_deterministic_and_repeatable():
+    case, q, kc, vc = _decode_case([700, 33, 1500, 90, 4000], 32, 8, 128, 16, torch.bfloat16, seed=5)
+    a = _run_decode(case, q, kc, vc, 128 ** -0.5)
+    b = _run_decode(case, q, kc, vc, 128 ** -0.5)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,bs", [(16, 4, 32, 16), (8, 2, 48, 8), (4, 4, 128, 256)])
+def test_paged_decode_fp32_matches_oracle(Hq, Hkv, D, bs):
+    lens = [1, bs, bs + 1, 0, 77, 300]
+    case, q, kc, vc = _decode_case(lens, Hq, Hkv, D, bs, torch.float32, seed=D)
+    scale = D ** -0.5
+    want = _oracle().paged_decode_gqa(q, kc, vc, case.block_tables, case.context_lens, scale)
+    got = _run_decode(case, q, kc, vc, scale)
+    assert_close(got, want, torch.float32)
+
+
+def test_paged_decode_bf16_generic_path_for_other_block_sizes():
+    case, q, kc, vc = _decode_case([5, 300, 64], 8, 2, 64, 32, torch.bfloat16, seed=9)
+    want = _oracle().paged_decode_gqa(q, kc, vc, case.block_tables, case.context_lens, 0.125)
+    got = _run_decode(case, q, kc, vc, 0.125)
+    assert_close(got, want, torch.bfloat16)
+
+
+def test_paged_decode_microbenchmark_shape_sampled_rows():
+    """Benchmark-size batch (256 sequences, log-uniform contexts up to 8192); the oracle checks a
+    sample of rows, and decoding each sampled row alone must give the same bits as in the batch
+    only up to split placement, so the comparison is by tolerance."""
+    from llm_from_scratch_b200.workloads import c2_decode_case
+    ops = _ops()
+    case = c2_decode_case()
+    Hq, Hkv, D = 32, 8, 128
+    g = torch.Generator(device="cuda").manual_seed(1)
+    kc = torch.randn(case.num_blocks, 16, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(case.num_blocks, 16, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn(case.batch, Hq, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    bt = torch.from_numpy(case.block_tables).cuda()
+    cl = torch.from_numpy(case.context_lens).cuda()
+    out = ops.paged_decode_gqa(q, kc, vc, bt, cl, D ** -0.5)
+    ops.check_status()
+    assert torch.isfinite(out.float()).all()
+    rows = [0, 1, 17, 100, 255, int(np.argmax(case.context_lens)), int(np.argmin(case.context_lens))]
+    for b in rows:
+        L = int(case.context_lens[b])
+        nblk = (L + 15) // 16
+        ids = torch.from_numpy(case.block_tables[b, :nblk].astype(np.int64)).cuda()
+        kcb, vcb = kc[ids].cpu(), vc[ids].cpu()
+        want = _oracle().paged_decode_gqa(q[b:b + 1].cpu(), kcb, vcb, [list(range(nblk))], [L], D ** -0.5)
+        assert_close(out[b:b + 1], want, torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- varlen prefill
+def _prefill_inputs(lens, Hq, Hkv, Dqk, Dv, dtype, seed):
+    T = sum(lens)
+    q = _randn((T, Hq, Dqk), seed, dtype)
+    k = _randn((T, Hkv, Dqk), seed + 1, dtype)
+    v = _randn((T, Hkv, Dv), seed + 2, dtype)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    return q, k, v, cu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D", [(16, 4, 32), (32, 8, 128), (4, 4, 64), (16, 4, 64)])
+def test_prefill_varlen_matches_oracle(dtype, Hq, Hkv, D):
+    ops = _ops()
+    lens = [1, 16, 17, 45, 128, 3, 200]
+    q, k, v, cu = _prefill_inputs(lens, Hq, Hkv, D, D, dtype, seed=D + Hq)
+    scale = D ** -0.5
+    want = _oracle().prefill_varlen(q, k, v, cu, cu, scale)
+    got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), scale)
+    ops.check_status()
+    assert_close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prefill_varlen_with_cached_prefix_through_block_tables(dtype):
+    ops, orc = _ops(), _oracle()
+    Hq, Hkv, D, bs = 16, 4, 64, 16
+    k_lens = [48, 100, 16, 37]
+    cached = [32, 64, 0, 16]
+    q_lens = [a - b for a, b in zip(k_lens, cached)]
+    rng = np.random.default_rng(3)
+    case = deal_blocks(k_lens, bs, rng, pad_blocks=1)
+    kc = _randn((case.num_blocks, bs, Hkv, D), 21, dtype)
+    vc = _randn((case.num_blocks, bs, Hkv, D), 22, dtype)
+    q = _randn((sum(q_lens), Hq, D), 23, dtype)
+    cu_q = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    cu_k = torch.tensor(np.concatenate([[0], np.cumsum(k_lens)]), dtype=torch.int32)
+    scale = D ** -0.5
+    want = orc.prefill_varlen(q, None, None, cu_q, cu_k, scale, kc, vc, case.block_tables)
+    got = ops.prefill_varlen(q.cuda(), None, None, cu_q.cuda(), cu_k.cuda(), max(q_lens), max(k_lens), scale,
+                             kc.cuda(), vc.cuda(), torch.from_numpy(case.block_tables).cuda())
+    ops.check_status()
+    assert_close(got, want, dtype)
+
+
+def test_prefill_varlen_mla_head_dims_192_128():
+    ops = _ops()
+    lens = [33, 70, 5]
+    q, k, v, cu = _prefill_inputs(lens, 16, 16, 192, 128, torch.bfloat16, seed=40)
+    scale = 192 ** -0.5
+    want = _oracle().prefill_varlen(q, k, v, cu, cu, scale)
+    got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), scale)
+    assert_close(got, want, torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- MLA decode
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("H,r,dr", [(16, 512, 64), (8, 128, 32), (16, 256, 16)])
+def test_mla_decode_matches_oracle(dtype, H, r, dr):
+    ops = _ops()
+    lens = [1, 16, 17, 0, 100, 513, 40]
+    bs = 16
+    case = deal_blocks(lens, bs, np.random.default_rng(4), pad_blocks=2)
+    B = len(lens)
+    qa = (_randn((B, H, r), 50, torch.float32) * 0.3).to(dtype)
+    qr = _randn((B, H, dr), 51, dtype)
+    lat = _randn((case.num_blocks, bs, r + dr), 52, dtype)
+    scale = (128 + dr) ** -0.5
+    want = _oracle().mla_decode(qa, qr, lat, case.block_tables, case.context_lens, scale)
+    got = ops.mla_decode(qa.cuda(), qr.cuda(), lat.cuda(), torch.from_numpy(case.block_tables).cuda(),
+                         torch.from_numpy(case.context_lens).cuda(), scale)
+    ops.check_status()
+    assert_close(got, want, dtype)
