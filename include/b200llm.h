@@ -48,6 +48,7 @@ extern "C" {
 #define B200_ERR_WORKSPACE (-5)    /* workspace smaller than *_workspace_bytes asks for      */
 #define B200_ERR_BOUNDS (-6)       /* device-side: block id or slot outside the pool         */
 #define B200_ERR_NO_DEVICE (-7)    /* no usable CUDA device                                  */
+#define B200_ERR_TOO_LARGE (-8)    /* scratch needed exceeds a fixed built-in capacity       */
 
 int b200_abi_version(void);
 const char* b200_strerror(int code);
@@ -105,6 +106,29 @@ int b200_paged_decode_gqa(const void* q, const void* k_cache, const void* v_cach
                           int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
                           int64_t num_blocks, float scale, void* workspace, size_t workspace_bytes,
                           int32_t dtype, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Paged GQA decode for callers that cannot allocate device memory (no counterpart in the
+ * reference, whose engine allocates freely through torch).  Same arguments and results as
+ * b200_paged_decode_gqa minus the workspace: the split-context scratch is a fixed
+ * B200_STATIC_SCRATCH_BYTES (8 MiB) device array inside the library, held by every GPU that loads
+ * the library until the process exits.  It is meant for hosts that gave all
+ * device memory to the KV pool, or that may not call an allocator on the decode path.
+ *   - calls no cudaMalloc/cudaFree or any allocating routine;
+ *   - returns B200_ERR_TOO_LARGE when b200_paged_decode_gqa_workspace_bytes(...) for the shape
+ *     exceeds the capacity (nothing is launched);
+ *   - the first call on each device looks up the array's device address (a host-side symbol query,
+ *     made with that device current); make that first call before starting any stream capture;
+ *   - all calls share the array: calls that overlap on the GPU (two streams, two threads) race on
+ *     it.  Nothing in it has to be cleared between calls.
+ * ------------------------------------------------------------------------------------------- */
+#define B200_STATIC_SCRATCH_BYTES ((size_t)8 << 20)
+int b200_paged_decode_gqa_static(const void* q, const void* k_cache, const void* v_cache,
+                                 void* out, const int32_t* block_tables, int64_t bt_stride,
+                                 const int64_t* context_lens, int32_t batch, int32_t num_q_heads,
+                                 int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
+                                 int64_t num_blocks, float scale, int32_t dtype, int32_t* status,
+                                 void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Ragged (varlen) causal prefill attention over sequences packed with cu_seqlens.

@@ -135,6 +135,7 @@ const char* b200_strerror(int code) {
     case B200_ERR_WORKSPACE: return "workspace too small";
     case B200_ERR_BOUNDS: return "block id or slot outside the pool (access skipped)";
     case B200_ERR_NO_DEVICE: return "no usable CUDA device";
+    case B200_ERR_TOO_LARGE: return "problem needs more scratch than the built-in static array holds";
     default: return "unknown error";
   }
 }

@@ -634,3 +634,69 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
     paged_decode_simple_kernel<__nv_bfloat16><<<grid, kSimpleWarps * 32, 0, s>>>(a);
   return launch_result();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Paged GQA decode for callers that cannot allocate device memory.
+//
+// Some hosts of this library hold no allocator they may call on the decode path: an engine that
+// has handed the whole GPU to its KV pool and keeps nothing back for scratch, a plugin loaded into
+// a server whose memory is budgeted by someone else, or a step replayed from a pre-recorded
+// command list where a cudaMalloc would serialise the device.  For them the split-context scratch
+// lives in a fixed device array that is part of the library image: every GPU that loads the
+// library holds kStaticScratchBytes of it until the process exits, and problems whose scratch
+// would not fit are refused instead of allocated for.
+//
+// The array's name is only a device address inside device code.  On the host it is a stand-in
+// symbol, so the device address is looked up once per device with cudaGetSymbolAddress (with that
+// device current) and cached; that first call per device does the lookup and should therefore be
+// made before any stream capture starts.  All calls share the one array and it keeps whatever the
+// previous call left in it: nothing in it needs to start at zero, because every slot that a call
+// reads was written earlier in that same call, but two calls that overlap on the GPU (different
+// streams, or different host threads) would overwrite each other's partial results.
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+namespace {
+
+constexpr size_t kStaticScratchBytes = B200_STATIC_SCRATCH_BYTES;  // 8 MiB per GPU
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+int static_scratch_address(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_ERR_NO_DEVICE;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_decode_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return B200_ERR_LAUNCH;
+    }
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_paged_decode_gqa_static(const void* q, const void* k_cache,
+                                            const void* v_cache, void* out,
+                                            const int32_t* block_tables, int64_t bt_stride,
+                                            const int64_t* context_lens, int32_t batch,
+                                            int32_t num_q_heads, int32_t num_kv_heads,
+                                            int32_t head_dim, int32_t block_size,
+                                            int64_t num_blocks, float scale, int32_t dtype,
+                                            int32_t* status, void* stream) {
+  using namespace b200;
+  if (batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0) {
+    const size_t need = b200_paged_decode_gqa_workspace_bytes(batch, num_q_heads, num_kv_heads,
+                                                              head_dim, dtype);
+    if (need > kStaticScratchBytes) return B200_ERR_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != B200_OK) return rc;
+  return b200_paged_decode_gqa(q, k_cache, v_cache, out, block_tables, bt_stride, context_lens,
+                               batch, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
+                               scale, scratch, kStaticScratchBytes, dtype, status, stream);
+}
