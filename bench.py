@@ -133,12 +133,16 @@ def time_cpu_oracle(sample, repeats=1):
 
 
 def main():
+    global BATCH, CPU_SAMPLE_SEQS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg (profiling runs)")
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="sequences per GPU; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -149,8 +153,10 @@ def main():
     n_gpus = max(args.gpus, world)
 
     from llm_from_scratch_b200.workloads import c2_decode_case, decode_algorithmic_bytes
+    BATCH = args.batch
+    CPU_SAMPLE_SEQS = min(CPU_SAMPLE_SEQS, BATCH)
     case = c2_decode_case(BATCH, 128, 8192, BS, seed=1)
-    config = {"workload": "paged GQA decode attention microbenchmark: 256 seqs/GPU, ctx log-uniform "
+    config = {"workload": f"paged GQA decode attention microbenchmark: {BATCH} seqs/GPU, ctx log-uniform "
                           "[128,8192], 32 q heads / 8 kv heads, head_dim 128, block 16, bf16",
               "batch_per_gpu": BATCH, "context_tokens_per_gpu": case.total_tokens,
               "l2": "inputs (>2 GB of K/V per GPU) exceed the 126 MB L2; no flush needed",
@@ -270,18 +276,20 @@ def main():
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
-    for _ in range(args.warmup):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = reduce_max(max(e0.elapsed_time(e1), 0.0))
-    e2e_wall_ms = reduce_max((time.perf_counter() - t0) * 1e3)
-    e2e_ms = max(e2e_ms, e2e_wall_ms)  # host-side stalls between steps count
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        for _ in range(args.warmup):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = reduce_max(max(e0.elapsed_time(e1), 0.0))
+        e2e_wall_ms = reduce_max((time.perf_counter() - t0) * 1e3)
+        e2e_ms = max(e2e_ms, e2e_wall_ms)  # host-side stalls between steps count
     sampler.stop()
     sampler.join(timeout=2)
     ops.check_status(dev)
@@ -307,9 +315,9 @@ def main():
                      "frac_of_nominal_8TBs": achieved / 8000.0,
                      "algorithmic_bytes_per_launch": alg_bytes, "traffic": None,
                      "kernel": "paged_decode_bf16_kernel<128,1> (+ combine, timed together)"},
-        "e2e": {"value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+        "e2e": None if args.no_e2e else {
+            "value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": 2 * args.steps,
         "clocks": sampler.summary(),
     }
