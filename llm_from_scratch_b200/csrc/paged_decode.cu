@@ -382,32 +382,87 @@ paged_decode_bf16_kernel(const DecodeArgs a) {
 }
 
 // Merges the partial results of sequences that were cut across CTAs; zero-fills rows whose
-// context is empty.  One CTA per sequence.
-__global__ void __launch_bounds__(256) paged_decode_combine_kernel(const DecodeArgs a) {
+// context is empty.  One CTA per sequence.  Most sequences are not cut and leave at once; for the
+// others the per-head weights 2^(m_p - M) / L are computed once into shared memory, then every
+// thread sums its float4 columns over the parts with all loads of a trip independent.
+constexpr int kCombineThreads = 256;
+constexpr int kCombineMaxParts = 8;  // parts whose weights are kept in shared memory per trip
+
+__global__ void __launch_bounds__(kCombineThreads)
+paged_decode_combine_kernel(const DecodeArgs a) {
+  extern __shared__ float s_w[];  // [kCombineMaxParts][Hq]
   const int i = blockIdx.x;
   const int n = a.Hq * a.D;
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + static_cast<int64_t>(i) * n;
-  if (a.lens[i] <= 0) {
-    for (int e = threadIdx.x; e < n; e += blockDim.x) op[e] = __float2bfloat16_rn(0.f);
+  const int64_t len = a.lens[i];
+  const int first = a.seq_info[2 * i], last = a.seq_info[2 * i + 1];
+  if (len <= 0) {
+    for (int e = threadIdx.x; e < n; e += kCombineThreads) op[e] = __float2bfloat16_rn(0.f);
     return;
   }
-  const int first = a.seq_info[2 * i], last = a.seq_info[2 * i + 1];
   if (first < 0) return;
-  for (int e = threadIdx.x; e < n; e += blockDim.x) {
-    const int head = e / a.D;
+  const int np = last - first + 1;
+  auto slot_of = [&](int p) -> int64_t {
+    return static_cast<int64_t>(first + p) * 2 + (p == 0 ? 1 : 0);
+  };
+  // per-head maximum and normaliser over all parts (np is small: a sequence of L tokens spans
+  // about L / (tokens per CTA) + 1 CTAs)
+  float* s_M = s_w + kCombineMaxParts * a.Hq;  // [Hq]
+  float* s_inv = s_M + a.Hq;                   // [Hq]
+  for (int h = threadIdx.x; h < a.Hq; h += kCombineThreads) {
     float M = -INFINITY;
-    for (int p = first; p <= last; ++p) {
-      const int64_t ps = static_cast<int64_t>(p) * 2 + (p == first ? 1 : 0);
-      M = fmaxf(M, a.part_ml[(ps * a.Hq + head) * 2]);
+    for (int p = 0; p < np; ++p) M = fmaxf(M, a.part_ml[(slot_of(p) * a.Hq + h) * 2]);
+    float L = 0.f;
+    for (int p = 0; p < np; ++p) {
+      const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + (slot_of(p) * a.Hq + h) * 2);
+      L += exp2f(ml.x - M) * ml.y;
     }
-    float acc = 0.f, Lsum = 0.f;
-    for (int p = first; p <= last; ++p) {
-      const int64_t ps = static_cast<int64_t>(p) * 2 + (p == first ? 1 : 0);
-      const float w = exp2f(a.part_ml[(ps * a.Hq + head) * 2] - M);
-      Lsum += w * a.part_ml[(ps * a.Hq + head) * 2 + 1];
-      acc += w * a.part_o[ps * n + e];
+    s_M[h] = M;
+    s_inv[h] = 1.f / L;
+  }
+  __syncthreads();
+  constexpr int kVec = 4;
+  const int nvec = n / kVec;  // D is a multiple of 16 on this path
+  float4 acc[4];
+  // every thread owns up to 4 float4 columns (n <= 16 * 256 * 4 covers Hq*D <= 16384)
+  for (int base = 0; base < nvec; base += kCombineThreads * 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p0 = 0; p0 < np; p0 += kCombineMaxParts) {
+      const int pc = min(kCombineMaxParts, np - p0);
+      __syncthreads();
+      for (int t = threadIdx.x; t < pc * a.Hq; t += kCombineThreads) {
+        const int p = p0 + t / a.Hq, h = t % a.Hq;
+        s_w[t] = exp2f(a.part_ml[(slot_of(p) * a.Hq + h) * 2] - s_M[h]) * s_inv[h];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vi = base + u * kCombineThreads + threadIdx.x;
+        if (vi < nvec) {
+          const int head = (vi * kVec) / a.D;
+          for (int p = 0; p < pc; ++p) {
+            const float4 x =
+                *reinterpret_cast<const float4*>(a.part_o + slot_of(p0 + p) * n + vi * kVec);
+            const float w = s_w[p * a.Hq + head];
+            acc[u].x += w * x.x;
+            acc[u].y += w * x.y;
+            acc[u].z += w * x.z;
+            acc[u].w += w * x.w;
+          }
+        }
+      }
     }
-    op[e] = __float2bfloat16_rn(acc / Lsum);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int vi = base + u * kCombineThreads + threadIdx.x;
+      if (vi < nvec) {
+        uint2 packed;
+        packed.x = pack_bf16x2(acc[u].x, acc[u].y);
+        packed.y = pack_bf16x2(acc[u].z, acc[u].w);
+        *reinterpret_cast<uint2*>(op + vi * kVec) = packed;
+      }
+    }
   }
 }
 
@@ -622,7 +677,8 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
     else
       rc = pl.nt == 1 ? launch_fast<32, 1>(a, pl, gi, s) : launch_fast<32, 2>(a, pl, gi, s);
     if (rc != B200_OK) return rc;
-    paged_decode_combine_kernel<<<batch, 256, 0, s>>>(a);
+    paged_decode_combine_kernel<<<batch, kCombineThreads,
+                                  (kCombineMaxParts + 2) * num_q_heads * sizeof(float), s>>>(a);
     return launch_result();
   }
 
