@@ -1,0 +1,167 @@
+"""Paged KV-block pool with chained-hash prefix caching (reference: engine/block_manager.py:8-157).
+
+Public surface is the reference's: ``BlockManager(num_blocks, block_size)``, ``compute_hash``,
+``can_allocate`` / ``allocate`` / ``deallocate``, ``can_append`` / ``append`` and the attributes
+``blocks``, ``hash_to_block_id``, ``free_block_ids``, ``used_block_ids``.
+
+Differences in mechanism, not in results:
+
+* block hashes come from the library's native XXH64 (``b200_block_hash``) instead of the xxhash
+  package + a numpy round trip per block;
+* the free list is an insertion-ordered dict used as an ordered set, so "take the oldest free
+  block", "take this particular free block" and "return a block" are all O(1); the reference's
+  ``deque.remove`` is O(num_blocks) per allocation (engine/block_manager.py:67).
+
+Two behaviours are selectable with ``reference_exact``:
+
+``reference_exact=True`` reproduces the reference's integer results bit for bit, including its
+ref-count arithmetic: a block's count starts at 0 (block_manager.py:23-26), so an unshared block
+falls to -1 when released and never returns to the free list, and a block shared by two sequences
+returns to the free list when the first of them finishes.  The parity tests run in this mode on
+workloads whose pool never runs dry (outside that the reference raises or drops requests).
+
+The default keeps the same allocation order and hashing but counts references from 1, so blocks
+are released exactly when their last user finishes, released blocks keep their contents and can be
+revived by a later prefix hit, and ``can_append`` asks for a free block on the same step on which
+``append`` takes one.
+"""
+from __future__ import annotations
+
+from .sequence import Sequence
+from .. import ops
+
+
+class Block:
+    __slots__ = ("block_id", "hash", "ref_count", "token_ids")
+
+    def __init__(self, block_id: int):
+        self.block_id = block_id
+        self.hash = -1
+        self.ref_count = 0
+        self.token_ids: list[int] = []
+
+    def update(self, h: int, token_ids) -> None:
+        self.hash = h
+        self.token_ids = token_ids
+
+    def reset(self) -> None:
+        self.hash = -1
+        self.ref_count = 0
+        self.token_ids = []
+
+
+class BlockManager:
+    def __init__(self, num_blocks: int, block_size: int, reference_exact: bool = False):
+        self.block_size = block_size
+        self.reference_exact = reference_exact
+        self.blocks = [Block(i) for i in range(num_blocks)]
+        self.hash_to_block_id: dict[int, int] = {}
+        self._free: dict[int, None] = dict.fromkeys(range(num_blocks))  # ordered set, oldest first
+        self.used_block_ids: set[int] = set()
+
+    # ------------------------------------------------------------------ views
+    @property
+    def free_block_ids(self):
+        """Free block ids, oldest first (supports len(), iteration and ``in``)."""
+        return self._free.keys()
+
+    @property
+    def num_free_blocks(self) -> int:
+        return len(self._free)
+
+    # ------------------------------------------------------------------ hashing
+    @staticmethod
+    def compute_hash(token_ids, prefix_hash_value: int = -1) -> int:
+        """XXH64 over [8-byte LE prefix hash unless -1] || int32-LE token ids (block_manager.py:45-57)."""
+        return ops.block_hash(token_ids, prefix_hash_value)
+
+    # ------------------------------------------------------------------ block moves
+    def _oldest_free(self) -> int:
+        try:
+            return next(iter(self._free))
+        except StopIteration:
+            raise IndexError("KV block pool exhausted") from None
+
+    def _allocate_block(self, block_id: int, keep_contents: bool = False) -> Block:
+        block = self.blocks[block_id]
+        if self.reference_exact:
+            assert block.ref_count == 0, "block is already allocated"
+            block.reset()
+        else:
+            if not keep_contents:
+                if block.hash != -1 and self.hash_to_block_id.get(block.hash) == block_id:
+                    del self.hash_to_block_id[block.hash]
+                block.reset()
+            block.ref_count = 1
+        del self._free[block_id]
+        self.used_block_ids.add(block_id)
+        return block
+
+    def _deallocate_block(self, block_id: int) -> None:
+        block = self.blocks[block_id]
+        assert block.ref_count == 0, "block is still in use"
+        if self.reference_exact:
+            block.token_ids = []
+        self.used_block_ids.remove(block_id)
+        self._free[block_id] = None
+
+    # ------------------------------------------------------------------ prefill-time allocation
+    def can_allocate(self, seq: Sequence) -> bool:
+        return len(self._free) >= seq.num_blocks
+
+    def allocate(self, seq: Sequence) -> None:
+        """Give ``seq`` a block per ``block_size`` tokens, reusing blocks whose chained hash and
+        token ids match (block_manager.py:85-114)."""
+        h = -1
+        bs = self.block_size
+        for i in range(seq.num_blocks):
+            token_ids = seq.block(i)
+            h = self.compute_hash(token_ids, h) if len(token_ids) == bs else -1
+            block_id = self.hash_to_block_id.get(h, -1)
+            hit = block_id != -1 and self.blocks[block_id].token_ids == token_ids
+            if hit:
+                seq.num_cached_tokens += bs
+                if block_id in self.used_block_ids:
+                    block = self.blocks[block_id]
+                    block.ref_count += 1
+                else:
+                    block = self._allocate_block(block_id, keep_contents=True)
+            else:
+                block = self._allocate_block(self._oldest_free())
+                block.update(h, token_ids)
+                if h != -1:
+                    self.hash_to_block_id[h] = block.block_id
+            seq.block_table.append(block.block_id)
+
+    def deallocate(self, seq: Sequence) -> None:
+        order = seq.block_table if self.reference_exact else reversed(seq.block_table)
+        for block_id in order:
+            block = self.blocks[block_id]
+            block.ref_count -= 1
+            if block.ref_count == 0:
+                self._deallocate_block(block_id)
+        seq.block_table = []
+        seq.num_cached_tokens = 0
+
+    # ------------------------------------------------------------------ decode-time growth
+    def can_append(self, seq: Sequence) -> bool:
+        trigger = 0 if self.reference_exact else 1   # block_manager.py:132 tests == 0
+        return len(self._free) > 0 if len(seq) % self.block_size == trigger else True
+
+    def append(self, seq: Sequence) -> None:
+        """Called once per decode step before the step runs (block_manager.py:136-157): opens a new
+        block when the previous one has just filled, seals the hash of a block that is now full."""
+        table = seq.block_table
+        last = self.blocks[table[-1]]
+        rem = len(seq) % self.block_size
+        if rem == 0:
+            prefix = -1 if len(table) == 1 else self.blocks[table[-2]].hash
+            token_ids = seq.block(seq.num_blocks - 1)
+            h = self.compute_hash(token_ids, prefix)
+            last.update(h, token_ids)
+            self.hash_to_block_id[h] = last.block_id
+        elif rem == 1:
+            assert last.hash != -1, "previous block should have been sealed"
+            table.append(self._allocate_block(self._oldest_free()).block_id)
+        else:
+            assert last.block_id in self.used_block_ids and last.hash == -1

@@ -1,0 +1,108 @@
+"""Prefill-first continuous batching (reference: engine/scheduler.py:8-95).
+
+``schedule()`` returns ``(sequences, is_prefill)``; batches are never mixed: as soon as at least
+one waiting request was admitted the step is a prefill step, otherwise every running sequence gets
+one decode token.  ``postprocess()`` appends the sampled tokens and retires finished sequences.
+
+``reference_exact=True`` reproduces the reference decision for decision, including that a running
+sequence that cannot grow is dropped from the step after a victim was preempted
+(scheduler.py:52-57) and the ``1 + completions >= max_tokens`` stop rule (scheduler.py:89), which
+ends a request after ``max_tokens - 1`` generated tokens.  The default differs only when the pool
+runs dry: it preempts newest-first until the sequence at hand can grow, then keeps it.
+The stop rule is the reference's in both modes.
+"""
+from __future__ import annotations
+
+from collections import deque
+
+from .block_manager import BlockManager
+from .sequence import Sequence, SequenceStatus
+
+
+class Scheduler:
+    def __init__(self, max_num_sequences: int, max_num_batched_tokens: int, max_cached_blocks: int,
+                 block_size: int, eos: int, reference_exact: bool = False):
+        self.max_num_sequences = max_num_sequences
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.eos = eos
+        self.reference_exact = reference_exact
+        self.block_manager = BlockManager(max_cached_blocks, block_size, reference_exact)
+        self.waiting: deque[Sequence] = deque()
+        self.running: deque[Sequence] = deque()
+
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def add_sequence(self, sequence: Sequence) -> None:
+        self.waiting.append(sequence)
+
+    # ------------------------------------------------------------------ one step
+    def schedule(self) -> tuple[list[Sequence], bool]:
+        admitted = self._admit_waiting()
+        if admitted:
+            return admitted, True
+        return self._grow_running(), False
+
+    def _admit_waiting(self) -> list[Sequence]:
+        bm, batch, tokens = self.block_manager, [], 0
+        while self.waiting and len(batch) < self.max_num_sequences:
+            seq = self.waiting[0]
+            if tokens + len(seq) > self.max_num_batched_tokens or not bm.can_allocate(seq):
+                break
+            self.waiting.popleft()
+            bm.allocate(seq)
+            seq.status = SequenceStatus.RUNNING
+            self.running.append(seq)
+            batch.append(seq)
+            tokens += len(seq)
+        return batch
+
+    def _grow_running(self) -> list[Sequence]:
+        bm, batch = self.block_manager, []
+        while self.running:
+            seq = self.running.popleft()
+            if self.reference_exact:
+                if not bm.can_append(seq):
+                    if self.running:
+                        self.preempt(self.running.pop())
+                    else:
+                        self.preempt(seq)
+                        break
+                    continue
+            else:
+                evicted_self = False
+                while not bm.can_append(seq):
+                    if self.running:
+                        self.preempt(self.running.pop())
+                    else:
+                        self.preempt(seq)
+                        evicted_self = True
+                        break
+                if evicted_self:
+                    break
+            if len(batch) >= self.max_num_sequences or len(batch) >= self.max_num_batched_tokens:
+                if not self.reference_exact:
+                    self.running.appendleft(seq)
+                break
+            bm.append(seq)
+            batch.append(seq)
+        if batch:
+            self.running.extendleft(reversed(batch))
+        return batch
+
+    def preempt(self, seq: Sequence) -> None:
+        self.block_manager.deallocate(seq)
+        seq.status = SequenceStatus.WAITING
+        self.waiting.appendleft(seq)
+
+    # ------------------------------------------------------------------ after the model ran
+    def postprocess(self, seqs: list[Sequence], token_ids: list[int]) -> None:
+        for seq, token_id in zip(seqs, token_ids):
+            seq.append_token(token_id)
+            hit_eos = token_id == self.eos and not seq.ignore_eos
+            hit_max_tokens = 1 + seq.num_completion_tokens >= seq.max_tokens
+            hit_max_length = seq.max_model_length is not None and seq.num_tokens >= seq.max_model_length
+            if hit_eos or hit_max_tokens or hit_max_length:
+                seq.status = SequenceStatus.FINISHED
+                self.block_manager.deallocate(seq)
+                self.running.remove(seq)
