@@ -77,6 +77,8 @@ uint64_t b200_block_hash(const int32_t* token_ids_host, int32_t num_tokens, uint
  *   k, v            [num_tokens, Hkv, D]; rows Hkv*D contiguous, token stride given in ELEMENTS
  *                   (k/v may be column slices of a fused qkv projection)
  *   k_cache,v_cache [num_slots, Hkv, D] contiguous
+ *   v and v_cache may both be NULL for a single pool (the MLA latent cache: Hkv = 1,
+ *   D = kv_lora_rank + rope_dim)
  * ------------------------------------------------------------------------------------------- */
 int b200_store_kvcache(const void* k, const void* v, int64_t k_token_stride,
                        int64_t v_token_stride, void* k_cache, void* v_cache,

@@ -38,7 +38,7 @@ store_kvcache_vec16(const uint4* __restrict__ k, const uint4* __restrict__ v, in
           if (slot < num_slots) {
             dst[u] = slot * cpr + c;
             kr[u] = __ldcs(k + t * k_stride + c);
-            vr[u] = __ldcs(v + t * v_stride + c);
+            if (v != nullptr) vr[u] = __ldcs(v + t * v_stride + c);
           } else {
             report(status, B200_ERR_BOUNDS);
           }
@@ -49,7 +49,7 @@ store_kvcache_vec16(const uint4* __restrict__ k, const uint4* __restrict__ v, in
     for (int u = 0; u < kUnroll; ++u) {
       if (dst[u] >= 0) {
         kc[dst[u]] = kr[u];
-        vc[dst[u]] = vr[u];
+        if (v != nullptr) vc[dst[u]] = vr[u];
       }
     }
   }
@@ -74,7 +74,7 @@ store_kvcache_scalar(const T* __restrict__ k, const T* __restrict__ v, int64_t k
       continue;
     }
     kc[slot * row + c] = k[t * k_stride + c];
-    vc[slot * row + c] = v[t * v_stride + c];
+    if (v != nullptr) vc[slot * row + c] = v[t * v_stride + c];
   }
 }
 
@@ -90,7 +90,9 @@ extern "C" int b200_store_kvcache(const void* k, const void* v, int64_t k_token_
   if (num_tokens < 0 || num_kv_heads <= 0 || head_dim <= 0 || num_slots < 0) return B200_ERR_ARG;
   if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
   if (num_tokens == 0) return B200_OK;
-  if (!k || !v || !k_cache || !v_cache || !slot_mapping) return B200_ERR_ARG;
+  if (!k || !k_cache || !slot_mapping) return B200_ERR_ARG;
+  if ((v == nullptr) != (v_cache == nullptr)) return B200_ERR_ARG;  // both or neither
+  if (v == nullptr) v_token_stride = k_token_stride;
   const int esize = dtype == B200_DTYPE_F32 ? 4 : 2;
   const int64_t row = static_cast<int64_t>(num_kv_heads) * head_dim;
   if (k_token_stride < row || v_token_stride < row) return B200_ERR_ARG;
@@ -100,7 +102,7 @@ extern "C" int b200_store_kvcache(const void* k, const void* v, int64_t k_token_
   const int64_t row_bytes = row * esize;
   const bool vec = (row_bytes % 16 == 0) && (k_token_stride * esize % 16 == 0) &&
                    (v_token_stride * esize % 16 == 0) && aligned16(k) && aligned16(v) &&
-                   aligned16(k_cache) && aligned16(v_cache);
+                   aligned16(k_cache) && aligned16(v_cache);  // a null v is "aligned"
   if (vec) {
     const int cpr = static_cast<int>(row_bytes / 16);
     const int64_t total = static_cast<int64_t>(num_tokens) * cpr;

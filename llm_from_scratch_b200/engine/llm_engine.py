@@ -1,0 +1,88 @@
+"""Engine facade (reference: engine/llm_engine.py:24-102): ``add_prompt`` / ``step`` / ``generate``.
+
+One engine = one process = one GPU replica with its own scheduler, block pool and KV cache; the
+reference's tensor-parallel worker processes are not part of this design.  ``step`` always
+returns the 3-tuple ``(finished outputs, tokens processed, is_prefill)`` (the reference returns a
+2-tuple when nothing is schedulable, which its own ``generate`` cannot unpack).  Prompts may be
+strings (a tokenizer with ``encode`` / ``decode`` must then be supplied) or lists of token ids.
+"""
+from __future__ import annotations
+
+import time
+
+from .model_runner import ModelRunner, _cfg
+from .sampling_params import SamplingParams
+from .scheduler import Scheduler
+from .sequence import Sequence
+
+
+class LLMEngine:
+    def __init__(self, config: dict, model=None, tokenizer=None, verbose: bool = False):
+        self.config = config
+        block_size = _cfg(config, "block_size", default=256)
+        Sequence.block_size = block_size
+        self.model_runner = ModelRunner(config, model)
+        self.scheduler = Scheduler(
+            max_num_sequences=_cfg(config, "max_num_sequences", "max_num_seqs", default=16),
+            max_num_batched_tokens=_cfg(config, "max_num_batched_tokens", "max_num_batch_tokens", default=1024),
+            max_cached_blocks=self.model_runner.num_kv_blocks,
+            block_size=block_size,
+            eos=_cfg(config, "eos", default=50256),
+        )
+        self.tokenizer = tokenizer
+        self.verbose = verbose
+        self.stats = dict(prefill_tokens=0, decode_tokens=0, prefill_time=0.0, decode_time=0.0, steps=0)
+
+    def exit(self) -> None:
+        self.model_runner.exit()
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, token_ids, sampling_params: SamplingParams | None = None) -> Sequence:
+        seq = Sequence(token_ids, sampling_params or SamplingParams())
+        self.scheduler.add_sequence(seq)
+        return seq
+
+    def add_prompt(self, prompt, sampling_params: SamplingParams | None = None) -> Sequence:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("a string prompt needs a tokenizer; pass token ids or LLMEngine(tokenizer=...)")
+            prompt = self.tokenizer.encode(prompt)
+        return self.add_request(prompt, sampling_params)
+
+    # ------------------------------------------------------------------ one step
+    def step(self):
+        seqs, is_prefill = self.scheduler.schedule()
+        if not seqs:
+            return [], 0, is_prefill
+        token_ids = self.model_runner.run(seqs, is_prefill)
+        self.scheduler.postprocess(seqs, token_ids)
+        outputs = [(s.seq_id, s.completion_token_ids) for s in seqs if s.is_finished]
+        processed = sum(len(s) for s in seqs) if is_prefill else len(seqs)
+        return outputs, processed, is_prefill
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    # ------------------------------------------------------------------ whole job
+    def generate(self, prompts, sampling_params) -> dict:
+        if isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompts)
+        for prompt, sp in zip(prompts, sampling_params):
+            self.add_prompt(prompt, sp)
+        done: dict[int, list[int]] = {}
+        while not self.scheduler.is_finished():
+            t0 = time.perf_counter()
+            outputs, n, is_prefill = self.step()
+            dt = time.perf_counter() - t0
+            if n == 0 and not outputs:
+                raise RuntimeError("nothing schedulable: the KV pool is too small for the waiting request")
+            kind = "prefill" if is_prefill else "decode"
+            self.stats[kind + "_tokens"] += n
+            self.stats[kind + "_time"] += dt
+            self.stats["steps"] += 1
+            if self.verbose:
+                print(f"{n} tokens, {n / (dt + 1e-10):.0f} tokens/s during {kind}")
+            done.update(outputs)
+        token_ids = [done[k] for k in sorted(done)]
+        text = [self.tokenizer.decode(t) for t in token_ids] if self.tokenizer is not None else None
+        return {"text": text, "token_ids": token_ids}

@@ -1,0 +1,301 @@
+"""Engine-mode decoder over flat ragged token batches and paged caches.
+
+The reference's engine expects a model that takes flat 1-D ``input_ids`` and reads the global
+attention ``Context`` (engine/model_runner.py:288-293); it does not ship one.  This module supplies
+it, with the layer arithmetic of the reference's dense-batch model:
+
+* residual stream with fused add + RMSNorm          model/transformer.py:90-118, model/utils.py:54-67
+* GQA: biased q/k/v projections, RMSNorm over the whole projected q / k vector with
+  eps = finfo(dtype).eps, half-split RoPE, K cached after norm + RoPE, V raw   model/attention/GQA.py:79-130
+* MLA: absorbed form, one latent row [kv_norm(kv_down(x)) | rope(k_rope(x))] cached per token,
+  kv_up_proj_fused biases unused                     model/attention/MLA.py:114-178
+* SwiGLU MLP with biases, sigmoid-score top-k MoE with renormalised weights, experts applied in
+  ascending order, shared expert added last          mlp.py:61-67, moe.py:45-90,272-341
+
+Attention itself is not computed here: q/k/v go to the CUDA kernels behind ``ops`` (store_kvcache,
+varlen prefill, paged decode, MLA decode).  The projections are plain torch GEMMs.
+
+Precision: ``dtype=float32`` computes everything in fp32.  ``dtype=bfloat16`` reproduces the
+rounding points of the reference's mixed-precision mode (fp32 parameters under bf16 autocast):
+linear layers, attention and caches in bf16; RMSNorm arithmetic and RoPE in fp32; the embedding
+lookup stays fp32 so the first norm sees fp32, as under autocast.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import ops
+from ..utils.context import get_context
+from .config import ModelConfig
+
+
+def _rope_table(theta: float, d_k: int, max_len: int) -> torch.Tensor:
+    """[max_len, d_k] rows cat(cos, sin) (model/attention/utils.py:25-32); built on the CPU."""
+    inv = 1.0 / (theta ** (torch.arange(0, d_k, 2).float() / d_k))
+    ang = torch.einsum("i,j->ij", torch.arange(max_len).float(), inv)
+    return torch.cat([torch.cos(ang), torch.sin(ang)], dim=-1)
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """x [T, H, d_x] rotated at positions [T]; the table is sliced to d_x columns exactly as the
+    reference does (utils.py:38), including when d_x is smaller than the table width."""
+    d_x = x.shape[-1]
+    cs = table[positions, :d_x].unsqueeze(1)
+    cos, sin = torch.chunk(cs, 2, dim=-1)
+    x1, x2 = torch.chunk(x, 2, dim=-1)
+    y1 = torch.addcmul(x1 * cos, x2, sin, value=-1)
+    y2 = torch.addcmul(x2 * cos, x1, sin, value=1)
+    return torch.cat((y1, y2), dim=-1)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """fp32 RMSNorm returning the input dtype; with ``residual`` also returns the new residual."""
+    dt = x.dtype
+    xf = x.float()
+    if residual is not None:
+        xf = xf + residual.float()
+    y = (weight * xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dt)
+    return y if residual is None else (y, xf.to(dt))
+
+
+def _vector_norm(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """nn.RMSNorm(eps=None) over the last dim: eps = finfo(x.dtype).eps, result in x.dtype."""
+    eps = torch.finfo(x.dtype).eps
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight).to(x.dtype)
+
+
+class _Params:
+    """Moves reference-named weights to the device in the compute dtype."""
+
+    def __init__(self, weights: dict, device, dtype):
+        self.w, self.device, self.dtype = weights, device, dtype
+
+    def lin(self, *names):
+        """Concatenated [sum(out), in] weight and bias of one or more Linear layers."""
+        W = torch.cat([self.w[n + ".weight"] for n in names], dim=0).to(self.device, self.dtype).contiguous()
+        b = torch.cat([self.w[n + ".bias"] for n in names], dim=0).to(self.device, self.dtype).contiguous()
+        return W, b
+
+    def f32(self, name):
+        return self.w[name].to(self.device, torch.float32).contiguous()
+
+
+class MLP(nn.Module):
+    def __init__(self, p: _Params, prefix: str):
+        super().__init__()
+        self.w13, self.b13 = p.lin(prefix + ".w1", prefix + ".w3")
+        self.w2, self.b2 = p.lin(prefix + ".w2")
+        self.d_ff = self.w2.shape[1]
+
+    def forward(self, x):
+        h = F.linear(x, self.w13, self.b13)
+        return F.linear(F.silu(h[..., :self.d_ff]) * h[..., self.d_ff:], self.w2, self.b2)
+
+
+class MoE(nn.Module):
+    """Routing of Gate.forward (moe.py:45-90) and the expert loop of MOE.moe_infer (moe.py:288-341):
+    experts visited in ascending order, outputs accumulated in the activation dtype."""
+
+    def __init__(self, p: _Params, prefix: str, cfg: ModelConfig):
+        super().__init__()
+        self.E, self.K = cfg.n_routed_experts, cfg.num_experts_per_tok
+        self.gate_w = p.w[prefix + ".gate.weight"].to(p.device, p.dtype).contiguous()
+        self.gate_bias = p.f32(prefix + ".gate.expert_bias")
+        self.experts = nn.ModuleList([MLP(p, f"{prefix}.experts.{e}") for e in range(self.E)])
+        self.shared = MLP(p, prefix + ".shared_expert") if cfg.n_shared_experts > 0 else None
+
+    def route(self, x):
+        logits = x @ self.gate_w.t()
+        scores = torch.sigmoid(logits)
+        biased = logits + self.gate_bias.to(logits.dtype).unsqueeze(0)
+        _, idx = torch.topk(biased, k=self.K, dim=-1, sorted=False)
+        wts = torch.gather(scores, -1, idx)
+        if self.K > 1:
+            wts = wts / (wts.sum(-1, keepdim=True) + 1e-10)
+        return idx, wts
+
+    def forward(self, x):
+        idx, wts = self.route(x)
+        flat_idx = idx.reshape(-1)
+        flat_w = wts.reshape(-1, 1).to(x.dtype)
+        out = torch.zeros_like(x)
+        order = flat_idx.argsort()
+        counts = flat_idx.bincount(minlength=self.E).tolist()   # one host sync per layer, as moe.py:307
+        tok = order // self.K
+        lo = 0
+        for e in range(self.E):
+            hi = lo + counts[e]
+            if hi > lo:
+                t = tok[lo:hi]
+                y = self.experts[e](x[t]) * flat_w[order[lo:hi]]
+                out.index_add_(0, t, y)
+            lo = hi
+        if self.shared is not None:
+            out = out + self.shared(x)
+        return out
+
+
+class GQAAttention(nn.Module):
+    def __init__(self, p: _Params, prefix: str, cfg: ModelConfig, rope: torch.Tensor):
+        super().__init__()
+        self.H, self.Hkv, self.hd, self.d = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.d_model
+        self.w_qkv, self.b_qkv = p.lin(prefix + ".q_proj", prefix + ".k_proj", prefix + ".v_proj")
+        self.w_o, self.b_o = p.lin(prefix + ".output_proj")
+        self.q_norm, self.k_norm = p.f32(prefix + ".q_norm.weight"), p.f32(prefix + ".k_norm.weight")
+        self.rope = rope
+        self.scale = self.hd ** -0.5
+        self.dtype = p.dtype
+        # views into the pool; set by ModelRunner.allocate_kv_cache (model_runner.py:186-190)
+        self.k_cache = self.v_cache = torch.empty(0)
+
+    def forward(self, x, ctx, positions):
+        T = x.shape[0]
+        kvw = self.Hkv * self.hd
+        qkv = F.linear(x.to(self.dtype), self.w_qkv, self.b_qkv)
+        q = _vector_norm(qkv[:, :self.d], self.q_norm).view(T, self.H, self.hd)
+        k = _vector_norm(qkv[:, self.d:self.d + kvw], self.k_norm).view(T, self.Hkv, self.hd)
+        v = qkv[:, self.d + kvw:].view(T, self.Hkv, self.hd)
+        q = apply_rope(q, positions, self.rope).to(self.dtype)
+        k = apply_rope(k, positions, self.rope).to(self.dtype)
+        if self.k_cache.numel():
+            ops.store_kvcache(k, v, self.k_cache, self.v_cache, ctx.slot_mapping)
+        if ctx.is_prefill:
+            if ctx.block_tables is not None:   # part of the context is already cached
+                o = ops.prefill_varlen(q, None, None, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
+                                       ctx.max_seqlen_k, self.scale, self.k_cache, self.v_cache, ctx.block_tables)
+            else:
+                o = ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
+                                       ctx.max_seqlen_k, self.scale)
+        else:
+            o = ops.paged_decode_gqa(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens, self.scale)
+        return F.linear(o.view(T, self.d), self.w_o, self.b_o)
+
+
+class MLAAttention(nn.Module):
+    def __init__(self, p: _Params, prefix: str, cfg: ModelConfig, rope: torch.Tensor):
+        super().__init__()
+        self.H, self.hd, self.d = cfg.num_heads, cfg.head_dim, cfg.d_model
+        self.r, self.dr = cfg.kv_lora_rank, cfg.rope_dim
+        self.w_qd, self.b_qd = p.lin(prefix + ".q_down_proj")
+        self.w_qu, self.b_qu = p.lin(prefix + ".q_up_proj_fused")
+        # kv_down_proj and k_rope_proj read the same input: one GEMM
+        self.w_kv, self.b_kv = p.lin(prefix + ".kv_down_proj", prefix + ".k_rope_proj")
+        up = p.w[prefix + ".kv_up_proj_fused.weight"].to(p.device, p.dtype)
+        self.w_uk = up[:self.d].view(self.H, self.hd, self.r).contiguous()      # [H, hd, r]
+        self.w_uv = up[self.d:].view(self.H, self.hd, self.r).contiguous()      # [H, hd, r]
+        self.w_o, self.b_o = p.lin(prefix + ".output_proj")
+        self.q_norm, self.kv_norm = p.f32(prefix + ".q_norm.weight"), p.f32(prefix + ".kv_norm.weight")
+        self.rope = rope
+        self.scale = (self.hd + self.dr) ** -0.5
+        self.dtype = p.dtype
+        self.latent_cache = torch.empty(0)   # [num_blocks, block_size, r + dr]; set by the runner
+
+    def forward(self, x, ctx, positions):
+        T, H, hd, r, dr = x.shape[0], self.H, self.hd, self.r, self.dr
+        x = x.to(self.dtype)
+        qc = _vector_norm(F.linear(x, self.w_qd, self.b_qd), self.q_norm)
+        qf = F.linear(qc, self.w_qu, self.b_qu)
+        q_nope = qf[:, :self.d].view(T, H, hd)
+        q_rope = apply_rope(qf[:, self.d:].view(T, H, dr), positions, self.rope).to(self.dtype)
+        kvp = F.linear(x, self.w_kv, self.b_kv)
+        c = _vector_norm(kvp[:, :r], self.kv_norm)
+        pe = apply_rope(kvp[:, r:].unsqueeze(1), positions, self.rope).squeeze(1).to(self.dtype)
+        rows = torch.cat([c, pe], dim=-1)                                   # [T, r + dr]
+        if self.latent_cache.numel():
+            ops.store_rows(rows, self.latent_cache, ctx.slot_mapping)
+        if ctx.is_prefill:
+            o = self._prefill(q_nope, q_rope, rows, ctx)
+        else:
+            q_abs = torch.einsum("thd,hdk->thk", q_nope, self.w_uk)          # absorb W_UK (MLA.py:153)
+            lat = ops.mla_decode(q_abs.contiguous(), q_rope.contiguous(), self.latent_cache, ctx.block_tables,
+                                 ctx.context_lens, self.scale)
+            o = torch.einsum("thk,hdk->thd", lat, self.w_uv)                 # absorb W_UV (MLA.py:178)
+        return F.linear(o.reshape(T, H * hd), self.w_o, self.b_o)
+
+    def _prefill(self, q_nope, q_rope, rows, ctx):
+        """Causal attention of the packed new tokens over their contexts.
+
+        Prefill expands the latent rows once per step instead of absorbing the up-projections into
+        every query: K = [c W_UK^T | pe], V = c W_UV^T per head, without the kv_up_proj_fused biases.
+        That is the same function as the absorbed form the reference evaluates (the q.b_k term is
+        constant over keys and cancels in the softmax; b_v is absent from the reference's cache
+        branch), at 320 instead of 1088 multiply-adds per (query, key, head).
+        """
+        r, H, dr = self.r, self.H, self.dr
+        if ctx.block_tables is not None:
+            rows = self._gather_context_rows(ctx)
+        c, pe = rows[:, :r], rows[:, r:]
+        k = torch.cat([torch.einsum("tk,hdk->thd", c, self.w_uk), pe.unsqueeze(1).expand(-1, H, dr)], dim=-1)
+        v = torch.einsum("tk,hdk->thd", c, self.w_uv).contiguous()
+        q = torch.cat([q_nope, q_rope], dim=-1)
+        return ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
+                                  ctx.max_seqlen_k, self.scale)
+
+    def _gather_context_rows(self, ctx):
+        """Packed latent rows of every sequence's full context, read back through the block tables."""
+        bs = self.latent_cache.shape[1]
+        cu_k = ctx.cu_seqlens_k.long()
+        total = int(cu_k[-1])
+        seq = torch.repeat_interleave(torch.arange(cu_k.numel() - 1, device=cu_k.device), cu_k[1:] - cu_k[:-1],
+                                      output_size=total)
+        pos = torch.arange(total, device=cu_k.device) - cu_k[seq]
+        blk = ctx.block_tables.long()[seq, pos // bs]
+        return self.latent_cache.view(-1, self.latent_cache.shape[-1])[blk * bs + pos % bs]
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, p: _Params, i: int, cfg: ModelConfig, rope: torch.Tensor):
+        super().__init__()
+        prefix = f"layers.{i}"
+        att_cls = MLAAttention if cfg.attention_type == "MLA" else GQAAttention
+        self.att = att_cls(p, prefix + ".att", cfg, rope)
+        self.ffn = MoE(p, prefix + ".ffn", cfg) if cfg.is_moe_layer(i) else MLP(p, prefix + ".ffn")
+        self.att_norm, self.ffn_norm = p.f32(prefix + ".att_norm.weight"), p.f32(prefix + ".ffn_norm.weight")
+        self.eps = cfg.rms_eps
+
+    def forward(self, x, residual, ctx, positions):
+        if residual is None:
+            h, residual = rms_norm(x, self.att_norm, self.eps), x
+        else:
+            h, residual = rms_norm(x, self.att_norm, self.eps, residual)
+        a = self.att(h, ctx, positions)
+        h, residual = rms_norm(a, self.ffn_norm, self.eps, residual)
+        return self.ffn(h), residual
+
+
+class EngineTransformerLM(nn.Module):
+    """``model(input_ids)`` -> hidden states [T, d]; ``compute_logits(hidden)`` -> [num_seqs, vocab]."""
+
+    def __init__(self, cfg: ModelConfig, weights: dict, device, dtype=torch.float32):
+        super().__init__()
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        p = _Params(weights, self.device, dtype)
+        self.embed = p.f32("token_embeddings.weight")
+        rope = _rope_table(cfg.rope_theta, cfg.head_dim, cfg.context_length).to(self.device)
+        self.layers = nn.ModuleList([DecoderLayer(p, i, cfg, rope) for i in range(cfg.num_layers)])
+        self.final_norm = p.f32("final_norm.weight")
+        self.w_head, self.b_head = p.lin("lm_head")
+
+    @property
+    def attention_layers(self):
+        return [layer.att for layer in self.layers]
+
+    def forward(self, input_ids: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        ctx = get_context()
+        if positions is None:
+            positions = ctx.positions if ctx.positions is not None else ctx.context_lens - 1
+        x = self.embed[input_ids]
+        residual = None
+        for layer in self.layers:
+            x, residual = layer(x, residual, ctx, positions)
+        h, _ = rms_norm(x, self.final_norm, self.cfg.rms_eps, residual)
+        return h
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        ctx = get_context()
+        if ctx.is_prefill:
+            hidden = hidden[ctx.cu_seqlens_q[1:].long() - 1]
+        return F.linear(hidden.to(self.dtype), self.w_head, self.b_head)

@@ -97,6 +97,22 @@ def store_kvcache(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cac
                                  _stream()), "store_kvcache")
 
 
+def store_rows(rows: torch.Tensor, cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """cache[slot_mapping[t]] = rows[t] for a single pool (the MLA latent cache).
+
+    rows: [T, W] with contiguous rows; cache: [..., W] contiguous.
+    """
+    dev = _cuda(rows, cache, slot_mapping)
+    T, W = rows.shape
+    if cache.shape[-1] != W or cache.dtype != rows.dtype or not cache.is_contiguous() or rows.stride(1) != 1:
+        raise ValueError("rows/cache shape, dtype or layout mismatch")
+    if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != T or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous int64 tensor with one entry per row")
+    check(lib.b200_store_kvcache(rows.data_ptr(), None, rows.stride(0), 0, cache.data_ptr(), None,
+                                 slot_mapping.data_ptr(), T, 1, W, cache.numel() // W, _dt(rows),
+                                 status_word(dev).data_ptr(), _stream()), "store_rows")
+
+
 def paged_decode_gqa(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_tables: torch.Tensor, context_lens: torch.Tensor, scale: float,
                      out: torch.Tensor | None = None) -> torch.Tensor:

@@ -21,6 +21,8 @@ class Context:
     slot_mapping: Optional[torch.Tensor] = None   # int64 [num_tokens], -1 = skip
     context_lens: Optional[torch.Tensor] = None   # int64 [batch] (decode)
     block_tables: Optional[torch.Tensor] = None   # int32 [batch, max_blocks], -1 padded
+    # not in the reference (its runner builds no positions although the model needs them for RoPE):
+    positions: Optional[torch.Tensor] = None      # int64 [num_tokens]; None in decode = context_lens - 1
 
 
 _current = Context()
@@ -31,10 +33,10 @@ def get_context() -> Context:
 
 
 def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
-                slot_mapping=None, context_lens=None, block_tables=None) -> None:
+                slot_mapping=None, context_lens=None, block_tables=None, positions=None) -> None:
     global _current
     _current = Context(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                       slot_mapping, context_lens, block_tables)
+                       slot_mapping, context_lens, block_tables, positions)
 
 
 def reset_context() -> None:

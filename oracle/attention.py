@@ -153,3 +153,13 @@ def mla_decode(q_abs: torch.Tensor, q_rope: torch.Tensor, latent_cache: torch.Te
         p = torch.softmax(score * scale, dim=-1)
         out[b] = torch.einsum("ht,tk->hk", p, c)
     return out
+
+
+# --------------------------------------------------------------------------- model/utils.py:54-67
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None):
+    """RMSNorm in fp32 returning the input dtype; with ``residual`` the sum is normalised and also
+    returned as the new residual (the fused add + norm of the reference's residual stream)."""
+    dt = x.dtype
+    xf = x.float() if residual is None else x.float() + residual.float()
+    y = (weight * xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dt)
+    return y if residual is None else (y, xf.to(dt))
