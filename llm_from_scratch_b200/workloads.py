@@ -74,3 +74,35 @@ def decode_algorithmic_bytes(case: PagedDecodeCase, num_q_heads: int, num_kv_hea
 def randn_bf16_pool(shape, seed: int, device) -> torch.Tensor:
     g = torch.Generator(device=device).manual_seed(seed)
     return torch.randn(shape, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+
+
+def c5_prefill_lengths(num_seqs: int = 64, total: int = 262144, lo: int = 1, hi: int = 16384,
+                       alpha: float = 1.2, seed: int = 5) -> np.ndarray:
+    """Ragged prefill stress lengths: Zipf(alpha) truncated to [lo, hi] by inverse CDF, rescaled so
+    that the lengths sum to ``total`` (remainder goes to the longest sequence that still has room)."""
+    rng = np.random.default_rng(seed)
+    ks = np.arange(lo, hi + 1, dtype=np.float64)
+    cdf = np.cumsum(ks ** -alpha)
+    cdf /= cdf[-1]
+    lens = ks[np.searchsorted(cdf, rng.uniform(size=num_seqs))]
+    lens = np.clip(np.rint(lens * (total / lens.sum())), lo, hi).astype(np.int64)
+    for _ in range(64):
+        diff = total - int(lens.sum())
+        if diff == 0:
+            break
+        order = np.argsort(-lens)
+        for i in order:
+            room = (hi - lens[i]) if diff > 0 else (lens[i] - lo)
+            step = int(np.sign(diff)) * min(abs(diff), int(room))
+            lens[i] += step
+            diff -= step
+            if diff == 0:
+                break
+    return lens
+
+
+def prefill_flops(lens, num_q_heads: int, head_dim_qk: int, head_dim_v: int) -> float:
+    """Causal attention FLOPs: every (query, visible key) pair costs 2*Dqk (scores) + 2*Dv (values)."""
+    lens = np.asarray(lens, dtype=np.float64)
+    pairs = (lens * (lens + 1) / 2).sum()
+    return float(pairs * num_q_heads * 2 * (head_dim_qk + head_dim_v))

@@ -302,3 +302,73 @@ def test_mla_decode_matches_oracle(dtype, H, r, dr):
                          torch.from_numpy(case.context_lens).cuda(), scale)
     ops.check_status()
     assert_close(got, want, dtype)
+
+
+# ----------------------------------------------------------------------------- prefill, larger cases
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (4, 1, 32)])
+def test_prefill_varlen_long_ragged_batch_bf16(Hq, Hkv, D):
+    ops = _ops()
+    lens = [1, 63, 64, 65, 127, 128, 129, 700, 1500, 2]
+    q, k, v, cu = _prefill_inputs(lens, Hq, Hkv, D, D, torch.bfloat16, seed=3 * D)
+    scale = D ** -0.5
+    want = _oracle().prefill_varlen(q, k, v, cu, cu, scale)
+    got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), scale)
+    ops.check_status()
+    assert_close(got, want, torch.bfloat16)
+
+
+def test_prefill_varlen_strided_q_and_v_views():
+    """q/k/v as column slices of one fused projection output (token stride > row width)."""
+    ops = _ops()
+    lens = [70, 9, 130]
+    T, Hq, Hkv, D = sum(lens), 8, 2, 64
+    qkv = _randn((T, (Hq + 2 * Hkv) * D), 77, torch.bfloat16)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+
+    def views(t):
+        return (t[:, :Hq * D].view(T, Hq, D), t[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D),
+                t[:, (Hq + Hkv) * D:].view(T, Hkv, D))
+    q, k, v = views(qkv)
+    want = _oracle().prefill_varlen(q, k, v, cu, cu, D ** -0.5)
+    qd, kd, vd = views(qkv.cuda())
+    got = ops.prefill_varlen(qd, kd, vd, cu.cuda(), cu.cuda(), max(lens), max(lens), D ** -0.5)
+    assert_close(got, want, torch.bfloat16)
+
+
+def test_prefill_varlen_stress_shape_properties():
+    """Ragged prefill stress shape (64 sequences, Zipf(1.2) lengths in [1,16384], 262,144 tokens,
+    32/8 heads, head_dim 128): too large for the CPU oracle, so size-independent properties:
+    (1) a sequence computed alone gives bit-identical rows to the same sequence inside the batch;
+    (2) causality: changing the last third of a sequence's K/V leaves its earlier rows bit-identical;
+    (3) the first row of every sequence equals its own V row (softmax over one key)."""
+    from llm_from_scratch_b200.workloads import c5_prefill_lengths
+    ops = _ops()
+    lens = c5_prefill_lengths()
+    T, Hq, Hkv, D = int(lens.sum()), 32, 8, 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(T, Hq, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    cu_np = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cu = torch.from_numpy(cu_np).cuda()
+    scale = D ** -0.5
+    out = ops.prefill_varlen(q, k, v, cu, cu, int(lens.max()), int(lens.max()), scale)
+    ops.check_status()
+    assert torch.isfinite(out.float()).all()
+    first_rows = torch.from_numpy(cu_np[:-1].astype(np.int64)).cuda()
+    want_first = v[first_rows].repeat_interleave(Hq // Hkv, dim=1)
+    assert (out[first_rows].float() - want_first.float()).abs().max().item() <= 1e-2
+    order = np.argsort(-lens)
+    for s in (int(order[0]), int(order[len(order) // 2]), int(order[-1])):
+        a, b = int(cu_np[s]), int(cu_np[s + 1])
+        L = b - a
+        cu1 = torch.tensor([0, L], dtype=torch.int32, device="cuda")
+        alone = ops.prefill_varlen(q[a:b], k[a:b], v[a:b], cu1, cu1, L, L, scale)
+        assert torch.equal(alone, out[a:b])
+        if L >= 3:
+            cut = a + (2 * L) // 3
+            k2, v2 = k[a:b].clone(), v[a:b].clone()
+            k2[cut - a:] = 0
+            v2[cut - a:] = 1
+            changed = ops.prefill_varlen(q[a:b], k2, v2, cu1, cu1, L, L, scale)
+            assert torch.equal(changed[:cut - a], out[a:cut])
