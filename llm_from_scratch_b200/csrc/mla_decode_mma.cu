@@ -1,14 +1,402 @@
-// Tensor-core path of the MLA latent-cache decode (bf16).
-#include "common.cuh"
+// MLA latent-cache decode, bf16, tensor-core path (kv_lora_rank 512, rope_dim 64, <= 16 heads,
+// block size 16).
+//
+// Every cached token is one 1152-byte latent row [c (512) | pe (64)] shared by all heads, so a
+// 16-token block is one contiguous 18 KiB segment.  The heads of a sequence are the M = 16 rows
+// of mma.sync m16n8k16:  S[head, token] = Q[head, 576] . row^T  and  O[head, 512] += P . c.
+// At 16 heads that is 30 flop per byte read — HBM-bound, but far more arithmetic than FMA units
+// sustain, which is the only reason the contractions sit on the tensor cores.
+//
+// Work split: as in the GQA decode kernel the flat list of all KV blocks is cut into equal
+// contiguous ranges, one per persistent CTA (one CTA per SM); sequences cut across CTAs are merged
+// by the shared combine kernel.  A CTA (8 warps) consumes its range in groups of four blocks
+// (64 tokens) held in a two-group shared-memory ring filled by 16-byte cp.async copies, so one
+// group (72 KiB) is always in flight while the previous one is being used:
+//   phase 1  warp w: tokens 16*(w&3)..+15, half (w>>2) of the 576-wide contraction -> partial S
+//   phase 2  all threads: sum the halves, scale, mask, online softmax (fp32, log2 domain), P -> smem
+//   phase 3  warp w: O[:, 64w..64w+63] += P . c
+#include "decode_common.cuh"
 
 namespace b200 {
+namespace {
 
-size_t mla_decode_mma_workspace(int, int, int, int) { return 256; }
+constexpr int kTok = 16;
+constexpr int R = 512, DR = 64, ROW = R + DR;     // latent row, elements
+constexpr int ROWB = ROW * 2;                     // 1152 bytes
+constexpr int CPR = ROWB / 16;                    // 72 chunks per row
+constexpr int BLKB = kTok * ROWB;                 // 18432 bytes per block
+constexpr int GROUP = 4;                          // blocks per group (64 tokens)
+constexpr int GT = GROUP * kTok;                  // 64
+constexpr int kThreads = 256;
+constexpr int KSTEPS = ROW / 16;                  // 36
+constexpr int HALF_K = KSTEPS / 2;                // 18
 
-int mla_decode_mma_launch(const void*, const void*, const void*, void*, const int32_t*, int64_t,
-                          const int64_t*, int, int, int, int, int, int64_t, float, void*, size_t,
-                          int32_t*, cudaStream_t) {
-  return B200_ERR_UNSUPPORTED;
+// shared memory map (bytes)
+constexpr int OFF_RING = 0;                                   // 2 groups x 4 blocks
+constexpr int OFF_Q = OFF_RING + 2 * GROUP * BLKB;            // 16 x 1152
+constexpr int OFF_SPART = OFF_Q + 16 * ROWB;                  // [2][16][64] fp32
+constexpr int OFF_P = OFF_SPART + 2 * 16 * GT * 4;            // [16][64] bf16
+constexpr int OFF_STAT = OFF_P + 16 * GT * 2;                 // alpha[16], m[16], l[16] fp32
+constexpr int OFF_SCAN = OFF_STAT + 3 * 16 * 4;               // 34 ints
+constexpr int SMEM_BYTES = OFF_SCAN + 34 * 4 + 8;
+
+struct MlaArgs {
+  const __nv_bfloat16* q_abs;   // [B, H, 512]
+  const __nv_bfloat16* q_rope;  // [B, H, 64]
+  const uint8_t* lat;           // [num_blocks, 16, 576] bf16
+  __nv_bfloat16* out;           // [B, H, 512]
+  const int32_t* bt;
+  int64_t bt_stride;
+  const int64_t* lens;
+  int batch, H;
+  int64_t num_blocks;
+  float scale_log2;
+  float* part_o;
+  float* part_ml;
+  int32_t* seq_info;
+  int32_t* status;
+};
+
+struct Cursor {
+  int seq, blk, nblk, len, remaining;
+};
+struct Group {
+  int seq, blk0, n, len, nblk;
+};
+
+__device__ __forceinline__ int swz72(int c, int row) { return c ^ (row & 7); }
+
+__global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  float* s_part = reinterpret_cast<float*>(smem + OFF_SPART);
+  float* s_alpha = reinterpret_cast<float*>(smem + OFF_STAT);
+  float* s_m = s_alpha + 16;
+  float* s_l = s_alpha + 32;
+  int* s_scan = reinterpret_cast<int*>(smem + OFF_SCAN);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int B = a.batch, H = a.H, p = blockIdx.x;
+
+  const CtaRange rg = plan_cta_range(a.lens, B, a.bt_stride, kTok, s_scan);
+  if (rg.cnt == 0) return;
+
+  auto load_seq = [&](Cursor& c) {
+    const int64_t len = a.lens[c.seq];
+    c.nblk = num_kv_blocks(len, a.bt_stride, kTok);
+    const int64_t cap = static_cast<int64_t>(c.nblk) * kTok;
+    if (len > cap) report(a.status, B200_ERR_BOUNDS);
+    c.len = static_cast<int>(len < cap ? len : cap);
+  };
+  // next group of up to four consecutive blocks of one sequence inside this CTA's range
+  auto next_group = [&](Cursor& c) -> Group {
+    Group gr;
+    gr.seq = c.seq;
+    gr.blk0 = c.blk;
+    gr.len = c.len;
+    gr.nblk = c.nblk;
+    gr.n = min(GROUP, min(c.nblk - c.blk, c.remaining));
+    c.blk += gr.n;
+    c.remaining -= gr.n;
+    if (c.blk >= c.nblk && c.remaining > 0) {
+      c.blk = 0;
+      do {
+        ++c.seq;
+        load_seq(c);
+      } while (c.nblk == 0 && c.seq + 1 < B);
+    }
+    return gr;
+  };
+
+  Cursor L, C;
+  L.seq = rg.start_seq;
+  L.blk = rg.start_off;
+  L.remaining = rg.cnt;
+  load_seq(L);
+  C = L;
+
+  // fills ring half `half` with the four blocks of a group; missing rows / blocks are zero-filled
+  auto issue_group = [&](const Group& gr, int half) {
+#pragma unroll
+    for (int b = 0; b < GROUP; ++b) {
+      const uint32_t dst = sbase + OFF_RING + (half * GROUP + b) * BLKB;
+      int valid = 0;
+      const uint8_t* src = a.lat;
+      if (b < gr.n) {
+        const int id = __ldg(a.bt + static_cast<int64_t>(gr.seq) * a.bt_stride + gr.blk0 + b);
+        if (static_cast<uint64_t>(static_cast<int64_t>(id)) < static_cast<uint64_t>(a.num_blocks)) {
+          valid = min(kTok, gr.len - (gr.blk0 + b) * kTok);
+          src = a.lat + static_cast<int64_t>(id) * BLKB;
+        } else {
+          report(a.status, B200_ERR_BOUNDS);
+        }
+      }
+      for (int idx = tid; idx < kTok * CPR; idx += kThreads) {
+        const int r = idx / CPR, c = idx - r * CPR;
+        const bool ok = r < valid;
+        cp_async16(dst + r * ROWB + swz72(c, r) * 16, ok ? src + idx * 16 : a.lat, ok ? 16 : 0);
+      }
+    }
+  };
+  int groups_issued = 0, groups_total = 0;
+  {
+    // number of groups in the range (walk a copy of the cursor; a few iterations)
+    Cursor t = L;
+    while (t.remaining > 0) {
+      next_group(t);
+      ++groups_total;
+    }
+  }
+  for (int s = 0; s < 2; ++s) {
+    if (groups_issued < groups_total) {
+      const Group gr = next_group(L);
+      issue_group(gr, groups_issued & 1);
+      ++groups_issued;
+    }
+    cp_async_commit();
+  }
+
+  float o[8][4];
+  bool fresh = true;
+  int seg_first = 0;
+  int flat = rg.start;   // flat index of the first block of the current group
+
+  for (int gi = 0; gi < groups_total; ++gi) {
+    const Group gr = next_group(C);
+    const int half = gi & 1;
+    const uint32_t ring = sbase + OFF_RING + half * GROUP * BLKB;
+    // ---- new segment: stage Q = [q_abs | q_rope] (rows >= H are zero), reset the running state
+    if (fresh) {
+      fresh = false;
+      seg_first = gr.blk0;
+      for (int idx = tid; idx < 16 * CPR; idx += kThreads) {
+        const int r = idx / CPR, c = idx - r * CPR;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (r < H) {
+          const int64_t row = static_cast<int64_t>(gr.seq) * H + r;
+          val = c < R / 8 ? __ldg(reinterpret_cast<const uint4*>(a.q_abs + row * R) + c)
+                          : __ldg(reinterpret_cast<const uint4*>(a.q_rope + row * DR) + (c - R / 8));
+        }
+        *reinterpret_cast<uint4*>(smem + OFF_Q + r * ROWB + swz72(c, r) * 16) = val;
+      }
+#pragma unroll
+      for (int n = 0; n < 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+      if (tid < 16) {
+        s_m[tid] = -INFINITY;
+        s_l[tid] = 0.f;
+      }
+    }
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // ---- phase 1: partial S[head, token] over this warp's 16 tokens and half of the 576 columns
+    {
+      const int t4 = warp & 3, kh = warp >> 2;
+      float sacc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+      const uint32_t blk = ring + t4 * BLKB, sQ = sbase + OFF_Q;
+      const int rq = (lane & 7) + ((lane >> 3) & 1) * 8, chq = lane >> 4;   // A: Q rows
+      const int rb = (lane & 7) + (lane >> 4) * 8, chb = (lane >> 3) & 1;   // B: token rows
+#pragma unroll 6
+      for (int i = 0; i < HALF_K; ++i) {
+        const int ks = kh * HALF_K + i;
+        uint32_t af[4], bf[4];
+        ldmatrix_x4(af, sQ + rq * ROWB + swz72(2 * ks + chq, rq) * 16);
+        ldmatrix_x4(bf, blk + rb * ROWB + swz72(2 * ks + chb, rb) * 16);
+        const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+        mma_bf16_16816(sacc[0], af, b0);
+        mma_bf16_16816(sacc[1], af, b1);
+      }
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int token = t4 * 16 + n * 8 + tq * 2;
+        *reinterpret_cast<float2*>(s_part + (kh * 16 + g) * GT + token) = make_float2(sacc[n][0], sacc[n][1]);
+        *reinterpret_cast<float2*>(s_part + (kh * 16 + g + 8) * GT + token) = make_float2(sacc[n][2], sacc[n][3]);
+      }
+    }
+    __syncthreads();
+
+    // ---- phase 2: online softmax over the 64 tokens of the group; thread = (head, 4 tokens)
+    {
+      const int h = tid >> 4, tqd = tid & 15, t0 = tqd * 4;
+      const int valid = min(gr.len - gr.blk0 * kTok, gr.n * kTok);
+      const float4 x0 = *reinterpret_cast<const float4*>(s_part + h * GT + t0);
+      const float4 x1 = *reinterpret_cast<const float4*>(s_part + (16 + h) * GT + t0);
+      float x[4] = {(x0.x + x1.x) * a.scale_log2, (x0.y + x1.y) * a.scale_log2,
+                    (x0.z + x1.z) * a.scale_log2, (x0.w + x1.w) * a.scale_log2};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (t0 + e >= valid) x[e] = -INFINITY;
+      float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float m_old = s_m[h], l_old = s_l[h];
+      const float m_new = fmaxf(m_old, mx);   // finite: token 0 of every group is valid
+      const float alpha = fast_exp2(m_old - m_new);
+      float pr[4], sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pr[e] = fast_exp2(x[e] - m_new);
+        sum += pr[e];
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      __syncwarp();
+      if (tqd == 0) {
+        s_m[h] = m_new;
+        s_l[h] = l_old * alpha + sum;
+        s_alpha[h] = alpha;
+      }
+      uint2 packed;
+      packed.x = pack_bf16x2(pr[0], pr[1]);
+      packed.y = pack_bf16x2(pr[2], pr[3]);
+      *reinterpret_cast<uint2*>(smem + OFF_P + h * 128 + (((tqd >> 1) ^ (h & 7)) * 16) + (tqd & 1) * 8) = packed;
+    }
+    __syncthreads();
+
+    // ---- phase 3: O[:, 64*warp .. +63] = alpha * O + P . c
+    {
+      const float al0 = s_alpha[g], al1 = s_alpha[g + 8];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        o[n][0] *= al0;
+        o[n][1] *= al0;
+        o[n][2] *= al1;
+        o[n][3] *= al1;
+      }
+      const uint32_t sP = sbase + OFF_P;
+      const int rp = (lane & 7) + ((lane >> 3) & 1) * 8, chp = lane >> 4;   // A: P rows; B: token rows
+#pragma unroll
+      for (int kk = 0; kk < GROUP; ++kk) {
+        uint32_t pf[4];
+        ldmatrix_x4(pf, sP + rp * 128 + (((2 * kk + chp) ^ (rp & 7)) * 16));
+#pragma unroll
+        for (int pr2 = 0; pr2 < 4; ++pr2) {
+          uint32_t bf[4];
+          const int chunk = 8 * warp + 2 * pr2 + chp;
+          ldmatrix_x4_trans(bf, ring + kk * BLKB + rp * ROWB + swz72(chunk, rp) * 16);
+          const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+          mma_bf16_16816(o[2 * pr2], pf, b0);
+          mma_bf16_16816(o[2 * pr2 + 1], pf, b1);
+        }
+      }
+    }
+    __syncthreads();   // this ring half, P and the partial-S buffer are free again
+
+    if (groups_issued < groups_total) {
+      const Group nx = next_group(L);
+      issue_group(nx, half);
+      ++groups_issued;
+    }
+    cp_async_commit();
+
+    const bool seq_end = gr.blk0 + gr.n == gr.nblk;
+    if (seq_end || gi == groups_total - 1) {
+      fresh = true;
+      const bool whole = seq_end && seg_first == 0;
+      const int h0 = g, h1 = g + 8;
+      if (whole) {
+        const float i0 = 1.f / s_l[h0], i1 = 1.f / s_l[h1];
+        __nv_bfloat16* ob = a.out + static_cast<int64_t>(gr.seq) * H * R;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const int d = 64 * warp + n * 8 + tq * 2;
+          if (h0 < H) *reinterpret_cast<uint32_t*>(ob + h0 * R + d) = pack_bf16x2(o[n][0] * i0, o[n][1] * i0);
+          if (h1 < H) *reinterpret_cast<uint32_t*>(ob + h1 * R + d) = pack_bf16x2(o[n][2] * i1, o[n][3] * i1);
+        }
+      } else {
+        const int64_t pslot = static_cast<int64_t>(p) * 2 + (seg_first > 0 ? 0 : 1);
+        float* po = a.part_o + pslot * H * R;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const int d = 64 * warp + n * 8 + tq * 2;
+          if (h0 < H) *reinterpret_cast<float2*>(po + h0 * R + d) = make_float2(o[n][0], o[n][1]);
+          if (h1 < H) *reinterpret_cast<float2*>(po + h1 * R + d) = make_float2(o[n][2], o[n][3]);
+        }
+        if (tid < H)
+          *reinterpret_cast<float2*>(a.part_ml + (pslot * H + tid) * 2) = make_float2(s_m[tid], s_l[tid]);
+      }
+      if (seq_end && tid == 0) {
+        const int seq_start_flat = flat - gr.blk0;
+        a.seq_info[2 * gr.seq] = whole ? -1 : seq_start_flat / rg.per_cta;
+        a.seq_info[2 * gr.seq + 1] = whole ? -1 : p;
+      }
+      __syncthreads();   // the running state is re-initialised by the next segment
+    }
+    flat += gr.n;
+  }
+  cp_async_wait<0>();
+}
+
+bool mla_fast_shape(int H, int r, int dr, int bs) {
+  return r == R && dr == DR && bs == kTok && H >= 1 && H <= 16;
+}
+
+}  // namespace
+
+size_t mla_decode_mma_workspace(int batch, int H, int r, int dr) {
+  if (!mla_fast_shape(H, r, dr, kTok)) return 256;
+  int sms = sm_count_cached();
+  if (sms <= 0) sms = 148;
+  return decode_workspace_bytes(static_cast<size_t>(sms), batch, H, R);
+}
+
+int mla_decode_mma_launch(const void* q_abs, const void* q_rope, const void* lat, void* out,
+                          const int32_t* bt, int64_t bt_stride, const int64_t* lens, int batch,
+                          int H, int r, int dr, int bs, int64_t num_blocks, float scale,
+                          void* workspace, size_t workspace_bytes, int32_t* status,
+                          cudaStream_t s) {
+  if (!mla_fast_shape(H, r, dr, bs)) return B200_ERR_UNSUPPORTED;
+  if (!aligned16(q_abs) || !aligned16(q_rope) || !aligned16(lat) || !aligned16(out))
+    return B200_ERR_UNSUPPORTED;
+  const int sms = sm_count_cached();
+  if (sms <= 0) return B200_ERR_NO_DEVICE;
+  const size_t grid = static_cast<size_t>(sms);
+  const size_t need = decode_workspace_bytes(grid, batch, H, R);
+  if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(mla_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    configured[dev] = true;
+  }
+  MlaArgs a{};
+  a.q_abs = static_cast<const __nv_bfloat16*>(q_abs);
+  a.q_rope = static_cast<const __nv_bfloat16*>(q_rope);
+  a.lat = static_cast<const uint8_t*>(lat);
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.bt = bt;
+  a.bt_stride = bt_stride;
+  a.lens = lens;
+  a.batch = batch;
+  a.H = H;
+  a.num_blocks = num_blocks;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  a.part_o = reinterpret_cast<float*>(w);
+  w += align256(grid * 2 * H * R * sizeof(float));
+  a.part_ml = reinterpret_cast<float*>(w);
+  w += align256(grid * 2 * H * 2 * sizeof(float));
+  a.seq_info = reinterpret_cast<int32_t*>(w);
+  mla_decode_mma_kernel<<<static_cast<int>(grid), kThreads, SMEM_BYTES, s>>>(a);
+  const int rc = launch_result();
+  if (rc != B200_OK) return rc;
+  CombineArgs c{};
+  c.out = out;
+  c.lens = lens;
+  c.part_o = a.part_o;
+  c.part_ml = a.part_ml;
+  c.seq_info = a.seq_info;
+  c.batch = batch;
+  c.H = H;
+  c.D = R;
+  return decode_combine_launch(c, s);
 }
 
 }  // namespace b200

@@ -22,7 +22,7 @@
 // fp32 FMA arithmetic.  It is the path the fp32 engine configuration uses.
 #include <limits.h>
 
-#include "common.cuh"
+#include "decode_common.cuh"
 
 namespace b200 {
 namespace {
@@ -47,34 +47,6 @@ struct DecodeArgs {
   int32_t* seq_info; // [batch][2]         first / last CTA of a split sequence, or -1
   int32_t* status;
 };
-
-__device__ __forceinline__ int num_kv_blocks(int64_t len, int64_t bt_stride, int bs) {
-  if (len <= 0) return 0;
-  int64_t n = (len + bs - 1) / bs;
-  return static_cast<int>(n < bt_stride ? n : bt_stride);
-}
-
-// inclusive scan over the CTA; `scratch` holds one int per warp
-__device__ __forceinline__ int block_inclusive_scan(int v, int* scratch, int* total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  int x = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    int y = __shfl_up_sync(0xffffffffu, x, o);
-    if (lane >= o) x += y;
-  }
-  if (lane == 31) scratch[warp] = x;
-  __syncthreads();
-  int add = 0, tot = 0;
-  for (int w = 0; w < nw; ++w) {
-    int s = scratch[w];
-    if (w < warp) add += s;
-    tot += s;
-  }
-  __syncthreads();
-  *total = tot;
-  return x + add;
-}
 
 struct Cursor {
   int seq, blk, nblk, len;
@@ -466,6 +438,25 @@ paged_decode_combine_kernel(const DecodeArgs a) {
   }
 }
 
+}  // namespace
+
+int decode_combine_launch(const CombineArgs& c, cudaStream_t s) {
+  DecodeArgs a{};
+  a.out = c.out;
+  a.lens = c.lens;
+  a.part_o = const_cast<float*>(c.part_o);
+  a.part_ml = const_cast<float*>(c.part_ml);
+  a.seq_info = const_cast<int32_t*>(c.seq_info);
+  a.batch = c.batch;
+  a.Hq = c.H;
+  a.D = c.D;
+  paged_decode_combine_kernel<<<c.batch, kCombineThreads,
+                                (kCombineMaxParts + 2) * c.H * sizeof(float), s>>>(a);
+  return launch_result();
+}
+
+namespace {
+
 // ---------------------------------------------------------------------------------------------
 // Generic path: grid (batch, Hq), 4 warps; warp w takes tokens w, w+4, ...; a lane owns the
 // head-dim elements lane, lane+32, ...
@@ -579,8 +570,6 @@ FastPlan fast_plan(int Hq, int Hkv, int D, int bs, int dtype) {
   pl.ok = true;
   return pl;
 }
-
-inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 template <int D, int NT>
 int launch_fast(const DecodeArgs& a, const FastPlan& pl, int grid, cudaStream_t s) {

@@ -106,3 +106,11 @@ def prefill_flops(lens, num_q_heads: int, head_dim_qk: int, head_dim_v: int) -> 
     lens = np.asarray(lens, dtype=np.float64)
     pairs = (lens * (lens + 1) / 2).sum()
     return float(pairs * num_q_heads * 2 * (head_dim_qk + head_dim_v))
+
+
+def c4_decode_case(batch: int = 240, lo: int = 512, hi: int = 16384, block_size: int = 16,
+                   seed: int = 4) -> PagedDecodeCase:
+    """MLA decode part of the mixed MLA workload: contexts uniform in [lo, hi]."""
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(lo, hi + 1, size=batch).astype(np.int64)
+    return deal_blocks(lens, block_size, rng, pad_blocks=8)

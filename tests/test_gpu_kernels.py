@@ -372,3 +372,37 @@ def test_prefill_varlen_stress_shape_properties():
             v2[cut - a:] = 1
             changed = ops.prefill_varlen(q[a:b], k2, v2, cu1, cu1, L, L, scale)
             assert torch.equal(changed[:cut - a], out[a:cut])
+
+
+def test_mla_decode_bf16_long_contexts_cut_across_ctas():
+    ops = _ops()
+    H, r, dr, bs = 16, 512, 64, 16
+    lens = [9000, 3, 16 * 148 * 2 + 5, 64, 65, 1]
+    case = deal_blocks(lens, bs, np.random.default_rng(8), pad_blocks=2)
+    B = len(lens)
+    qa = (_randn((B, H, r), 60, torch.float32) * 0.2).to(torch.bfloat16)
+    qr = _randn((B, H, dr), 61, torch.bfloat16)
+    lat = _randn((case.num_blocks, bs, r + dr), 62, torch.bfloat16)
+    scale = 192 ** -0.5
+    want = _oracle().mla_decode(qa, qr, lat, case.block_tables, case.context_lens, scale)
+    bt, cl = torch.from_numpy(case.block_tables).cuda(), torch.from_numpy(case.context_lens).cuda()
+    got = ops.mla_decode(qa.cuda(), qr.cuda(), lat.cuda(), bt, cl, scale)
+    ops.check_status()
+    assert_close(got, want, torch.bfloat16)
+    again = ops.mla_decode(qa.cuda(), qr.cuda(), lat.cuda(), bt, cl, scale)
+    assert torch.equal(got, again)
+
+
+def test_mla_decode_bf16_fewer_than_16_heads():
+    ops = _ops()
+    H, r, dr, bs = 5, 512, 64, 16
+    lens = [130, 700, 31]
+    case = deal_blocks(lens, bs, np.random.default_rng(9), pad_blocks=1)
+    qa = (_randn((3, H, r), 70, torch.float32) * 0.2).to(torch.bfloat16)
+    qr = _randn((3, H, dr), 71, torch.bfloat16)
+    lat = _randn((case.num_blocks, bs, r + dr), 72, torch.bfloat16)
+    want = _oracle().mla_decode(qa, qr, lat, case.block_tables, case.context_lens, 0.07)
+    got = ops.mla_decode(qa.cuda(), qr.cuda(), lat.cuda(), torch.from_numpy(case.block_tables).cuda(),
+                         torch.from_numpy(case.context_lens).cuda(), 0.07)
+    ops.check_status()
+    assert_close(got, want, torch.bfloat16)
