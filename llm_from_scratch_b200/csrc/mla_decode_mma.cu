@@ -62,6 +62,7 @@ struct Cursor {
 };
 struct Group {
   int seq, blk0, n, len, nblk;
+  int ids[4];   // physical block ids, fetched when the group is formed (well before they are used)
 };
 
 __device__ __forceinline__ int swz72(int c, int row) { return c ^ (row & 7); }
@@ -89,13 +90,18 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
     c.len = static_cast<int>(len < cap ? len : cap);
   };
   // next group of up to four consecutive blocks of one sequence inside this CTA's range
-  auto next_group = [&](Cursor& c) -> Group {
+  auto next_group = [&](Cursor& c, bool with_ids) -> Group {
     Group gr;
     gr.seq = c.seq;
     gr.blk0 = c.blk;
     gr.len = c.len;
     gr.nblk = c.nblk;
     gr.n = min(GROUP, min(c.nblk - c.blk, c.remaining));
+#pragma unroll
+    for (int b = 0; b < GROUP; ++b)
+      gr.ids[b] = (with_ids && b < gr.n)
+                      ? __ldg(a.bt + static_cast<int64_t>(gr.seq) * a.bt_stride + gr.blk0 + b)
+                      : -1;
     c.blk += gr.n;
     c.remaining -= gr.n;
     if (c.blk >= c.nblk && c.remaining > 0) {
@@ -123,7 +129,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
       int valid = 0;
       const uint8_t* src = a.lat;
       if (b < gr.n) {
-        const int id = __ldg(a.bt + static_cast<int64_t>(gr.seq) * a.bt_stride + gr.blk0 + b);
+        const int id = gr.ids[b];
         if (static_cast<uint64_t>(static_cast<int64_t>(id)) < static_cast<uint64_t>(a.num_blocks)) {
           valid = min(kTok, gr.len - (gr.blk0 + b) * kTok);
           src = a.lat + static_cast<int64_t>(id) * BLKB;
@@ -143,13 +149,13 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
     // number of groups in the range (walk a copy of the cursor; a few iterations)
     Cursor t = L;
     while (t.remaining > 0) {
-      next_group(t);
+      next_group(t, false);
       ++groups_total;
     }
   }
   for (int s = 0; s < 2; ++s) {
     if (groups_issued < groups_total) {
-      const Group gr = next_group(L);
+      const Group gr = next_group(L, true);
       issue_group(gr, groups_issued & 1);
       ++groups_issued;
     }
@@ -162,8 +168,14 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
   int flat = rg.start;   // flat index of the first block of the current group
 
   for (int gi = 0; gi < groups_total; ++gi) {
-    const Group gr = next_group(C);
+    const Group gr = next_group(C, false);
     const int half = gi & 1;
+    // form the group that will refill this ring half after phase 3 now, so that its block ids
+    // (and, on a sequence change, its context length) are in registers by then
+    Group nx;
+    nx.n = 0;
+    const bool have_next = groups_issued < groups_total;
+    if (have_next) nx = next_group(L, true);
     const uint32_t ring = sbase + OFF_RING + half * GROUP * BLKB;
     // ---- new segment: stage Q = [q_abs | q_rope] (rows >= H are zero), reset the running state
     if (fresh) {
@@ -284,8 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
     }
     __syncthreads();   // this ring half, P and the partial-S buffer are free again
 
-    if (groups_issued < groups_total) {
-      const Group nx = next_group(L);
+    if (have_next) {
       issue_group(nx, half);
       ++groups_issued;
     }

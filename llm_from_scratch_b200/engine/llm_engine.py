@@ -17,11 +17,13 @@ from .sequence import Sequence
 
 
 class LLMEngine:
-    def __init__(self, config: dict, model=None, tokenizer=None, verbose: bool = False):
+    def __init__(self, config: dict, model=None, tokenizer=None, verbose: bool = False, runner=None):
         self.config = config
         block_size = _cfg(config, "block_size", default=256)
         Sequence.block_size = block_size
-        self.model_runner = ModelRunner(config, model)
+        # ``runner`` lets a caller supply its own executor (anything with ``run(seqs, is_prefill)``,
+        # ``num_kv_blocks`` and ``exit()``); by default the GPU model runner is built here
+        self.model_runner = runner if runner is not None else ModelRunner(config, model)
         self.scheduler = Scheduler(
             max_num_sequences=_cfg(config, "max_num_sequences", "max_num_seqs", default=16),
             max_num_batched_tokens=_cfg(config, "max_num_batched_tokens", "max_num_batch_tokens", default=1024),

@@ -1,0 +1,79 @@
+"""Data-parallel serving: independent engine replicas, one per GPU, no collective on the hot path.
+
+The reference's only multi-GPU scaffold is tensor-parallel worker processes that are never given
+sharded layers (engine/llm_engine.py:38-50, engine/model_runner.py:66-134).  This design shards
+REQUESTS instead: request i goes to replica ``i mod N``; every replica owns its scheduler, block
+pool and KV cache, so the token stream of a request is bit-identical to what a single-GPU run of
+the same sub-list produces.  ``torch.distributed`` is used only off the hot path, to hand the
+results and timing back to rank 0 (``gather_object``) — NCCL on GPUs, gloo on CPU ranks in tests.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+
+def shard_requests(requests: list, world_size: int, rank: int) -> list:
+    """The sub-list of ``requests`` served by ``rank`` (round-robin by arrival index)."""
+    return requests[rank::world_size]
+
+
+def merge_outputs(per_rank: list[list], total: int) -> list:
+    """Inverse of ``shard_requests``: per-rank result lists back into arrival order."""
+    world = len(per_rank)
+    out = [None] * total
+    for r, items in enumerate(per_rank):
+        for j, item in enumerate(items):
+            out[r + j * world] = item
+    if any(x is None for x in out):
+        raise ValueError("replica results do not cover every request")
+    return out
+
+
+@dataclass
+class ReplicaReport:
+    rank: int
+    token_ids: list = field(default_factory=list)     # completions of this rank's shard, in shard order
+    wall_s: float = 0.0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    steps: int = 0
+
+
+def serve_shard(engine, shard: list, rank: int = 0) -> ReplicaReport:
+    """Runs one replica over its shard: ``shard`` is a list of (token_ids, SamplingParams)."""
+    seqs = [engine.add_request(tok, sp) for tok, sp in shard]
+    rep = ReplicaReport(rank=rank)
+    t0 = time.perf_counter()
+    while not engine.is_finished():
+        outputs, n, is_prefill = engine.step()
+        if n == 0 and not outputs:
+            raise RuntimeError("nothing schedulable: KV pool too small for the waiting request")
+        rep.steps += 1
+        if is_prefill:
+            rep.prefill_tokens += n
+        else:
+            rep.decode_tokens += n
+    rep.wall_s = time.perf_counter() - t0
+    rep.token_ids = [s.completion_token_ids for s in seqs]
+    return rep
+
+
+def serve_sharded(make_engine, requests: list):
+    """Every rank of the initialised process group serves its shard; rank 0 gets
+    ``(token_ids in arrival order, [ReplicaReport per rank])``, other ranks get ``(None, None)``.
+
+    ``make_engine(rank)`` builds the replica's engine (on ``cuda:LOCAL_RANK`` for GPU runs).
+    Without an initialised process group this is a single replica.
+    """
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        rep = serve_shard(make_engine(0), requests, 0)
+        return rep.token_ids, [rep]
+    rank, world = dist.get_rank(), dist.get_world_size()
+    rep = serve_shard(make_engine(rank), shard_requests(requests, world, rank), rank)
+    gathered = [None] * world if rank == 0 else None
+    dist.gather_object(rep, gathered, dst=0)
+    if rank != 0:
+        return None, None
+    return merge_outputs([r.token_ids for r in gathered], len(requests)), gathered
