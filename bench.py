@@ -141,11 +141,29 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg (profiling runs)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "store"],
+                    help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
+                         "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="sequences per GPU; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+
+    if args.workload != "decode":
+        from llm_from_scratch_b200 import microbench
+        torch.cuda.set_device(0)
+        fn = getattr(microbench, args.workload)
+        kw = dict(steps=args.steps, warmup=args.warmup)
+        if args.batch != BATCH:   # profiling cases: fewer sequences / tokens
+            kw["batch" if args.workload == "mla_decode" else ("total" if args.workload == "prefill" else "tokens")] = args.batch
+        res = fn(**kw)
+        peak, kind = hbm_peak()
+        if "gbs" in res:
+            res["hbm_frac"] = res["gbs"] / peak
+            res["hbm_peak"] = f"{peak} GB/s of {kind}"
+        print(json.dumps(res))
+        return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

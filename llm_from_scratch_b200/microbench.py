@@ -1,0 +1,83 @@
+"""Timed runs of the secondary kernels on their benchmark shapes (used by ``bench.py --workload``).
+
+Each function builds the seeded synthetic inputs on the current CUDA device, times the op with CUDA
+events after warm-up and returns a dict with the time per call, the algorithmic bytes / FLOPs of a
+call and the achieved rate.  Inputs are larger than the 126 MB L2, so no flush is needed.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import ops
+from .workloads import c4_decode_case, c5_prefill_lengths, prefill_flops
+
+
+def _time(fn, steps: int, warmup: int) -> float:
+    for _ in range(max(warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def mla_decode(steps: int = 50, warmup: int = 5, batch: int = 240) -> dict:
+    """MLA latent decode: ``batch`` sequences, contexts uniform in [512,16384], 16 heads, 512+64."""
+    case = c4_decode_case(batch)
+    H, r, dr = 16, 512, 64
+    g = torch.Generator(device="cuda").manual_seed(4)
+    lat = torch.randn(case.num_blocks, 16, r + dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    qa = (torch.randn(case.batch, H, r, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    qr = torch.randn(case.batch, H, dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    bt, cl = torch.from_numpy(case.block_tables).cuda(), torch.from_numpy(case.context_lens).cuda()
+    out = torch.empty_like(qa)
+    ms = _time(lambda: ops.mla_decode(qa, qr, lat, bt, cl, 192 ** -0.5, out=out), steps, warmup)
+    ops.check_status()
+    tok = case.total_tokens
+    nbytes = tok * (r + dr) * 2 + case.batch * H * (2 * r + dr) * 2 + 4 * int(((case.context_lens + 15) // 16).sum())
+    flops = tok * H * 2 * (2 * r + dr)
+    return dict(workload=f"MLA latent decode: {case.batch} seqs, ctx uniform [512,16384], 16 heads, r=512, dr=64, bf16",
+                ms=ms, context_tokens=tok, algorithmic_bytes=nbytes, flops=flops, gbs=nbytes / ms / 1e6,
+                tflops=flops / ms / 1e9, launches_per_call=2)
+
+
+def prefill(steps: int = 5, warmup: int = 2, total: int = 262144) -> dict:
+    """Ragged causal prefill: 64 sequences, Zipf(1.2) lengths in [1,16384], 32/8 heads, head_dim 128."""
+    lens = c5_prefill_lengths(total=total)
+    T, Hq, Hkv, D = int(lens.sum()), 32, 8, 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(T, Hq, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).cuda()
+    out = torch.empty_like(q)
+    mx = int(lens.max())
+    ms = _time(lambda: ops.prefill_varlen(q, k, v, cu, cu, mx, mx, D ** -0.5, out=out), steps, warmup)
+    ops.check_status()
+    flops = prefill_flops(lens, Hq, D, D)
+    return dict(workload=f"ragged causal prefill: 64 seqs, Zipf(1.2) lengths in [1,16384], {T} tokens, 32/8 heads, "
+                         "head_dim 128, bf16", ms=ms, tokens=T, lengths=sorted(lens.tolist(), reverse=True),
+                flops=flops, tflops=flops / ms / 1e9, launches_per_call=1)
+
+
+def store(steps: int = 50, warmup: int = 5, tokens: int = 262144) -> dict:
+    """store_kvcache of the prefill stress batch: shuffled slot mapping (seed 2), 8 x 128 bf16 rows."""
+    Hkv, D, bs = 8, 128, 16
+    g = torch.Generator(device="cuda").manual_seed(2)
+    k = torch.randn(tokens, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(tokens, Hkv, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    nblk = tokens // bs
+    perm = torch.randperm(nblk, generator=g, device="cuda")
+    slots = (perm.repeat_interleave(bs) * bs + torch.arange(bs, device="cuda").repeat(nblk)).to(torch.int64)
+    kc = torch.zeros(nblk, bs, Hkv, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    ms = _time(lambda: ops.store_kvcache(k, v, kc, vc, slots), steps, warmup)
+    ops.check_status()
+    nbytes = tokens * (2 * Hkv * D * 2 * 2 + 8)
+    return dict(workload=f"store_kvcache: {tokens} tokens, 8 kv heads x 128, bf16, block-contiguous shuffled slots",
+                ms=ms, tokens=tokens, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, launches_per_call=1)
