@@ -9,12 +9,13 @@
 //
 // Work split: as in the GQA decode kernel the flat list of all KV blocks is cut into equal
 // contiguous ranges, one per persistent CTA (one CTA per SM); sequences cut across CTAs are merged
-// by the shared combine kernel.  A CTA (8 warps) consumes its range in groups of four blocks
+// by the shared combine kernel.  A CTA (16 warps) consumes its range in groups of four blocks
 // (64 tokens) held in a two-group shared-memory ring filled by 16-byte cp.async copies, so one
 // group (72 KiB) is always in flight while the previous one is being used:
-//   phase 1  warp w: tokens 16*(w&3)..+15, half (w>>2) of the 576-wide contraction -> partial S
-//   phase 2  all threads: sum the halves, scale, mask, online softmax (fp32, log2 domain), P -> smem
-//   phase 3  warp w: O[:, 64w..64w+63] += P . c
+//   phase 1  warp w: tokens 16*(w&3)..+15, quarter (w>>2) of the 576-wide contraction -> partial S
+//            (its Q fragments stay in registers for the whole sequence segment)
+//   phase 2  warp h: sums the quarters of head h, scale, mask, online softmax (fp32, log2 domain), P -> smem
+//   phase 3  warp w: O[:, 32w..32w+31] += P . c
 #include "decode_common.cuh"
 
 namespace b200 {
@@ -27,15 +28,17 @@ constexpr int CPR = ROWB / 16;                    // 72 chunks per row
 constexpr int BLKB = kTok * ROWB;                 // 18432 bytes per block
 constexpr int GROUP = 4;                          // blocks per group (64 tokens)
 constexpr int GT = GROUP * kTok;                  // 64
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;                     // 16 warps: 4 token blocks x 4 k-quarters
 constexpr int KSTEPS = ROW / 16;                  // 36
-constexpr int HALF_K = KSTEPS / 2;                // 18
+constexpr int QUART_K = KSTEPS / 4;               // 9 k-steps per warp in phase 1
+constexpr int SP_STRIDE = GT + 8;                 // padded row of the partial-S buffer (floats)
+constexpr int LOADS = (kTok * CPR + kThreads - 1) / kThreads;   // cp.async per thread per block
 
 // shared memory map (bytes)
 constexpr int OFF_RING = 0;                                   // 2 groups x 4 blocks
 constexpr int OFF_Q = OFF_RING + 2 * GROUP * BLKB;            // 16 x 1152
-constexpr int OFF_SPART = OFF_Q + 16 * ROWB;                  // [2][16][64] fp32
-constexpr int OFF_P = OFF_SPART + 2 * 16 * GT * 4;            // [16][64] bf16
+constexpr int OFF_SPART = OFF_Q + 16 * ROWB;                  // [4][16][72] fp32
+constexpr int OFF_P = OFF_SPART + 4 * 16 * SP_STRIDE * 4;     // [16][64] bf16
 constexpr int OFF_STAT = OFF_P + 16 * GT * 2;                 // alpha[16], m[16], l[16] fp32
 constexpr int OFF_SCAN = OFF_STAT + 3 * 16 * 4;               // 34 ints
 constexpr int SMEM_BYTES = OFF_SCAN + 34 * 4 + 8;
@@ -121,6 +124,16 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
   load_seq(L);
   C = L;
 
+  // per-thread copy pattern of one block, fixed for the whole kernel
+  int ld_row[LOADS], ld_dst[LOADS], ld_src[LOADS];
+#pragma unroll
+  for (int i = 0; i < LOADS; ++i) {
+    const int idx = tid + i * kThreads;
+    const int r = idx / CPR, c = idx - r * CPR;
+    ld_row[i] = idx < kTok * CPR ? r : -1;
+    ld_dst[i] = r * ROWB + swz72(c, r) * 16;
+    ld_src[i] = idx * 16;
+  }
   // fills ring half `half` with the four blocks of a group; missing rows / blocks are zero-filled
   auto issue_group = [&](const Group& gr, int half) {
 #pragma unroll
@@ -137,10 +150,11 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
           report(a.status, B200_ERR_BOUNDS);
         }
       }
-      for (int idx = tid; idx < kTok * CPR; idx += kThreads) {
-        const int r = idx / CPR, c = idx - r * CPR;
-        const bool ok = r < valid;
-        cp_async16(dst + r * ROWB + swz72(c, r) * 16, ok ? src + idx * 16 : a.lat, ok ? 16 : 0);
+#pragma unroll
+      for (int i = 0; i < LOADS; ++i) {
+        if (ld_row[i] < 0) continue;
+        const bool ok = ld_row[i] < valid;
+        cp_async16(dst + ld_dst[i], ok ? src + ld_src[i] : a.lat, ok ? 16 : 0);
       }
     }
   };
@@ -162,8 +176,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
     cp_async_commit();
   }
 
-  float o[8][4];
-  bool fresh = true;
+  float o[4][4];
+  uint32_t qf[QUART_K][4];
+  bool fresh = true, load_q = false;
   int seg_first = 0;
   int flat = rg.start;   // flat index of the first block of the current group
 
@@ -192,7 +207,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         *reinterpret_cast<uint4*>(smem + OFF_Q + r * ROWB + swz72(c, r) * 16) = val;
       }
 #pragma unroll
-      for (int n = 0; n < 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+      for (int n = 0; n < 4; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+      load_q = true;
       if (tid < 16) {
         s_m[tid] = -INFINITY;
         s_l[tid] = 0.f;
@@ -201,77 +217,74 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
     cp_async_wait<1>();
     __syncthreads();
 
-    // ---- phase 1: partial S[head, token] over this warp's 16 tokens and half of the 576 columns
+    // ---- phase 1: partial S[head, token] over this warp's 16 tokens and a quarter of the 576 columns
     {
-      const int t4 = warp & 3, kh = warp >> 2;
+      const int t4 = warp & 3, kq = warp >> 2;
+      if (load_q) {
+        load_q = false;
+        const uint32_t sQ = sbase + OFF_Q;
+        const int rq = (lane & 7) + ((lane >> 3) & 1) * 8, chq = lane >> 4;   // A operand: Q rows
+#pragma unroll
+        for (int i = 0; i < QUART_K; ++i)
+          ldmatrix_x4(qf[i], sQ + rq * ROWB + swz72(2 * (kq * QUART_K + i) + chq, rq) * 16);
+      }
       float sacc[2][4];
 #pragma unroll
       for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
-      const uint32_t blk = ring + t4 * BLKB, sQ = sbase + OFF_Q;
-      const int rq = (lane & 7) + ((lane >> 3) & 1) * 8, chq = lane >> 4;   // A: Q rows
-      const int rb = (lane & 7) + (lane >> 4) * 8, chb = (lane >> 3) & 1;   // B: token rows
-#pragma unroll 6
-      for (int i = 0; i < HALF_K; ++i) {
-        const int ks = kh * HALF_K + i;
-        uint32_t af[4], bf[4];
-        ldmatrix_x4(af, sQ + rq * ROWB + swz72(2 * ks + chq, rq) * 16);
-        ldmatrix_x4(bf, blk + rb * ROWB + swz72(2 * ks + chb, rb) * 16);
+      const uint32_t blk = ring + t4 * BLKB;
+      const int rb = (lane & 7) + (lane >> 4) * 8, chb = (lane >> 3) & 1;   // B operand: token rows
+#pragma unroll
+      for (int i = 0; i < QUART_K; ++i) {
+        uint32_t bf[4];
+        ldmatrix_x4(bf, blk + rb * ROWB + swz72(2 * (kq * QUART_K + i) + chb, rb) * 16);
         const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
-        mma_bf16_16816(sacc[0], af, b0);
-        mma_bf16_16816(sacc[1], af, b1);
+        mma_bf16_16816(sacc[0], qf[i], b0);
+        mma_bf16_16816(sacc[1], qf[i], b1);
       }
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
         const int token = t4 * 16 + n * 8 + tq * 2;
-        *reinterpret_cast<float2*>(s_part + (kh * 16 + g) * GT + token) = make_float2(sacc[n][0], sacc[n][1]);
-        *reinterpret_cast<float2*>(s_part + (kh * 16 + g + 8) * GT + token) = make_float2(sacc[n][2], sacc[n][3]);
+        *reinterpret_cast<float2*>(s_part + (kq * 16 + g) * SP_STRIDE + token) = make_float2(sacc[n][0], sacc[n][1]);
+        *reinterpret_cast<float2*>(s_part + (kq * 16 + g + 8) * SP_STRIDE + token) = make_float2(sacc[n][2], sacc[n][3]);
       }
     }
     __syncthreads();
 
-    // ---- phase 2: online softmax over the 64 tokens of the group; thread = (head, 4 tokens)
+    // ---- phase 2: online softmax over the 64 tokens of the group; warp = head, lane = 2 tokens
     {
-      const int h = tid >> 4, tqd = tid & 15, t0 = tqd * 4;
+      const int h = warp, t0 = lane * 2;
       const int valid = min(gr.len - gr.blk0 * kTok, gr.n * kTok);
-      const float4 x0 = *reinterpret_cast<const float4*>(s_part + h * GT + t0);
-      const float4 x1 = *reinterpret_cast<const float4*>(s_part + (16 + h) * GT + t0);
-      float x[4] = {(x0.x + x1.x) * a.scale_log2, (x0.y + x1.y) * a.scale_log2,
-                    (x0.z + x1.z) * a.scale_log2, (x0.w + x1.w) * a.scale_log2};
+      float x[2] = {0.f, 0.f};
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (t0 + e >= valid) x[e] = -INFINITY;
-      float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      for (int kq = 0; kq < 4; ++kq) {
+        const float2 v = *reinterpret_cast<const float2*>(s_part + (kq * 16 + h) * SP_STRIDE + t0);
+        x[0] += v.x;
+        x[1] += v.y;
+      }
+      x[0] = t0 < valid ? x[0] * a.scale_log2 : -INFINITY;
+      x[1] = t0 + 1 < valid ? x[1] * a.scale_log2 : -INFINITY;
+      const float mx = warp_max(fmaxf(x[0], x[1]));
       const float m_old = s_m[h], l_old = s_l[h];
       const float m_new = fmaxf(m_old, mx);   // finite: token 0 of every group is valid
       const float alpha = fast_exp2(m_old - m_new);
-      float pr[4], sum = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        pr[e] = fast_exp2(x[e] - m_new);
-        sum += pr[e];
-      }
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      const float p0 = fast_exp2(x[0] - m_new), p1 = fast_exp2(x[1] - m_new);
+      const float sum = warp_sum(p0 + p1);
       __syncwarp();
-      if (tqd == 0) {
+      if (lane == 0) {
         s_m[h] = m_new;
         s_l[h] = l_old * alpha + sum;
         s_alpha[h] = alpha;
       }
-      uint2 packed;
-      packed.x = pack_bf16x2(pr[0], pr[1]);
-      packed.y = pack_bf16x2(pr[2], pr[3]);
-      *reinterpret_cast<uint2*>(smem + OFF_P + h * 128 + (((tqd >> 1) ^ (h & 7)) * 16) + (tqd & 1) * 8) = packed;
+      *reinterpret_cast<uint32_t*>(smem + OFF_P + h * 128 + (((lane >> 2) ^ (h & 7)) * 16) + (lane & 3) * 4) =
+          pack_bf16x2(p0, p1);
     }
     __syncthreads();
 
-    // ---- phase 3: O[:, 64*warp .. +63] = alpha * O + P . c
+    // ---- phase 3: O[:, 32*warp .. +31] = alpha * O + P . c
     {
       const float al0 = s_alpha[g], al1 = s_alpha[g + 8];
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+      for (int n = 0; n < 4; ++n) {
         o[n][0] *= al0;
         o[n][1] *= al0;
         o[n][2] *= al1;
@@ -284,9 +297,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         uint32_t pf[4];
         ldmatrix_x4(pf, sP + rp * 128 + (((2 * kk + chp) ^ (rp & 7)) * 16));
 #pragma unroll
-        for (int pr2 = 0; pr2 < 4; ++pr2) {
+        for (int pr2 = 0; pr2 < 2; ++pr2) {
           uint32_t bf[4];
-          const int chunk = 8 * warp + 2 * pr2 + chp;
+          const int chunk = 4 * warp + 2 * pr2 + chp;
           ldmatrix_x4_trans(bf, ring + kk * BLKB + rp * ROWB + swz72(chunk, rp) * 16);
           const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
           mma_bf16_16816(o[2 * pr2], pf, b0);
@@ -311,8 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         const float i0 = 1.f / s_l[h0], i1 = 1.f / s_l[h1];
         __nv_bfloat16* ob = a.out + static_cast<int64_t>(gr.seq) * H * R;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const int d = 64 * warp + n * 8 + tq * 2;
+        for (int n = 0; n < 4; ++n) {
+          const int d = 32 * warp + n * 8 + tq * 2;
           if (h0 < H) *reinterpret_cast<uint32_t*>(ob + h0 * R + d) = pack_bf16x2(o[n][0] * i0, o[n][1] * i0);
           if (h1 < H) *reinterpret_cast<uint32_t*>(ob + h1 * R + d) = pack_bf16x2(o[n][2] * i1, o[n][3] * i1);
         }
@@ -320,8 +333,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         const int64_t pslot = static_cast<int64_t>(p) * 2 + (seg_first > 0 ? 0 : 1);
         float* po = a.part_o + pslot * H * R;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const int d = 64 * warp + n * 8 + tq * 2;
+        for (int n = 0; n < 4; ++n) {
+          const int d = 32 * warp + n * 8 + tq * 2;
           if (h0 < H) *reinterpret_cast<float2*>(po + h0 * R + d) = make_float2(o[n][0], o[n][1]);
           if (h1 < H) *reinterpret_cast<float2*>(po + h1 * R + d) = make_float2(o[n][2], o[n][3]);
         }
