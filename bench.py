@@ -141,7 +141,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "store"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "store", "engine"],
                     help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
                          "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
     ap.add_argument("--batch", type=int, default=BATCH,
@@ -156,7 +156,8 @@ def main():
         fn = getattr(microbench, args.workload)
         kw = dict(steps=args.steps, warmup=args.warmup)
         if args.batch != BATCH:   # profiling cases: fewer sequences / tokens
-            kw["batch" if args.workload == "mla_decode" else ("total" if args.workload == "prefill" else "tokens")] = args.batch
+            key = {"mla_decode": "batch", "engine": "batch", "prefill": "total", "store": "tokens"}[args.workload]
+            kw[key] = args.batch
         res = fn(**kw)
         peak, kind = hbm_peak()
         if "gbs" in res:

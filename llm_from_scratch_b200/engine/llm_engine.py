@@ -34,6 +34,10 @@ class LLMEngine:
         self.tokenizer = tokenizer
         self.verbose = verbose
         self.stats = dict(prefill_tokens=0, decode_tokens=0, prefill_time=0.0, decode_time=0.0, steps=0)
+        # wall time per step component: host scheduling, model run (incl. metadata upload and the
+        # device-to-host read of the sampled tokens), host post-processing
+        self.timing = dict(schedule_s=0.0, run_prefill_s=0.0, run_decode_s=0.0, postprocess_s=0.0,
+                           prefill_steps=0, decode_steps=0)
 
     def exit(self) -> None:
         self.model_runner.exit()
@@ -53,11 +57,19 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ one step
     def step(self):
+        t0 = time.perf_counter()
         seqs, is_prefill = self.scheduler.schedule()
+        t1 = time.perf_counter()
+        self.timing["schedule_s"] += t1 - t0
         if not seqs:
             return [], 0, is_prefill
         token_ids = self.model_runner.run(seqs, is_prefill)
+        t2 = time.perf_counter()
+        kind = "prefill" if is_prefill else "decode"
+        self.timing[f"run_{kind}_s"] += t2 - t1
+        self.timing[f"{kind}_steps"] += 1
         self.scheduler.postprocess(seqs, token_ids)
+        self.timing["postprocess_s"] += time.perf_counter() - t2
         outputs = [(s.seq_id, s.completion_token_ids) for s in seqs if s.is_finished]
         processed = sum(len(s) for s in seqs) if is_prefill else len(seqs)
         return outputs, processed, is_prefill

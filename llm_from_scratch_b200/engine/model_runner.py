@@ -90,8 +90,6 @@ class ModelRunner:
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_vars: dict[str, torch.Tensor] = {}
         self.allocate_kv_cache()
-        if self.model_config.use_moe:
-            self.enforce_eager = True   # the expert loop reads routing counts on the host
         if not self.enforce_eager:
             self.capture_cudagraph()
 

@@ -81,3 +81,45 @@ def store(steps: int = 50, warmup: int = 5, tokens: int = 262144) -> dict:
     nbytes = tokens * (2 * Hkv * D * 2 * 2 + 8)
     return dict(workload=f"store_kvcache: {tokens} tokens, 8 kv heads x 128, bf16, block-contiguous shuffled slots",
                 ms=ms, tokens=tokens, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, launches_per_call=1)
+
+
+C3_MODEL = dict(vocab_size=32000, context_length=2048, d_model=1024, num_layers=16, num_heads=16, num_kv_heads=4,
+                d_ff=704, attention_type="GQA", use_moe=True, n_routed_experts=16, num_experts_per_tok=2,
+                n_shared_experts=1)
+
+
+def engine(steps: int = 0, warmup: int = 0, batch: int = 512, device: str = "cuda:0") -> dict:
+    """End-to-end continuous batching, GQA+MoE decoder (d_model 1024, 16 layers, 16/4 heads, head_dim 64,
+    16 experts top-2 + shared, d_ff 704, vocab 32000), bf16, random init: ``batch`` requests present at
+    t = 0, prompts uniform [64,1024], outputs geometric(mean 256) capped at 1024, max 256 sequences and
+    8192 batched tokens per step, KV block 16.  ``steps`` / ``warmup`` are unused (the job runs once)."""
+    import itertools
+    import time
+
+    from .engine import SamplingParams, Sequence
+    from .engine.llm_engine import LLMEngine
+    from .engine.replicas import serve_shard
+    from .workloads import c3_requests
+    prompts, outs, _ = c3_requests(batch)
+    Sequence.counter = itertools.count()
+    cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256, max_num_batched_tokens=8192,
+               max_cached_blocks=40000, eos=-1, device=device, max_model_length=2048, seed=0)
+    t0 = time.perf_counter()
+    eng = LLMEngine(cfg)
+    build_s = time.perf_counter() - t0
+    shard = [(p, SamplingParams(temperature=0.0, max_tokens=int(n) + 1, ignore_eos=True)) for p, n in zip(prompts, outs)]
+    torch.cuda.synchronize()
+    rep = serve_shard(eng, shard)
+    torch.cuda.synchronize()
+    ops.check_status()
+    gen = sum(len(t) for t in rep.token_ids)
+    assert gen == int(outs.sum()), (gen, int(outs.sum()))
+    graphs = bool(eng.model_runner.graphs)
+    timing = dict(eng.timing)
+    eng.exit()
+    return dict(workload=f"continuous batching GQA+MoE bf16: {batch} requests at t=0, prompts U[64,1024], outputs "
+                         "geometric(256) cap 1024, max 256 seqs / 8192 tokens per step",
+                requests=batch, generated_tokens=gen, prompt_tokens=int(sum(len(p) for p in prompts)),
+                wall_s=rep.wall_s, steps=rep.steps, output_tokens_per_s=gen / rep.wall_s,
+                total_tokens_per_s=(gen + sum(len(p) for p in prompts)) / rep.wall_s, engine_build_s=build_s,
+                cuda_graphs=graphs, timing=timing)

@@ -96,8 +96,20 @@ class MLP(nn.Module):
 
 
 class MoE(nn.Module):
-    """Routing of Gate.forward (moe.py:45-90) and the expert loop of MOE.moe_infer (moe.py:288-341):
-    experts visited in ascending order, outputs accumulated in the activation dtype."""
+    """Routing of Gate.forward (moe.py:45-90) and the expert mixture of MOE.moe_infer (moe.py:288-341).
+
+    Two evaluation orders of the same sum  y[t] = sum_k w[t,k] * expert_{idx[t,k]}(x[t]) (+ shared):
+
+    * ``forward_sorted`` — the reference's: tokens grouped by expert, experts visited in ascending
+      order, each output scaled and accumulated in the activation dtype.  It reads the per-expert
+      counts on the host (one sync per layer, as moe.py:307) and is used for large (prefill) batches.
+    * ``forward_dense`` — for small (decode) batches: every expert is applied to every token with
+      three batched GEMMs over the stacked expert weights and the routing weights select the two
+      that count.  No host sync and a fixed launch sequence, so the decode step can be captured in
+      a CUDA graph; at decode sizes the layer is bound by reading the expert weights either way.
+    """
+
+    dense_max_tokens = 512
 
     def __init__(self, p: _Params, prefix: str, cfg: ModelConfig):
         super().__init__()
@@ -105,6 +117,14 @@ class MoE(nn.Module):
         self.gate_w = p.w[prefix + ".gate.weight"].to(p.device, p.dtype).contiguous()
         self.gate_bias = p.f32(prefix + ".gate.expert_bias")
         self.experts = nn.ModuleList([MLP(p, f"{prefix}.experts.{e}") for e in range(self.E)])
+        # stacked copies share storage with the per-expert modules
+        self.w13 = torch.stack([m.w13 for m in self.experts])      # [E, 2*d_ff, d]
+        self.b13 = torch.stack([m.b13 for m in self.experts])      # [E, 2*d_ff]
+        self.w2 = torch.stack([m.w2 for m in self.experts])        # [E, d, d_ff]
+        self.b2 = torch.stack([m.b2 for m in self.experts])        # [E, d]
+        for e, m in enumerate(self.experts):
+            m.w13, m.b13, m.w2, m.b2 = self.w13[e], self.b13[e], self.w2[e], self.b2[e]
+        self.d_ff = self.w2.shape[2]
         self.shared = MLP(p, prefix + ".shared_expert") if cfg.n_shared_experts > 0 else None
 
     def route(self, x):
@@ -119,11 +139,20 @@ class MoE(nn.Module):
 
     def forward(self, x):
         idx, wts = self.route(x)
+        if x.shape[0] <= self.dense_max_tokens:
+            out = self.forward_dense(x, idx, wts)
+        else:
+            out = self.forward_sorted(x, idx, wts)
+        if self.shared is not None:
+            out = out + self.shared(x)
+        return out
+
+    def forward_sorted(self, x, idx, wts):
         flat_idx = idx.reshape(-1)
         flat_w = wts.reshape(-1, 1).to(x.dtype)
         out = torch.zeros_like(x)
         order = flat_idx.argsort()
-        counts = flat_idx.bincount(minlength=self.E).tolist()   # one host sync per layer, as moe.py:307
+        counts = flat_idx.bincount(minlength=self.E).tolist()
         tok = order // self.K
         lo = 0
         for e in range(self.E):
@@ -133,9 +162,16 @@ class MoE(nn.Module):
                 y = self.experts[e](x[t]) * flat_w[order[lo:hi]]
                 out.index_add_(0, t, y)
             lo = hi
-        if self.shared is not None:
-            out = out + self.shared(x)
         return out
+
+    def forward_dense(self, x, idx, wts):
+        T = x.shape[0]
+        xe = x.unsqueeze(0).expand(self.E, T, x.shape[1])
+        h = torch.baddbmm(self.b13.unsqueeze(1), xe, self.w13.transpose(1, 2))          # [E, T, 2*d_ff]
+        act = F.silu(h[..., :self.d_ff]) * h[..., self.d_ff:]
+        y = torch.baddbmm(self.b2.unsqueeze(1), act, self.w2.transpose(1, 2))           # [E, T, d]
+        dense_w = torch.zeros(T, self.E, dtype=x.dtype, device=x.device).scatter_(1, idx, wts.to(x.dtype))
+        return torch.einsum("etd,te->td", y, dense_w)
 
 
 class GQAAttention(nn.Module):

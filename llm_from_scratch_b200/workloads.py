@@ -114,3 +114,16 @@ def c4_decode_case(batch: int = 240, lo: int = 512, hi: int = 16384, block_size:
     rng = np.random.default_rng(seed)
     lens = rng.integers(lo, hi + 1, size=batch).astype(np.int64)
     return deal_blocks(lens, block_size, rng, pad_blocks=8)
+
+
+def c3_requests(num_requests: int = 2048, vocab: int = 32000, seed: int = 3, prompt_lo: int = 64,
+                prompt_hi: int = 1024, mean_out: int = 256, max_out: int = 1024, rate: float | None = None):
+    """Continuous-batching request stream: prompt lengths uniform in [lo, hi], output lengths
+    geometric with the given mean capped at ``max_out``, token ids uniform; arrivals Poisson with
+    ``rate`` requests/s (``None`` = all present at t = 0).  Returns (prompts, out_lens, arrivals)."""
+    rng = np.random.default_rng(seed)
+    plens = rng.integers(prompt_lo, prompt_hi + 1, size=num_requests)
+    outs = np.minimum(rng.geometric(1.0 / mean_out, size=num_requests), max_out).astype(np.int64)
+    prompts = [rng.integers(0, vocab, size=int(n)).tolist() for n in plens]
+    arrivals = np.zeros(num_requests) if rate is None else np.cumsum(rng.exponential(1.0 / rate, size=num_requests))
+    return prompts, outs, arrivals

@@ -85,6 +85,25 @@ def test_small_moe_decoders_fp32(name, att):
     assert np.abs(torch.stack(last).numpy() - z["last_logits"]).max() <= 1e-3
 
 
+def test_moe_dense_and_sorted_paths_agree_and_decode_replays_from_graphs():
+    """The two evaluation orders of the expert mixture give the same layer output, and a MoE decoder
+    whose decode steps are replayed from CUDA graphs produces the eager streams."""
+    from llm_from_scratch_b200.model.transformer import MoE
+    z = load("moe_model.npz")
+    cfg = dict(vocab_size=512, context_length=128, d_model=128, num_layers=2, num_heads=8, d_ff=96, use_moe=True,
+               n_routed_experts=4, num_experts_per_tok=2, n_shared_experts=1, attention_type="GQA", num_kv_heads=2)
+    eng = make_engine(cfg, weights_of(z), eager=False)
+    assert eng.model_runner.graphs
+    streams, last = greedy_run(eng, prompts_of(z), 12)
+    assert streams == z["streams"].tolist()
+    moe = eng.model_runner.model.layers[0].ffn
+    assert isinstance(moe, MoE)
+    x = torch.randn(300, 128, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    idx, wts = moe.route(x)
+    a, b = moe.forward_dense(x, idx, wts), moe.forward_sorted(x, idx, wts)
+    assert (a - b).abs().max().item() <= 1e-5
+
+
 def test_small_moe_decoder_bf16_tracks_reference_autocast():
     """bf16 is compared by tolerance: logits of the first decode-free step (the prefill) against the
     reference modules under CPU autocast, and the fraction of matching greedy tokens."""
