@@ -49,6 +49,7 @@ extern "C" {
 #define B200_ERR_BOUNDS (-6)       /* device-side: block id or slot outside the pool         */
 #define B200_ERR_NO_DEVICE (-7)    /* no usable CUDA device                                  */
 #define B200_ERR_TOO_LARGE (-8)    /* scratch needed exceeds a fixed built-in capacity       */
+#define B200_ERR_TIMEOUT (-9)      /* device-side: a bounded barrier wait gave up            */
 
 int b200_abi_version(void);
 const char* b200_strerror(int code);

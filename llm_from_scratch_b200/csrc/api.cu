@@ -136,6 +136,7 @@ const char* b200_strerror(int code) {
     case B200_ERR_BOUNDS: return "block id or slot outside the pool (access skipped)";
     case B200_ERR_NO_DEVICE: return "no usable CUDA device";
     case B200_ERR_TOO_LARGE: return "problem needs more scratch than the built-in static array holds";
+    case B200_ERR_TIMEOUT: return "a bounded device-side barrier wait gave up (kernel aborted cleanly)";
     default: return "unknown error";
   }
 }

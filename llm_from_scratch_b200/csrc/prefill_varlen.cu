@@ -111,6 +111,13 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        const int32_t* bt, int64_t bt_stride, int bs, int64_t num_blocks,
                        int32_t* status, cudaStream_t s);
 
+// tcgen05 path (prefill_umma.cu): head_dim 128, even group size
+int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
+                        int64_t k_stride, int64_t v_stride, const int32_t* cu_q, const int32_t* cu_k,
+                        int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv, float scale,
+                        const void* kc, const void* vc, const int32_t* bt, int64_t bt_stride, int bs,
+                        int64_t num_blocks, int32_t* status, cudaStream_t s);
+
 }  // namespace b200
 
 extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
@@ -140,6 +147,11 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   if (dtype == B200_DTYPE_BF16) {
+    const int rcu = prefill_umma_launch(q, k, v, out, q_token_stride, k_token_stride, v_token_stride,
+                                        cu_seqlens_q, cu_seqlens_k, num_seqs, max_seqlen_q, num_q_heads,
+                                        num_kv_heads, head_dim_qk, head_dim_v, scale, k_cache, v_cache,
+                                        block_tables, bt_stride, block_size, num_blocks, status, s);
+    if (rcu != B200_ERR_UNSUPPORTED) return rcu;
     const int rc = prefill_mma_launch(q, k, v, out, q_token_stride, k_token_stride,
                                       v_token_stride, cu_seqlens_q, cu_seqlens_k, num_seqs,
                                       max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk,

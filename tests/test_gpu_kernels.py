@@ -274,6 +274,36 @@ def test_prefill_varlen_with_cached_prefix_through_block_tables(dtype):
     assert_close(got, want, dtype)
 
 
+def test_prefill_varlen_head_dim_128_cached_prefix_and_many_tiles():
+    """head_dim 128 with an even group size takes the tcgen05 path: packed and paged K/V, lengths
+    around the 128-row tile boundaries, several KV tiles per query tile."""
+    ops, orc = _ops(), _oracle()
+    Hq, Hkv, D, bs = 8, 2, 128, 16
+    k_lens = [127, 128, 129, 300, 1, 515, 256]
+    cached = [0, 64, 16, 160, 0, 400, 128]
+    q_lens = [a - b for a, b in zip(k_lens, cached)]
+    case = deal_blocks(k_lens, bs, np.random.default_rng(13), pad_blocks=1)
+    kc = _randn((case.num_blocks, bs, Hkv, D), 31, torch.bfloat16)
+    vc = _randn((case.num_blocks, bs, Hkv, D), 32, torch.bfloat16)
+    q = _randn((sum(q_lens), Hq, D), 33, torch.bfloat16)
+    cu_q = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    cu_k = torch.tensor(np.concatenate([[0], np.cumsum(k_lens)]), dtype=torch.int32)
+    scale = D ** -0.5
+    want = orc.prefill_varlen(q, None, None, cu_q, cu_k, scale, kc, vc, case.block_tables)
+    got = ops.prefill_varlen(q.cuda(), None, None, cu_q.cuda(), cu_k.cuda(), max(q_lens), max(k_lens), scale,
+                             kc.cuda(), vc.cuda(), torch.from_numpy(case.block_tables).cuda())
+    ops.check_status()
+    assert_close(got, want, torch.bfloat16)
+    # scores with a large spread exercise the lazy rescaling of the output accumulator
+    lens = [400, 130]
+    q2, k2, v2, cu = _prefill_inputs(lens, Hq, Hkv, D, D, torch.bfloat16, seed=91)
+    k2 = (k2.float() * torch.linspace(0.2, 6.0, sum(lens)).view(-1, 1, 1)).to(torch.bfloat16)
+    want = orc.prefill_varlen(q2, k2, v2, cu, cu, scale)
+    got = ops.prefill_varlen(q2.cuda(), k2.cuda(), v2.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), scale)
+    ops.check_status()
+    assert_close(got, want, torch.bfloat16)
+
+
 def test_prefill_varlen_mla_head_dims_192_128():
     ops = _ops()
     lens = [33, 70, 5]
