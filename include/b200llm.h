@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 1
+#define B200_ABI_VERSION 2
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -146,9 +146,12 @@ int b200_paged_decode_gqa_static(const void* q, const void* k_cache, const void*
  *       read from k_cache/v_cache through block_tables [num_seqs, bt_stride] and k/v are ignored
  *       (the caller has already stored the new tokens with b200_store_kvcache);
  *   out [total_q, Hq, Dv] contiguous.
+ *   total_q_tokens / total_k_tokens are the row counts of q and of k/v (= cu_seqlens[num_seqs],
+ *   which the host knows from its tensors): they bound the TMA tensor maps built over q/k/v.
  * ------------------------------------------------------------------------------------------- */
 int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                         int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                        int64_t total_q_tokens, int64_t total_k_tokens,
                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                         int32_t num_seqs, int32_t max_seqlen_q, int32_t max_seqlen_k,
                         int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,

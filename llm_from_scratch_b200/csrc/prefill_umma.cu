@@ -6,8 +6,11 @@
 // the 128x128 fp32 output accumulator O; the bf16 probabilities P overwrite the first 64 columns
 // of S and are consumed from tensor memory as the A operand of O += P.V.
 //
-//   warp 0      K loader (+ Q of head A)   16-byte cp.async into the 128-byte-swizzled tile layout
-//   warp 1      V loader (+ Q of head B)
+//   warp 0      K producer (+ both Q tiles): one thread issuing TMA tile copies (cp.async.bulk.tensor,
+//               128-byte swizzle, completion counted on an mbarrier) for packed k/v; for the paged
+//               pool the whole warp stages rows with 16-byte cp.async instead, because rows past the
+//               end of a context must be zero-filled rather than read
+//   warp 1      V producer, likewise
 //   warp 2      tensor-memory allocation; lane 0 issues every tcgen05.mma
 //   warps 4-7   softmax of problem A: one thread per query row, so row max / row sum need no shuffles
 //   warps 8-11  softmax of problem B
@@ -21,6 +24,9 @@
 //
 // Keys/values come from the packed k/v tensors or, with a cached prefix, from the paged pool through
 // the block table (mask bottom-right aligned).  Tiles above the causal diagonal are never loaded.
+#include <cuda.h>
+#include <string.h>
+
 #include "umma.cuh"
 
 namespace b200 {
@@ -64,7 +70,9 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c16) {
 }
 
 template <bool PAGED>
-__global__ void __launch_bounds__(kThreads, 1) prefill_umma_kernel(const UmmaArgs a) {
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
+                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sb = smem_u32(smem);
@@ -90,10 +98,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_umma_kernel(const UmmaArg
   const int n = (kmax + BN - 1) / BN;            // KV tiles; >= 1
 
   if (tid == 0) {
-    umma::mbar_init(bar(Q_FULL), 64);
+    // paged: every lane of a producer warp arrives; TMA: one arrival + the transferred byte count
+    umma::mbar_init(bar(Q_FULL), PAGED ? 64 : 1);
     for (int s = 0; s < 2; ++s) {
-      umma::mbar_init(bar(K_FULL + s), 32);
-      umma::mbar_init(bar(V_FULL + s), 32);
+      umma::mbar_init(bar(K_FULL + s), PAGED ? 32 : 1);
+      umma::mbar_init(bar(V_FULL + s), PAGED ? 32 : 1);
       umma::mbar_init(bar(K_EMPTY + s), 1);
       umma::mbar_init(bar(V_EMPTY + s), 1);
       umma::mbar_init(bar(S_FULL + s), 1);
@@ -120,8 +129,31 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_umma_kernel(const UmmaArg
     break;                                                           \
   }
 
-  if (warp < 2) {
-    // =============================== loaders ===============================
+  if (!PAGED && warp < 2) {
+    // =============================== TMA producers ===============================
+    if (lane == 0) {
+      const bool is_k = warp == 0;
+      if (is_k) {
+        umma::mbar_expect_tx(bar(Q_FULL), 2 * TILE_BYTES);
+        for (int x = 0; x < 2; ++x)
+          for (int h = 0; h < 2; ++h)
+            umma::tma_load_3d(sb + (x ? OFF_QB : OFF_QA) + h * HALF_BYTES, &tm_q, h * 64, x ? head_b : head_a,
+                              q0 + m0, bar(Q_FULL));
+      }
+      const int full0 = is_k ? K_FULL : V_FULL, empty0 = is_k ? K_EMPTY : V_EMPTY;
+      const uint32_t stage0 = sb + (is_k ? OFF_K : OFF_V);
+      const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
+      for (int j = 0; j < n; ++j) {
+        const int st = j & 1;
+        if (j >= 2) WAIT_OR_ABORT(empty0 + st, ((j >> 1) - 1) & 1)
+        umma::mbar_expect_tx(bar(full0 + st), TILE_BYTES);
+        for (int h = 0; h < 2; ++h)
+          umma::tma_load_3d(stage0 + st * TILE_BYTES + h * HALF_BYTES, tm, h * 64, kvh, k0 + j * BN,
+                            bar(full0 + st));
+      }
+    }
+  } else if (warp < 2) {
+    // =============================== cp.async producers (paged pool) ===============================
     const bool is_k = warp == 0;
     const int head = is_k ? head_a : head_b;
     // Q tile of this warp's head
@@ -336,9 +368,48 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_umma_kernel(const UmmaArg
 
 }  // namespace
 
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn tensor_map_encoder() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// [tokens, heads, 128] bf16 with a free token stride, seen as (d, head, token); one box is 64 columns
+// of one head for 128 consecutive tokens, written to shared memory with the 128-byte swizzle.
+bool make_map(CUtensorMap* m, const void* base, int64_t tokens, int heads, int64_t token_stride) {
+  EncodeFn enc = tensor_map_encoder();
+  if (enc == nullptr || tokens <= 0) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads),
+                              static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(token_stride) * 2};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(BN)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
 int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
-                        int64_t k_stride, int64_t v_stride, const int32_t* cu_q, const int32_t* cu_k,
-                        int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv, float scale,
+                        int64_t k_stride, int64_t v_stride, int64_t total_q, int64_t total_k,
+                        const int32_t* cu_q, const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv, float scale,
                         const void* kc, const void* vc, const int32_t* bt, int64_t bt_stride, int bs,
                         int64_t num_blocks, int32_t* status, cudaStream_t s) {
   const bool paged = bt != nullptr;
@@ -379,8 +450,18 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
       return B200_ERR_LAUNCH;
     configured[dev][paged] = true;
   }
+  CUtensorMap tm_q, tm_k, tm_v;
+  memset(&tm_q, 0, sizeof(tm_q));
+  memset(&tm_k, 0, sizeof(tm_k));
+  memset(&tm_v, 0, sizeof(tm_v));
+  if (!paged) {
+    // the token stride must be a multiple of 16 bytes for TMA (checked above)
+    if (!make_map(&tm_q, q, total_q, Hq, q_stride) || !make_map(&tm_k, k, total_k, Hkv, k_stride) ||
+        !make_map(&tm_v, v, total_k, Hkv, v_stride))
+      return B200_ERR_UNSUPPORTED;   // falls back to the mma.sync kernel
+  }
   dim3 grid(Hq / 2, num_seqs, ntiles);
-  kern<<<grid, kThreads, SMEM_BYTES, s>>>(a);
+  kern<<<grid, kThreads, SMEM_BYTES, s>>>(a, tm_q, tm_k, tm_v);
   return launch_result();
 }
 

@@ -113,7 +113,8 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
 
 // tcgen05 path (prefill_umma.cu): head_dim 128, even group size
 int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
-                        int64_t k_stride, int64_t v_stride, const int32_t* cu_q, const int32_t* cu_k,
+                        int64_t k_stride, int64_t v_stride, int64_t total_q, int64_t total_k,
+                        const int32_t* cu_q, const int32_t* cu_k,
                         int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv, float scale,
                         const void* kc, const void* vc, const int32_t* bt, int64_t bt_stride, int bs,
                         int64_t num_blocks, int32_t* status, cudaStream_t s);
@@ -122,7 +123,8 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
 
 extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                                    int64_t q_token_stride, int64_t k_token_stride,
-                                   int64_t v_token_stride, const int32_t* cu_seqlens_q,
+                                   int64_t v_token_stride, int64_t total_q_tokens,
+                                   int64_t total_k_tokens, const int32_t* cu_seqlens_q,
                                    const int32_t* cu_seqlens_k, int32_t num_seqs,
                                    int32_t max_seqlen_q, int32_t max_seqlen_k,
                                    int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
@@ -136,7 +138,8 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
     return B200_ERR_ARG;
   if (num_q_heads % num_kv_heads != 0) return B200_ERR_ARG;
   if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
-  if (num_seqs == 0 || max_seqlen_q == 0) return B200_OK;
+  if (total_q_tokens < 0 || total_k_tokens < 0) return B200_ERR_ARG;
+  if (num_seqs == 0 || max_seqlen_q == 0 || total_q_tokens == 0) return B200_OK;
   if (!q || !out || !cu_seqlens_q || !cu_seqlens_k) return B200_ERR_ARG;
   if (block_tables == nullptr) {
     if (!k || !v) return B200_ERR_ARG;
@@ -148,7 +151,7 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
 
   if (dtype == B200_DTYPE_BF16) {
     const int rcu = prefill_umma_launch(q, k, v, out, q_token_stride, k_token_stride, v_token_stride,
-                                        cu_seqlens_q, cu_seqlens_k, num_seqs, max_seqlen_q, num_q_heads,
+                                        total_q_tokens, total_k_tokens, cu_seqlens_q, cu_seqlens_k, num_seqs, max_seqlen_q, num_q_heads,
                                         num_kv_heads, head_dim_qk, head_dim_v, scale, k_cache, v_cache,
                                         block_tables, bt_stride, block_size, num_blocks, status, s);
     if (rcu != B200_ERR_UNSUPPORTED) return rcu;

@@ -127,6 +127,23 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory");
 }
+// The executing thread arrives once and announces `bytes` of asynchronous copies that will complete
+// on this barrier.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
+}
+// One TMA box of a rank-3 tensor map into this CTA's own shared memory; the copied bytes
+// are counted on `mbar`.  c0 is the innermost coordinate and must keep c0 * element size a multiple
+// of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
+                                            uint32_t mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], "
+      "[%5];\n" ::"r"(dst_smem),
+      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(c0), "r"(c1), "r"(c2), "r"(mbar)
+      : "memory");
+}
+
 // Waits for the phase with the given parity to complete.  Bounded: gives up after `limit` polls
 // (each poll may itself suspend for a short hardware-defined time) or as soon as `*abort_flag`
 // (shared memory) is set by another thread, and returns false.

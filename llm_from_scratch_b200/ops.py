@@ -179,6 +179,7 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
         kp, vp, ks, vs = k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0)
         kcp = vcp = btp = 0
         bts = bs = nb = 0
+        total_k = k.shape[0]
     else:
         if k_cache is None or v_cache is None:
             raise ValueError("paged prefill needs k_cache and v_cache")
@@ -192,12 +193,13 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
             raise ValueError("caches must be contiguous")
         kp = vp = 0
         ks = vs = 0
+        total_k = 0
         kcp, vcp, btp, bts = k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(), block_tables.stride(0)
     if out is None:
         out = torch.empty((Tq, Hq, Dv), dtype=q.dtype, device=q.device)
     elif out.shape != (Tq, Hq, Dv) or out.dtype != q.dtype or not out.is_contiguous():
         raise ValueError("out must be a contiguous [Tq, Hq, Dv] tensor")
-    check(lib.b200_prefill_varlen(q.data_ptr(), kp, vp, out.data_ptr(), q.stride(0), ks, vs,
+    check(lib.b200_prefill_varlen(q.data_ptr(), kp, vp, out.data_ptr(), q.stride(0), ks, vs, Tq, total_k,
                                   cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
                                   int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, Dqk, Dv,
                                   float(scale), kcp, vcp, btp, bts, bs, nb, _dt(q),

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} declared in b200llm.h but not exported"
     assert set(_lib.SIGNATURES) == set(declared_functions())
-    assert _lib.lib.b200_abi_version() == 1
+    assert _lib.lib.b200_abi_version() == 2
     assert _lib.lib.b200_strerror(-3) == b"unsupported shape or dtype"
 
 
@@ -39,7 +39,7 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.b200_store_kvcache(None, None, 0, 0, None, None, None, -1, 1, 1, 0, 0, None, None) == -1
     assert lib.b200_paged_decode_gqa(None, None, None, None, None, 0, None, 1, 7, 2, 64, 16, 1, 1.0,
                                      None, 0, 1, None, None) == -1  # 7 heads not divisible by 2
-    assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, None, None, 1, 1, 1, 4, 4, 64, 64,
+    assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, 1, 1, None, None, 1, 1, 1, 4, 4, 64, 64,
                                    1.0, None, None, None, 0, 0, 0, 5, None, None) == -3  # bad dtype
     assert lib.b200_mla_decode(None, None, None, None, None, 0, None, 1, 16, 512, 64, 16, 1, 1.0,
                                None, 0, 1, None, None) == -1  # bt_stride 0
