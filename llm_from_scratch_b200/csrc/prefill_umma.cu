@@ -279,18 +279,32 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
       umma::fence_after_sync();
       const int n0 = j * BN;
       const bool masked = n0 + BN - 1 > lim;
-      // pass 1: row maximum of the scaled scores
-      float mx = -INFINITY;
+      // tensor-memory loads are warp-collective, so the masked / unmasked variants are chosen per warp
+      const bool warp_masked = __any_sync(0xffffffffu, masked);
+      // pass 1: row maximum of the raw scores (the scale is positive, so it commutes with max)
+      float mx;
+      {
+        float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        umma::tmem_ld32(tSx + c * 32, r);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          umma::tmem_ld32(tSx + c * 32, r);
+          if (warp_masked) {
+            const int kb = n0 + c * 32;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float s = __uint_as_float(r[e]) * a.scale_log2;
-          if (masked && n0 + c * 32 + e > lim) s = -INFINITY;
-          mx = fmaxf(mx, s);
+            for (int e = 0; e < 32; e += 2) {
+              mx0 = fmaxf(mx0, kb + e > lim ? -INFINITY : __uint_as_float(r[e]));
+              mx1 = fmaxf(mx1, kb + e + 1 > lim ? -INFINITY : __uint_as_float(r[e + 1]));
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              mx0 = fmaxf(mx0, __uint_as_float(r[e]));
+              mx1 = fmaxf(mx1, __uint_as_float(r[e + 1]));
+            }
+          }
         }
+        mx = fmaxf(mx0, mx1) * a.scale_log2;
       }
       // lazy rescale: move the reference maximum only when it grows by more than the threshold
       const bool need = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
@@ -311,25 +325,37 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
         }
         m_ref = m_new;
       }
-      // pass 2: P = 2^(s - m_ref) as bf16 into the first 64 columns of S, row sum in fp32
+      // pass 2: P = 2^(s * scale - m_ref) as bf16 into the first 64 columns of S, row sum in fp32;
+      // the multiply-subtract and the row sum run two elements per instruction
       const float sub = m_ref == -INFINITY ? 0.f : m_ref;
+      const uint64_t scale2 = umma::pack_f32x2(a.scale_log2, a.scale_log2);
+      const uint64_t nsub2 = umma::pack_f32x2(-sub, -sub);
+      uint64_t lsum2 = umma::pack_f32x2(0.f, 0.f);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32], pk[16];
         umma::tmem_ld32(tSx + c * 32, r);
+        const int kb = n0 + c * 32;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float s0 = __uint_as_float(r[e]) * a.scale_log2 - sub;
-          float s1 = __uint_as_float(r[e + 1]) * a.scale_log2 - sub;
-          if (masked) {
-            if (n0 + c * 32 + e > lim) s0 = -INFINITY;
-            if (n0 + c * 32 + e + 1 > lim) s1 = -INFINITY;
+          float s0, s1;
+          umma::unpack_f32x2(
+              umma::fma_f32x2(umma::pack_f32x2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), scale2, nsub2),
+              s0, s1);
+          if (warp_masked) {
+            if (kb + e > lim) s0 = -INFINITY;
+            if (kb + e + 1 > lim) s1 = -INFINITY;
           }
           const float p0 = fast_exp2(s0), p1 = fast_exp2(s1);
-          l += p0 + p1;
+          lsum2 = umma::add_f32x2(lsum2, umma::pack_f32x2(p0, p1));
           pk[e >> 1] = pack_bf16x2(p0, p1);
         }
         umma::tmem_st16(tSx + c * 16, pk);
+      }
+      {
+        float la, lb;
+        umma::unpack_f32x2(lsum2, la, lb);
+        l += la + lb;
       }
       umma::tmem_wait_st();
       umma::fence_before_sync();
@@ -414,6 +440,7 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
                         int64_t num_blocks, int32_t* status, cudaStream_t s) {
   const bool paged = bt != nullptr;
   if (Dqk != D || Dv != D || Hkv <= 0 || Hq % Hkv != 0 || ((Hq / Hkv) & 1)) return B200_ERR_UNSUPPORTED;
+  if (!(scale > 0.f)) return B200_ERR_UNSUPPORTED;   // the row maximum is taken before scaling
   const int ntiles = (max_seqlen_q + BM - 1) / BM;
   if (num_seqs > 65535 || ntiles > 65535) return B200_ERR_UNSUPPORTED;
   auto al = [](const void* p, int64_t stride) { return aligned16(p) && (stride * 2) % 16 == 0; };
