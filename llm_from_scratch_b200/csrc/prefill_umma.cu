@@ -281,14 +281,12 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
       const bool masked = n0 + BN - 1 > lim;
       // tensor-memory loads are warp-collective, so the masked / unmasked variants are chosen per warp
       const bool warp_masked = __any_sync(0xffffffffu, masked);
-      // pass 1: row maximum of the raw scores (the scale is positive, so it commutes with max)
+      // pass 1: row maximum of the raw scores (the scale is positive, so it commutes with max).
+      // Chunks of 32 columns are double-buffered: the next load is in flight while one is reduced.
       float mx;
       {
         float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          umma::tmem_ld32(tSx + c * 32, r);
+        auto reduce = [&](const uint32_t (&r)[32], int c) {
           if (warp_masked) {
             const int kb = n0 + c * 32;
 #pragma unroll
@@ -303,7 +301,19 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
               mx1 = fmaxf(mx1, __uint_as_float(r[e + 1]));
             }
           }
-        }
+        };
+        uint32_t ra[32], rb[32];
+        umma::tmem_ld32(tSx, ra);
+        umma::tmem_ld32_issue(tSx + 32, rb);
+        reduce(ra, 0);
+        umma::tmem_ld32_wait(rb);
+        umma::tmem_ld32_issue(tSx + 64, ra);
+        reduce(rb, 1);
+        umma::tmem_ld32_wait(ra);
+        umma::tmem_ld32_issue(tSx + 96, rb);
+        reduce(ra, 2);
+        umma::tmem_ld32_wait(rb);
+        reduce(rb, 3);
         mx = fmaxf(mx0, mx1) * a.scale_log2;
       }
       // lazy rescale: move the reference maximum only when it grows by more than the threshold
@@ -331,10 +341,8 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
       const uint64_t scale2 = umma::pack_f32x2(a.scale_log2, a.scale_log2);
       const uint64_t nsub2 = umma::pack_f32x2(-sub, -sub);
       uint64_t lsum2 = umma::pack_f32x2(0.f, 0.f);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], pk[16];
-        umma::tmem_ld32(tSx + c * 32, r);
+      auto emit = [&](const uint32_t (&r)[32], int c) {
+        uint32_t pk[16];
         const int kb = n0 + c * 32;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -351,6 +359,20 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
           pk[e >> 1] = pack_bf16x2(p0, p1);
         }
         umma::tmem_st16(tSx + c * 16, pk);
+      };
+      {
+        uint32_t ra[32], rb[32];
+        umma::tmem_ld32(tSx, ra);
+        umma::tmem_ld32_issue(tSx + 32, rb);
+        emit(ra, 0);
+        umma::tmem_ld32_wait(rb);
+        umma::tmem_ld32_issue(tSx + 64, ra);
+        emit(rb, 1);
+        umma::tmem_ld32_wait(ra);
+        umma::tmem_ld32_issue(tSx + 96, rb);
+        emit(ra, 2);
+        umma::tmem_ld32_wait(rb);
+        emit(rb, 3);
       }
       {
         float la, lb;
