@@ -144,6 +144,21 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return d;
 }
 
+// 2^x for x <= ~8 on the FMA/ALU pipes instead of the special-function unit (which sustains only 16
+// results per clock per SM and is the scarce unit of a softmax): x = j + f with j = round(x),
+// f in [-0.5, 0.5]; 2^f by a degree-4 polynomial (relative error < 1e-4, far below bf16 resolution);
+// 2^j by adding j to the exponent field.  Inputs below -126 (masked scores) give ~1e-38.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;             // 1.5 * 2^23: the low mantissa bits now hold round(x)
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
+  p = fmaf(f, p, 0.2402265070f);
+  p = fmaf(f, p, 0.6931471806f);
+  p = fmaf(f, p, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 // ---- mbarrier ---------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbar), "r"(count) : "memory");
