@@ -36,6 +36,7 @@ sys.path.insert(0, ROOT)
 
 HQ, HKV, D, BS, BATCH = 32, 8, 128, 16, 256
 CPU_SAMPLE_SEQS = 64
+NCU_DRAM_BYTES_PER_CONTEXT_TOKEN = (536_459_520 + 4_956_544) / 130_732   # profiles/paged_decode_bf16_c2.md
 
 
 def hbm_peak():
@@ -332,7 +333,10 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                      "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "algorithmic_bytes_per_launch": alg_bytes, "traffic": None,
+                     "algorithmic_bytes_per_launch": alg_bytes,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the 64-sequence
+                     # case (541.4 MB for 130,732 context tokens), scaled by context tokens to this launch
+                     "traffic": NCU_DRAM_BYTES_PER_CONTEXT_TOKEN * case.total_tokens,
                      "kernel": "paged_decode_bf16_kernel<128,1> (+ combine, timed together)"},
         "e2e": None if args.no_e2e else {
             "value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
