@@ -185,6 +185,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
+        torch.set_num_threads(os.cpu_count() or 1)   # torchrun pins OMP_NUM_THREADS=1; use every host core
         # The reference's CPU arithmetic for this step (gather + fp32 softmax attention) on a
         # bounded sample of the same workload; inputs synthesised on the host.
         g = torch.Generator().manual_seed(1)
@@ -345,6 +346,7 @@ def main():
         "clocks": sampler.summary(),
     }
     if n_gpus == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
         nseq = CPU_SAMPLE_SEQS
         sample = cpu_oracle_sample(case, q.cpu(), kc, vc, nseq)
         time_cpu_oracle(sample)  # warm-up
