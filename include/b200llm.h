@@ -176,6 +176,34 @@ int b200_mla_decode(const void* q_abs, const void* q_rope, const void* latent_ca
                     int64_t num_blocks, float scale, void* workspace, size_t workspace_bytes,
                     int32_t dtype, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Residual-stream RMSNorm with the reference's optional fused residual add (model/utils.py:54-67):
+ *   xf = float(x) [+ float(residual)];  y = (weight * xf * rsqrt(mean(xf^2) + eps)) in x's dtype;
+ *   residual_out = xf in x's dtype (may be NULL).  x, y, residual_out: [num_rows, dim] contiguous in
+ *   `dtype`; residual (may be NULL) in `residual_dtype`; weight fp32 [dim].
+ * ------------------------------------------------------------------------------------------- */
+int b200_add_rmsnorm(const void* x, const void* residual, const float* weight, void* y,
+                     void* residual_out, int64_t num_rows, int32_t dim, float eps, int32_t dtype,
+                     int32_t residual_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Everything GroupedQueryAttention.forward does between its projections and the attention call
+ * (model/attention/GQA.py:81-102), plus the store_kvcache scatter, in one pass over the fused
+ * projection output qkv [num_tokens, >= (Hq + 2 Hkv) * D] (token stride in elements):
+ *   q, k: RMSNorm over the whole projected vector (eps as given: the machine epsilon of the dtype in
+ *   the reference), rounded to the dtype, then half-split RoPE (model/attention/utils.py:34-45) in
+ *   fp32 at positions[t] using rope_table [rope_positions, D] = cat(cos, sin), rounded to the dtype;
+ *   q_out [num_tokens, Hq, D], k_out [num_tokens, Hkv, D];
+ *   if k_cache != NULL: k_cache[slot] = k_out row, v_cache[slot] = raw v row, slot < 0 skipped.
+ * ------------------------------------------------------------------------------------------- */
+int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const float* q_norm_weight,
+                            const float* k_norm_weight, const float* rope_table,
+                            int64_t rope_positions, const int64_t* positions, void* q_out, void* k_out,
+                            void* k_cache, void* v_cache, const int64_t* slot_mapping,
+                            int64_t num_slots, int64_t num_tokens, int32_t num_q_heads,
+                            int32_t num_kv_heads, int32_t head_dim, float eps, int32_t dtype,
+                            int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

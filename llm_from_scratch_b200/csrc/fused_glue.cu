@@ -1,0 +1,215 @@
+// Fused element-wise stages around attention (one launch each instead of ~10 / ~25 tensor ops):
+//
+//  add_rmsnorm          residual-stream RMSNorm with the optional fused residual add of the reference
+//                       (model/utils.py:54-67): xf = float(x) [+ float(residual)];
+//                       y = (w * xf * rsqrt(mean(xf^2) + eps)) -> dtype of x; new residual = xf -> dtype of x.
+//  qk_norm_rope_store   what GroupedQueryAttention.forward does between the projections and the
+//                       attention call (model/attention/GQA.py:81-102): RMSNorm over the WHOLE projected
+//                       q vector and the whole k vector (eps = machine epsilon of the dtype, result
+//                       rounded to the dtype), half-split RoPE in fp32 at the token's position, result
+//                       rounded to the dtype; K (after norm + RoPE) and V (raw) are also scattered into
+//                       the paged cache through slot_mapping.
+//
+// One CTA per token row; rows are read once with 16-byte loads, reduced with warp shuffles + one
+// shared-memory exchange, and written once.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();   // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) t += scratch[w];
+  return t;
+}
+
+template <typename T, typename R>
+__global__ void __launch_bounds__(kThreads)
+add_rmsnorm_kernel(const T* __restrict__ x, const R* __restrict__ residual, const float* __restrict__ w,
+                   T* __restrict__ y, T* __restrict__ res_out, int d, float eps) {
+  __shared__ float scratch[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * d;
+  const R* rr = residual ? residual + row * d : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += kThreads) {
+    float v = to_float<T>(xr[i]);
+    if (rr) v += to_float<R>(rr[i]);
+    ss += v * v;
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / static_cast<float>(d) + eps);
+  for (int i = threadIdx.x; i < d; i += kThreads) {
+    float v = to_float<T>(xr[i]);
+    if (rr) v += to_float<R>(rr[i]);
+    y[row * d + i] = from_float<T>(w[i] * v * inv);
+    if (res_out) res_out[row * d + i] = from_float<T>(v);
+  }
+}
+
+struct QkArgs {
+  const void* qkv;       // [T, qkv_stride]: q (Hq*D) | k (Hkv*D) | v (Hkv*D)
+  int64_t qkv_stride;
+  const float* q_norm_w; // [Hq*D]
+  const float* k_norm_w; // [Hkv*D]
+  const float* rope;     // [max_pos, D]: cos (D/2) | sin (D/2)
+  const int64_t* positions;
+  int64_t max_pos;
+  void* q_out;           // [T, Hq, D]
+  void* k_out;           // [T, Hkv, D]
+  void* k_cache;         // [num_slots, Hkv, D] or null
+  void* v_cache;
+  const int64_t* slots;
+  int64_t num_slots;
+  int Hq, Hkv, D;
+  float eps;
+  int32_t* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) qk_norm_rope_store_kernel(const QkArgs a) {
+  __shared__ float scratch[kThreads / 32];
+  const int64_t t = blockIdx.x;
+  const int Wq = a.Hq * a.D, Wk = a.Hkv * a.D, half = a.D / 2;
+  const T* row = static_cast<const T*>(a.qkv) + t * a.qkv_stride;
+  const T* qr = row;
+  const T* kr = row + Wq;
+  const T* vr = row + Wq + Wk;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < Wq; i += kThreads) {
+    const float v = to_float<T>(qr[i]);
+    sq += v * v;
+  }
+  for (int i = threadIdx.x; i < Wk; i += kThreads) {
+    const float v = to_float<T>(kr[i]);
+    sk += v * v;
+  }
+  const float iq = rsqrtf(block_sum(sq, scratch) / static_cast<float>(Wq) + a.eps);
+  const float ik = rsqrtf(block_sum(sk, scratch) / static_cast<float>(Wk) + a.eps);
+  int64_t pos = a.positions[t];
+  if (pos < 0 || pos >= a.max_pos) {
+    report(a.status, B200_ERR_BOUNDS);
+    pos = pos < 0 ? 0 : a.max_pos - 1;
+  }
+  const float* cs = a.rope + pos * a.D;
+  int64_t slot = a.k_cache ? a.slots[t] : -1;
+  if (slot >= a.num_slots) {
+    report(a.status, B200_ERR_BOUNDS);
+    slot = -1;
+  }
+  T* qo = static_cast<T*>(a.q_out) + t * Wq;
+  T* ko = static_cast<T*>(a.k_out) + t * Wk;
+  T* kc = slot >= 0 ? static_cast<T*>(a.k_cache) + slot * Wk : nullptr;
+  T* vc = slot >= 0 ? static_cast<T*>(a.v_cache) + slot * Wk : nullptr;
+  // normalised values are rounded to the dtype before the rotation, as nn.RMSNorm returns its input dtype
+  for (int i = threadIdx.x; i < a.Hq * half; i += kThreads) {
+    const int h = i / half, j = i - h * half;
+    const int i1 = h * a.D + j, i2 = i1 + half;
+    const float x1 = to_float<T>(from_float<T>(to_float<T>(qr[i1]) * iq * a.q_norm_w[i1]));
+    const float x2 = to_float<T>(from_float<T>(to_float<T>(qr[i2]) * iq * a.q_norm_w[i2]));
+    const float c = cs[j], s = cs[half + j];
+    qo[i1] = from_float<T>(x1 * c - x2 * s);
+    qo[i2] = from_float<T>(x2 * c + x1 * s);
+  }
+  for (int i = threadIdx.x; i < a.Hkv * half; i += kThreads) {
+    const int h = i / half, j = i - h * half;
+    const int i1 = h * a.D + j, i2 = i1 + half;
+    const float x1 = to_float<T>(from_float<T>(to_float<T>(kr[i1]) * ik * a.k_norm_w[i1]));
+    const float x2 = to_float<T>(from_float<T>(to_float<T>(kr[i2]) * ik * a.k_norm_w[i2]));
+    const float c = cs[j], s = cs[half + j];
+    const T y1 = from_float<T>(x1 * c - x2 * s), y2 = from_float<T>(x2 * c + x1 * s);
+    ko[i1] = y1;
+    ko[i2] = y2;
+    if (kc) {
+      kc[i1] = y1;
+      kc[i2] = y2;
+    }
+  }
+  if (vc)
+    for (int i = threadIdx.x; i < Wk; i += kThreads) vc[i] = vr[i];
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_add_rmsnorm(const void* x, const void* residual, const float* weight, void* y,
+                                void* residual_out, int64_t num_rows, int32_t dim, float eps,
+                                int32_t dtype, int32_t residual_dtype, void* stream) {
+  using namespace b200;
+  if (num_rows < 0 || dim <= 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (residual && residual_dtype != B200_DTYPE_F32 && residual_dtype != B200_DTYPE_BF16)
+    return B200_ERR_UNSUPPORTED;
+  if (num_rows == 0) return B200_OK;
+  if (!x || !weight || !y) return B200_ERR_ARG;
+  if (num_rows > 2147483647) return B200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>(num_rows);
+  const bool rf32 = !residual || residual_dtype == B200_DTYPE_F32;
+#define LAUNCH(T, R)                                                                               \
+  add_rmsnorm_kernel<T, R><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x),                     \
+                                                     static_cast<const R*>(residual), weight,      \
+                                                     static_cast<T*>(y),                           \
+                                                     static_cast<T*>(residual_out), dim, eps)
+  if (dtype == B200_DTYPE_F32) {
+    if (rf32) LAUNCH(float, float); else LAUNCH(float, __nv_bfloat16);
+  } else {
+    if (rf32) LAUNCH(__nv_bfloat16, float); else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef LAUNCH
+  return launch_result();
+}
+
+extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride,
+                                       const float* q_norm_weight, const float* k_norm_weight,
+                                       const float* rope_table, int64_t rope_positions,
+                                       const int64_t* positions, void* q_out, void* k_out,
+                                       void* k_cache, void* v_cache, const int64_t* slot_mapping,
+                                       int64_t num_slots, int64_t num_tokens, int32_t num_q_heads,
+                                       int32_t num_kv_heads, int32_t head_dim, float eps, int32_t dtype,
+                                       int32_t* status, void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) ||
+      rope_positions <= 0)
+    return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (num_tokens == 0) return B200_OK;
+  if (!qkv || !q_norm_weight || !k_norm_weight || !rope_table || !positions || !q_out || !k_out)
+    return B200_ERR_ARG;
+  if ((k_cache == nullptr) != (v_cache == nullptr)) return B200_ERR_ARG;
+  if (k_cache && !slot_mapping) return B200_ERR_ARG;
+  const int64_t width = static_cast<int64_t>(num_q_heads + 2 * num_kv_heads) * head_dim;
+  if (qkv_token_stride < width || num_tokens > 2147483647) return B200_ERR_ARG;
+  QkArgs a{};
+  a.qkv = qkv;
+  a.qkv_stride = qkv_token_stride;
+  a.q_norm_w = q_norm_weight;
+  a.k_norm_w = k_norm_weight;
+  a.rope = rope_table;
+  a.positions = positions;
+  a.max_pos = rope_positions;
+  a.q_out = q_out;
+  a.k_out = k_out;
+  a.k_cache = k_cache;
+  a.v_cache = v_cache;
+  a.slots = slot_mapping;
+  a.num_slots = num_slots;
+  a.Hq = num_q_heads;
+  a.Hkv = num_kv_heads;
+  a.D = head_dim;
+  a.eps = eps;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>(num_tokens);
+  if (dtype == B200_DTYPE_F32)
+    qk_norm_rope_store_kernel<float><<<grid, kThreads, 0, s>>>(a);
+  else
+    qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
+  return launch_result();
+}

@@ -51,7 +51,10 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) ->
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
-    """fp32 RMSNorm returning the input dtype; with ``residual`` also returns the new residual."""
+    """fp32 RMSNorm returning the input dtype; with ``residual`` also returns the new residual.
+    One fused kernel on the GPU; the tensor-op form below is its definition."""
+    if x.is_cuda and x.dim() == 2 and x.is_contiguous() and (residual is None or residual.is_contiguous()):
+        return ops.add_rmsnorm(x, weight, eps, residual)
     dt = x.dtype
     xf = x.float()
     if residual is not None:
@@ -110,6 +113,7 @@ class MoE(nn.Module):
     """
 
     dense_max_tokens = 512
+    use_grouped = True     # bf16: library grouped GEMM over tokens sorted by expert (no host sync)
 
     def __init__(self, p: _Params, prefix: str, cfg: ModelConfig):
         super().__init__()
@@ -139,7 +143,9 @@ class MoE(nn.Module):
 
     def forward(self, x):
         idx, wts = self.route(x)
-        if x.shape[0] <= self.dense_max_tokens:
+        if x.dtype == torch.bfloat16 and self.use_grouped:
+            out = self.forward_grouped(x, idx, wts)
+        elif x.shape[0] <= self.dense_max_tokens:
             out = self.forward_dense(x, idx, wts)
         else:
             out = self.forward_sorted(x, idx, wts)
@@ -164,6 +170,32 @@ class MoE(nn.Module):
             lo = hi
         return out
 
+    def forward_grouped(self, x, idx, wts):
+        """bf16: rows sorted by expert, two grouped GEMMs with device-side group offsets, then the
+        K contributions of every token are added in ascending expert order in the activation dtype
+        (the accumulation order of moe.py:312-339).  No host sync, no per-expert launch."""
+        T, K, E = x.shape[0], self.K, self.E
+        sidx, perm = idx.sort(dim=1)                       # ascending expert ids per token
+        w_sorted = wts.gather(1, perm).to(x.dtype).reshape(-1)
+        flat = sidx.reshape(-1)                            # expert of row t*K + k
+        order = flat.argsort(stable=True)                  # rows grouped by expert
+        experts = flat[order]
+        xs = x[order // K]
+        counts = torch.zeros(E, dtype=torch.int32, device=x.device).scatter_add_(
+            0, flat, torch.ones_like(flat, dtype=torch.int32))     # bincount would sync the host
+        offs = counts.cumsum(0).to(torch.int32)
+        h = torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs) + self.b13[experts]
+        act = F.silu(h[:, :self.d_ff]) * h[:, self.d_ff:]
+        y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs) + self.b2[experts]
+        y = y * w_sorted[order].unsqueeze(1)
+        yt = torch.empty_like(y)
+        yt[order] = y
+        yt = yt.view(T, K, -1)
+        out = yt[:, 0]
+        for k in range(1, K):
+            out = out + yt[:, k]
+        return out
+
     def forward_dense(self, x, idx, wts):
         T = x.shape[0]
         xe = x.unsqueeze(0).expand(self.E, T, x.shape[1])
@@ -184,6 +216,7 @@ class GQAAttention(nn.Module):
         self.rope = rope
         self.scale = self.hd ** -0.5
         self.dtype = p.dtype
+        self.fused = True   # False: the same stage as separate tensor ops + store_kvcache
         # views into the pool; set by ModelRunner.allocate_kv_cache (model_runner.py:186-190)
         self.k_cache = self.v_cache = torch.empty(0)
 
@@ -191,13 +224,18 @@ class GQAAttention(nn.Module):
         T = x.shape[0]
         kvw = self.Hkv * self.hd
         qkv = F.linear(x.to(self.dtype), self.w_qkv, self.b_qkv)
-        q = _vector_norm(qkv[:, :self.d], self.q_norm).view(T, self.H, self.hd)
-        k = _vector_norm(qkv[:, self.d:self.d + kvw], self.k_norm).view(T, self.Hkv, self.hd)
-        v = qkv[:, self.d + kvw:].view(T, self.Hkv, self.hd)
-        q = apply_rope(q, positions, self.rope).to(self.dtype)
-        k = apply_rope(k, positions, self.rope).to(self.dtype)
-        if self.k_cache.numel():
-            ops.store_kvcache(k, v, self.k_cache, self.v_cache, ctx.slot_mapping)
+        if self.fused:
+            # q/k RMSNorm + RoPE + store_kvcache in one kernel
+            q, k, v = ops.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.rope, positions, self.H, self.Hkv,
+                                             self.hd, self.k_cache, self.v_cache, ctx.slot_mapping)
+        else:
+            q = _vector_norm(qkv[:, :self.d], self.q_norm).view(T, self.H, self.hd)
+            k = _vector_norm(qkv[:, self.d:self.d + kvw], self.k_norm).view(T, self.Hkv, self.hd)
+            v = qkv[:, self.d + kvw:].view(T, self.Hkv, self.hd)
+            q = apply_rope(q, positions, self.rope).to(self.dtype)
+            k = apply_rope(k, positions, self.rope).to(self.dtype)
+            if self.k_cache.numel():
+                ops.store_kvcache(k, v, self.k_cache, self.v_cache, ctx.slot_mapping)
         if ctx.is_prefill:
             if ctx.block_tables is not None:   # part of the context is already cached
                 o = ops.prefill_varlen(q, None, None, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,

@@ -241,6 +241,58 @@ def mla_decode(q_abs: torch.Tensor, q_rope: torch.Tensor, latent_cache: torch.Te
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """RMSNorm of x (+ residual) in fp32, result in x's dtype.  Returns y, or (y, new_residual) when a
+    residual is given (the fused add + norm of the reference's residual stream)."""
+    _cuda(x, weight, residual)
+    if not x.is_contiguous() or weight.dtype != torch.float32 or weight.numel() != x.shape[-1]:
+        raise ValueError("x must be contiguous and weight an fp32 vector of the row width")
+    if residual is not None and (residual.shape != x.shape or not residual.is_contiguous()):
+        raise ValueError("residual must match x")
+    rows, dim = x.numel() // x.shape[-1], x.shape[-1]
+    y = torch.empty_like(x)
+    res_out = torch.empty_like(x) if residual is not None else None
+    check(lib.b200_add_rmsnorm(x.data_ptr(), residual.data_ptr() if residual is not None else None,
+                               weight.data_ptr(), y.data_ptr(), res_out.data_ptr() if res_out is not None else None,
+                               rows, dim, float(eps), _dt(x), _dt(residual) if residual is not None else 0,
+                               _stream()), "add_rmsnorm")
+    return y if residual is None else (y, res_out)
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torch.Tensor, rope_table: torch.Tensor,
+                       positions: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int,
+                       k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+                       slot_mapping: torch.Tensor | None):
+    """q/k RMSNorm over the whole projected vectors + RoPE + scatter of K/V into the paged cache.
+
+    qkv: [T, (Hq + 2 Hkv) * D] fused projection output; returns (q [T,Hq,D], k [T,Hkv,D], v view [T,Hkv,D]).
+    """
+    dev = _cuda(qkv, q_norm_w, k_norm_w, rope_table, positions, k_cache, v_cache, slot_mapping)
+    T = qkv.shape[0]
+    wq, wk = num_q_heads * head_dim, num_kv_heads * head_dim
+    if qkv.shape[1] != wq + 2 * wk or qkv.stride(1) != 1:
+        raise ValueError("qkv must be [T, (Hq + 2 Hkv) * D] with contiguous rows")
+    if positions.dtype != torch.int64 or positions.numel() != T or not positions.is_contiguous():
+        raise ValueError("positions must be a contiguous int64 [T] tensor")
+    if rope_table.dtype != torch.float32 or rope_table.shape[1] != head_dim or not rope_table.is_contiguous():
+        raise ValueError("rope_table must be fp32 [positions, head_dim]")
+    use_cache = k_cache is not None and k_cache.numel() > 0
+    if use_cache and (slot_mapping is None or slot_mapping.dtype != torch.int64 or slot_mapping.numel() != T):
+        raise ValueError("slot_mapping must be int64 [T]")
+    q = torch.empty(T, num_q_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, num_kv_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    eps = torch.finfo(qkv.dtype).eps
+    check(lib.b200_qk_norm_rope_store(
+        qkv.data_ptr(), qkv.stride(0), q_norm_w.data_ptr(), k_norm_w.data_ptr(), rope_table.data_ptr(),
+        rope_table.shape[0], positions.data_ptr(), q.data_ptr(), k.data_ptr(),
+        k_cache.data_ptr() if use_cache else None, v_cache.data_ptr() if use_cache else None,
+        slot_mapping.data_ptr() if use_cache else None, (k_cache.numel() // wk) if use_cache else 0, T,
+        num_q_heads, num_kv_heads, head_dim, float(eps), _dt(qkv), status_word(dev).data_ptr(), _stream()),
+        "qk_norm_rope_store")
+    v = qkv[:, wq + wk:].view(T, num_kv_heads, head_dim)
+    return q, k, v
+
+
 def block_hash(token_ids, prefix: int = -1) -> int:
     """Chained XXH64 block hash; same value as BlockManager.compute_hash of the reference."""
     buf = array.array("i", token_ids)

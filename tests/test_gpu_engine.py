@@ -104,6 +104,25 @@ def test_moe_dense_and_sorted_paths_agree_and_decode_replays_from_graphs():
     assert (a - b).abs().max().item() <= 1e-5
 
 
+def test_moe_grouped_gemm_path_matches_the_expert_loop_in_bf16():
+    """bf16: the grouped-GEMM evaluation equals the reference-order expert loop up to bf16 rounding of
+    the GEMM outputs, for a prefill-sized and a decode-sized batch, top-2 and top-4."""
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    from llm_from_scratch_b200.model.transformer import MoE, _Params
+    for topk in (2, 4):
+        cfg = ModelConfig(vocab_size=64, context_length=32, d_model=256, num_layers=1, num_heads=4, num_kv_heads=4,
+                          d_ff=192, use_moe=True, n_routed_experts=8, num_experts_per_tok=topk, n_shared_experts=1)
+        w = init_reference_order(cfg, 3)
+        moe = MoE(_Params(w, torch.device("cuda"), torch.bfloat16), "layers.0.ffn", cfg)
+        for T in (1, 37, 700):
+            x = torch.randn(T, 256, device="cuda", generator=torch.Generator(device="cuda").manual_seed(T)).bfloat16()
+            idx, wts = moe.route(x)
+            got = moe.forward_grouped(x, idx, wts).float()
+            want = moe.forward_sorted(x, idx, wts).float()
+            err = (got - want).abs().max().item()
+            assert err <= 2e-2 * max(1.0, want.abs().max().item()), (topk, T, err)
+
+
 def test_small_moe_decoder_bf16_tracks_reference_autocast():
     """bf16 is compared by tolerance: logits of the first decode-free step (the prefill) against the
     reference modules under CPU autocast, and the fraction of matching greedy tokens."""

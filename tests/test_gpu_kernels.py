@@ -436,3 +436,58 @@ def test_mla_decode_bf16_fewer_than_16_heads():
                          torch.from_numpy(case.context_lens).cuda(), 0.07)
     ops.check_status()
     assert_close(got, want, torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- fused glue kernels
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm_matches_oracle(dtype):
+    ops, orc = _ops(), _oracle()
+    x, res = _randn((37, 512), 1, dtype), _randn((37, 512), 2, torch.float32)
+    w = _randn((512,), 3, torch.float32)
+    want = orc.rms_norm(x, w, 1e-5)
+    got = ops.add_rmsnorm(x.cuda(), w.cuda(), 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (got.float().cpu() - want.float()).abs().max().item() <= tol
+    for r in (res, res.to(dtype)):     # residual in fp32 (first layer) or in the activation dtype
+        wy, wr = orc.rms_norm(x, w, 1e-5, r)
+        gy, gr = ops.add_rmsnorm(x.cuda(), w.cuda(), 1e-5, r.cuda())
+        assert gy.dtype == dtype and gr.dtype == dtype
+        assert (gy.float().cpu() - wy.float()).abs().max().item() <= tol
+        assert (gr.float().cpu() - wr.float()).abs().max().item() <= (1e-6 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype):
+    """Against the oracle's RMSNorm-over-the-whole-vector + RoPE (model/attention/GQA.py:81-94) and its
+    store_kvcache, including a padded (-1) slot."""
+    ops, orc = _ops(), _oracle()
+    T, Hq, Hkv, D, bs, nb = 29, 8, 2, 64, 16, 4
+    qkv = _randn((T, (Hq + 2 * Hkv) * D), 5, dtype)
+    qw, kw = _randn((Hq * D,), 6, torch.float32), _randn((Hkv * D,), 7, torch.float32)
+    table = orc.rope_table(10000.0, D, 128)
+    pos = torch.from_numpy(np.random.default_rng(0).integers(0, 128, size=T).astype(np.int64))
+    slots = torch.from_numpy(np.random.default_rng(1).permutation(nb * bs)[:T].astype(np.int64))
+    slots[3] = -1
+    eps = torch.finfo(dtype).eps
+
+    def vec_norm(x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w).to(dtype)
+    q = vec_norm(qkv[:, :Hq * D], qw).view(T, Hq, D).transpose(0, 1)
+    k = vec_norm(qkv[:, Hq * D:(Hq + Hkv) * D], kw).view(T, Hkv, D).transpose(0, 1)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    want_q = orc.apply_rope(q.float(), pos, table).transpose(0, 1).to(dtype)
+    want_k = orc.apply_rope(k.float(), pos, table).transpose(0, 1).to(dtype)
+    kc_ref, vc_ref = torch.zeros(nb, bs, Hkv, D, dtype=dtype), torch.zeros(nb, bs, Hkv, D, dtype=dtype)
+    orc.store_kvcache(want_k, v, kc_ref, vc_ref, slots)
+    kc, vc = torch.zeros_like(kc_ref).cuda(), torch.zeros_like(vc_ref).cuda()
+    gq, gk, gv = ops.qk_norm_rope_store(qkv.cuda(), qw.cuda(), kw.cuda(), table.cuda(), pos.cuda(), Hq, Hkv, D,
+                                        kc, vc, slots.cuda())
+    ops.check_status()
+    tol = 2e-5 if dtype == torch.float32 else 4e-2     # bf16: one rounding step of values up to ~4
+    assert (gq.float().cpu() - want_q.float()).abs().max().item() <= tol
+    assert (gk.float().cpu() - want_k.float()).abs().max().item() <= tol
+    assert torch.equal(gv.cpu(), v)
+    assert torch.equal(vc.cpu(), vc_ref)
+    assert torch.equal(kc.view(-1, Hkv, D)[slots[slots >= 0].cuda()].cpu(), gk.cpu()[slots >= 0])
+    assert (kc.view(-1, Hkv, D).float().abs().sum(dim=(1, 2)) > 0).sum().item() == T - 1
