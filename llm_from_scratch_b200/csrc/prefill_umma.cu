@@ -46,6 +46,8 @@ constexpr float kRescaleThreshold = 8.f;      // log2 units
 // the special-function unit.  Measured on the 262K-token stress batch: 855 TFLOP/s with 0 (off),
 // 789 TFLOP/s with 4 — the softmax warps are issue-bound, not SFU-bound — so it is off.
 constexpr int kPolyEvery = 0;
+// Also measured and not kept: two threads per query row (640-thread CTA, one named-barrier exchange
+// of the row statistics per KV tile): 802 TFLOP/s against 861 with one thread per row.
 
 enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_FINAL = 13, NUM_BARS = 14 };
 
