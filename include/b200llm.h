@@ -204,6 +204,23 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const flo
                             int32_t num_kv_heads, int32_t head_dim, float eps, int32_t dtype,
                             int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * MoE routing for inference (Gate.forward, model/architecture/moe.py:45-90, and the grouping by
+ * expert that MOE.moe_infer does with argsort + bincount on the host, moe.py:297-307) in one launch.
+ *   gate_logits [num_tokens, num_experts] in `dtype` (= x @ gate_weight^T), expert_bias fp32.
+ *   scores = sigmoid(logits); top_k experts by logits + bias (ties to the lower index); weights =
+ *   selected scores / (their sum + 1e-10) when top_k > 1; all rounded as the dtype would.
+ * Outputs, rows ordered by (expert, token):
+ *   sorted_token / sorted_expert int32 [num_tokens*top_k], sorted_weight `dtype` [num_tokens*top_k],
+ *   expert_offsets int32 [num_experts] (exclusive end of every expert's rows),
+ *   slot_to_row int32 [num_tokens, top_k]: row of token t's j-th expert in ascending expert order.
+ * Limits: num_experts <= 32, top_k <= 8, num_tokens*top_k <= 65536 (else B200_ERR_UNSUPPORTED).
+ * ------------------------------------------------------------------------------------------- */
+int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t num_tokens,
+                   int32_t num_experts, int32_t top_k, int32_t* sorted_token, int32_t* sorted_expert,
+                   void* sorted_weight, int32_t* expert_offsets, int32_t* slot_to_row, int32_t dtype,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -142,6 +142,10 @@ class MoE(nn.Module):
         return idx, wts
 
     def forward(self, x):
+        if (x.dtype == torch.bfloat16 and self.use_grouped and self.E <= ops.MOE_ROUTE_MAX_EXPERTS
+                and self.K <= ops.MOE_ROUTE_MAX_TOPK and x.shape[0] * self.K <= ops.MOE_ROUTE_MAX_ROWS):
+            out = self.forward_routed(x)
+            return out + self.shared(x) if self.shared is not None else out
         idx, wts = self.route(x)
         if x.dtype == torch.bfloat16 and self.use_grouped:
             out = self.forward_grouped(x, idx, wts)
@@ -168,6 +172,22 @@ class MoE(nn.Module):
                 y = self.experts[e](x[t]) * flat_w[order[lo:hi]]
                 out.index_add_(0, t, y)
             lo = hi
+        return out
+
+    def forward_routed(self, x):
+        """bf16 fast path: one routing kernel (top-k, weights, grouping by expert), two grouped GEMMs,
+        and a gather-based combine that adds every token's K contributions in ascending expert order."""
+        T, K = x.shape[0], self.K
+        tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, K)
+        xs = x.index_select(0, tok)
+        h = torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs) + self.b13.index_select(0, experts)
+        act = F.silu(h[:, :self.d_ff]) * h[:, self.d_ff:]
+        y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs) + self.b2.index_select(0, experts)
+        y = y * w.unsqueeze(1)
+        yt = y.index_select(0, inv.reshape(-1)).view(T, K, -1)
+        out = yt[:, 0]
+        for k in range(1, K):
+            out = out + yt[:, k]
         return out
 
     def forward_grouped(self, x, idx, wts):

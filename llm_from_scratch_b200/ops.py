@@ -293,6 +293,28 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torc
     return q, k, v
 
 
+MOE_ROUTE_MAX_EXPERTS, MOE_ROUTE_MAX_TOPK, MOE_ROUTE_MAX_ROWS = 32, 8, 65536
+
+
+def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int):
+    """Top-k routing + grouping by expert.  Returns (sorted_token, sorted_expert, sorted_weight,
+    expert_offsets, slot_to_row); see ``b200_moe_route`` in the header for the layout."""
+    _cuda(gate_logits, expert_bias)
+    T, E = gate_logits.shape
+    if not gate_logits.is_contiguous() or expert_bias.dtype != torch.float32 or expert_bias.numel() != E:
+        raise ValueError("gate_logits must be contiguous [T, E] and expert_bias fp32 [E]")
+    dev, n = gate_logits.device, T * top_k
+    tok = torch.empty(n, dtype=torch.int32, device=dev)
+    exp = torch.empty(n, dtype=torch.int32, device=dev)
+    w = torch.empty(n, dtype=gate_logits.dtype, device=dev)
+    offs = torch.empty(E, dtype=torch.int32, device=dev)
+    inv = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+    check(lib.b200_moe_route(gate_logits.data_ptr(), expert_bias.data_ptr(), T, E, top_k, tok.data_ptr(),
+                             exp.data_ptr(), w.data_ptr(), offs.data_ptr(), inv.data_ptr(), _dt(gate_logits),
+                             _stream()), "moe_route")
+    return tok, exp, w, offs, inv
+
+
 def block_hash(token_ids, prefix: int = -1) -> int:
     """Chained XXH64 block hash; same value as BlockManager.compute_hash of the reference."""
     buf = array.array("i", token_ids)

@@ -121,6 +121,24 @@ def test_moe_grouped_gemm_path_matches_the_expert_loop_in_bf16():
             want = moe.forward_sorted(x, idx, wts).float()
             err = (got - want).abs().max().item()
             assert err <= 2e-2 * max(1.0, want.abs().max().item()), (topk, T, err)
+            # the single-kernel routing picks the same experts (up to ties) with the same weights
+            from llm_from_scratch_b200 import ops
+            tok, experts, w, offs, inv = ops.moe_route((x @ moe.gate_w.t()).contiguous(), moe.gate_bias, topk)
+            assert offs[-1].item() == T * topk and torch.equal(offs, experts.bincount(minlength=8).cumsum(0).int())
+            assert torch.equal(tok.sort().values, torch.arange(T, device="cuda").repeat_interleave(topk).int())
+            assert (experts[1:] >= experts[:-1]).all()
+            rows = inv.long()
+            assert torch.equal(tok[rows.reshape(-1)].view(T, topk), torch.arange(T, device="cuda").view(T, 1).expand(T, topk).int())
+            sel = experts[rows.reshape(-1)].view(T, topk).long()
+            assert (sel[:, 1:] > sel[:, :-1]).all()
+            ref_sel = idx.sort(dim=1).values
+            same = (sel == ref_sel).all(dim=1)
+            assert same.float().mean().item() >= 0.95          # bf16 ties may resolve differently
+            ref_w = wts.gather(1, idx.sort(dim=1).indices).float()
+            got_w = w[rows.reshape(-1)].view(T, topk).float()
+            assert (got_w[same] - ref_w[same]).abs().max().item() <= 8e-3
+            routed = moe.forward_routed(x).float()
+            assert (routed[same] - want[same]).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
 
 
 def test_small_moe_decoder_bf16_tracks_reference_autocast():
