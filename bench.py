@@ -145,6 +145,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "store", "engine"],
                     help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
                          "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
+    ap.add_argument("--rate", type=float, default=0.0, help="engine workload: Poisson arrival rate (req/s); 0 = offline")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="sequences per GPU; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()
@@ -153,13 +154,17 @@ def main():
 
     if args.workload != "decode":
         from llm_from_scratch_b200 import microbench
-        torch.cuda.set_device(0)
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         fn = getattr(microbench, args.workload)
         kw = dict(steps=args.steps, warmup=args.warmup)
+        if args.workload == "engine" and args.rate > 0:
+            kw["rate"] = args.rate
         if args.batch != BATCH:   # profiling cases: fewer sequences / tokens
             key = {"mla_decode": "batch", "engine": "batch", "prefill": "total", "store": "tokens"}[args.workload]
             kw[key] = args.batch
         res = fn(**kw)
+        if not res:       # a non-zero rank of a multi-replica engine run
+            return
         peak, kind = hbm_peak()
         if "gbs" in res:
             res["hbm_frac"] = res["gbs"] / peak

@@ -40,12 +40,31 @@ class ReplicaReport:
     steps: int = 0
 
 
-def serve_shard(engine, shard: list, rank: int = 0) -> ReplicaReport:
-    """Runs one replica over its shard: ``shard`` is a list of (token_ids, SamplingParams)."""
-    seqs = [engine.add_request(tok, sp) for tok, sp in shard]
+def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaReport:
+    """Runs one replica over its shard: ``shard`` is a list of (token_ids, SamplingParams).
+
+    ``arrivals`` (seconds from the start, one per request, non-decreasing) turns the run into an online
+    one: a request is handed to the scheduler only once the wall clock has passed its arrival time, and
+    the replica sleeps when it is idle before the next arrival.  Without it every request is present
+    at t = 0.
+    """
     rep = ReplicaReport(rank=rank)
     t0 = time.perf_counter()
-    while not engine.is_finished():
+    if arrivals is None:
+        seqs = [engine.add_request(tok, sp) for tok, sp in shard]
+        pending = 0
+    else:
+        seqs, pending = [], 0
+    while pending < (len(shard) if arrivals is not None else 0) or not engine.is_finished():
+        if arrivals is not None:
+            now = time.perf_counter() - t0
+            while pending < len(shard) and arrivals[pending] <= now:
+                seqs.append(engine.add_request(*shard[pending]))
+                pending += 1
+            if engine.is_finished():
+                if pending < len(shard):
+                    time.sleep(max(0.0, arrivals[pending] - (time.perf_counter() - t0)))
+                continue
         outputs, n, is_prefill = engine.step()
         if n == 0 and not outputs:
             raise RuntimeError("nothing schedulable: KV pool too small for the waiting request")
@@ -59,7 +78,7 @@ def serve_shard(engine, shard: list, rank: int = 0) -> ReplicaReport:
     return rep
 
 
-def serve_sharded(make_engine, requests: list):
+def serve_sharded(make_engine, requests: list, arrivals=None):
     """Every rank of the initialised process group serves its shard; rank 0 gets
     ``(token_ids in arrival order, [ReplicaReport per rank])``, other ranks get ``(None, None)``.
 
@@ -68,10 +87,11 @@ def serve_sharded(make_engine, requests: list):
     """
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()):
-        rep = serve_shard(make_engine(0), requests, 0)
+        rep = serve_shard(make_engine(0), requests, 0, arrivals)
         return rep.token_ids, [rep]
     rank, world = dist.get_rank(), dist.get_world_size()
-    rep = serve_shard(make_engine(rank), shard_requests(requests, world, rank), rank)
+    rep = serve_shard(make_engine(rank), shard_requests(requests, world, rank), rank,
+                      None if arrivals is None else shard_requests(list(arrivals), world, rank))
     gathered = [None] * world if rank == 0 else None
     dist.gather_object(rep, gathered, dst=0)
     if rank != 0:

@@ -88,38 +88,62 @@ C3_MODEL = dict(vocab_size=32000, context_length=2048, d_model=1024, num_layers=
                 n_shared_experts=1)
 
 
-def engine(steps: int = 0, warmup: int = 0, batch: int = 512, device: str = "cuda:0") -> dict:
+def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None = None) -> dict:
     """End-to-end continuous batching, GQA+MoE decoder (d_model 1024, 16 layers, 16/4 heads, head_dim 64,
-    16 experts top-2 + shared, d_ff 704, vocab 32000), bf16, random init: ``batch`` requests present at
-    t = 0, prompts uniform [64,1024], outputs geometric(mean 256) capped at 1024, max 256 sequences and
-    8192 batched tokens per step, KV block 16.  ``steps`` / ``warmup`` are unused (the job runs once)."""
+    16 experts top-2 + shared, d_ff 704, vocab 32000), bf16, random init (seed 0): ``batch`` requests,
+    prompts uniform [64,1024], outputs geometric(mean 256) capped at 1024, max 256 sequences and 8192
+    batched tokens per step, KV block 16; arrivals Poisson with ``rate`` requests/s, or all at t = 0.
+    Under torchrun every rank is an independent replica serving requests rank, rank + N, ...; the
+    aggregate is tokens of all replicas / the slowest replica's wall time.  ``steps``/``warmup`` unused."""
     import itertools
+    import os
     import time
+
+    import torch.distributed as dist
 
     from .engine import SamplingParams, Sequence
     from .engine.llm_engine import LLMEngine
-    from .engine.replicas import serve_shard
+    from .engine.replicas import serve_sharded
     from .workloads import c3_requests
-    prompts, outs, _ = c3_requests(batch)
-    Sequence.counter = itertools.count()
-    cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256, max_num_batched_tokens=8192,
-               max_cached_blocks=40000, eos=-1, device=device, max_model_length=2048, seed=0)
-    t0 = time.perf_counter()
-    eng = LLMEngine(cfg)
-    build_s = time.perf_counter() - t0
-    shard = [(p, SamplingParams(temperature=0.0, max_tokens=int(n) + 1, ignore_eos=True)) for p, n in zip(prompts, outs)]
-    torch.cuda.synchronize()
-    rep = serve_shard(eng, shard)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    prompts, outs, arrivals = c3_requests(batch, rate=rate)
+    built = {}
+
+    def make_engine(rank):
+        Sequence.counter = itertools.count()
+        cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
+                   max_num_batched_tokens=8192, max_cached_blocks=40000, eos=-1, device=f"cuda:{local_rank}",
+                   max_model_length=2048, seed=0)
+        t0 = time.perf_counter()
+        built["engine"] = LLMEngine(cfg)
+        built["build_s"] = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()        # replicas start serving together
+        return built["engine"]
+
+    requests = [(p, SamplingParams(temperature=0.0, max_tokens=int(n) + 1, ignore_eos=True))
+                for p, n in zip(prompts, outs)]
+    tokens, reports = serve_sharded(make_engine, requests, None if rate is None else arrivals.tolist())
     torch.cuda.synchronize()
     ops.check_status()
-    gen = sum(len(t) for t in rep.token_ids)
-    assert gen == int(outs.sum()), (gen, int(outs.sum()))
-    graphs = bool(eng.model_runner.graphs)
-    timing = dict(eng.timing)
+    eng = built["engine"]
+    graphs, timing = bool(eng.model_runner.graphs), dict(eng.timing)
     eng.exit()
-    return dict(workload=f"continuous batching GQA+MoE bf16: {batch} requests at t=0, prompts U[64,1024], outputs "
-                         "geometric(256) cap 1024, max 256 seqs / 8192 tokens per step",
-                requests=batch, generated_tokens=gen, prompt_tokens=int(sum(len(p) for p in prompts)),
-                wall_s=rep.wall_s, steps=rep.steps, output_tokens_per_s=gen / rep.wall_s,
-                total_tokens_per_s=(gen + sum(len(p) for p in prompts)) / rep.wall_s, engine_build_s=build_s,
-                cuda_graphs=graphs, timing=timing)
+    if tokens is None:            # not rank 0
+        return {}
+    gen = sum(len(t) for t in tokens)
+    assert gen == int(outs.sum()), (gen, int(outs.sum()))
+    wall = max(r.wall_s for r in reports)
+    prompt_tokens = int(sum(len(p) for p in prompts))
+    return dict(workload=f"continuous batching GQA+MoE bf16: {batch} requests "
+                         f"({'all at t=0' if rate is None else f'Poisson {rate}/s'}), prompts U[64,1024], outputs "
+                         "geometric(256) cap 1024, max 256 seqs / 8192 tokens per step per replica",
+                replicas=world, requests=batch, generated_tokens=gen, prompt_tokens=prompt_tokens, wall_s=wall,
+                replica_wall_s=[r.wall_s for r in reports], steps=[r.steps for r in reports],
+                output_tokens_per_s=gen / wall, total_tokens_per_s=(gen + prompt_tokens) / wall,
+                engine_build_s=built["build_s"], cuda_graphs=graphs, rank0_timing=timing)

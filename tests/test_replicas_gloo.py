@@ -85,3 +85,15 @@ def test_two_replicas_over_gloo_match_one_replica():
     assert tokens == want
     assert [s[0] for s in summary] == [0, 1] and [s[3] for s in summary] == [12, 11]
     assert sum(s[1] for s in summary) > 0 and sum(s[2] for s in summary) > 0
+
+
+def test_online_arrivals_give_the_same_streams_as_offline():
+    """Requests handed over as their (Poisson) arrival times pass produce the same completions: a
+    request's stream depends only on its own tokens."""
+    from llm_from_scratch_b200.engine.replicas import serve_shard
+    reqs = _requests()[:9]
+    offline = serve_shard(_make_engine(0), reqs).token_ids
+    arrivals = [0.0, 0.0, 0.002, 0.004, 0.004, 0.01, 0.03, 0.03, 0.05]
+    online = serve_shard(_make_engine(0), reqs, arrivals=arrivals)
+    assert online.token_ids == offline
+    assert online.wall_s >= 0.05
