@@ -112,7 +112,6 @@ int mla_decode_mma_launch(const void* q_abs, const void* q_rope, const void* lat
                           void* workspace, size_t workspace_bytes, int32_t* status,
                           cudaStream_t s);
 size_t mla_decode_mma_workspace(int batch, int H, int r, int dr);
-
 }  // namespace b200
 
 extern "C" size_t b200_mla_decode_workspace_bytes(int32_t batch, int32_t num_heads,

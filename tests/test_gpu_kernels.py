@@ -491,3 +491,29 @@ def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype):
     assert torch.equal(vc.cpu(), vc_ref)
     assert torch.equal(kc.view(-1, Hkv, D)[slots[slots >= 0].cuda()].cpu(), gk.cpu()[slots >= 0])
     assert (kc.view(-1, Hkv, D).float().abs().sum(dim=(1, 2)) > 0).sum().item() == T - 1
+
+
+# ----------------------------------------------------------------------------- empty inputs
+def test_empty_inputs_are_no_ops():
+    """Zero tokens / zero sequences through every entry point: success, nothing launched or written."""
+    from llm_from_scratch_b200._lib import lib, DTYPE_BF16
+    ops = _ops()
+    dev = torch.device("cuda")
+    kc = torch.ones(2, 16, 2, 64, dtype=torch.bfloat16, device=dev)
+    vc = torch.ones_like(kc)
+    empty_kv = torch.empty(0, 2, 64, dtype=torch.bfloat16, device=dev)
+    ops.store_kvcache(empty_kv, empty_kv, kc, vc, torch.empty(0, dtype=torch.int64, device=dev))
+    assert (kc == 1).all() and (vc == 1).all()
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.b200_paged_decode_gqa(None, None, None, None, None, 1, None, 0, 8, 2, 64, 16, 2, 0.125, None, 0,
+                                     DTYPE_BF16, None, s) == 0
+    assert lib.b200_mla_decode(None, None, None, None, None, 1, None, 0, 16, 512, 64, 16, 2, 0.07, None, 0,
+                               DTYPE_BF16, None, s) == 0
+    assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, 0, 0, None, None, 0, 0, 0, 8, 2, 64, 64, 0.125,
+                                   None, None, None, 0, 0, 0, DTYPE_BF16, None, s) == 0
+    # a batch whose contexts are all empty: zero rows, no block is read
+    q = torch.randn(3, 8, 64, device=dev).bfloat16()
+    bt = torch.full((3, 4), -1, dtype=torch.int32, device=dev)
+    out = ops.paged_decode_gqa(q, kc, vc, bt, torch.zeros(3, dtype=torch.int64, device=dev), 0.125)
+    ops.check_status()
+    assert (out == 0).all()
