@@ -36,7 +36,8 @@ sys.path.insert(0, ROOT)
 
 HQ, HKV, D, BS, BATCH = 32, 8, 128, 16, 256
 CPU_SAMPLE_SEQS = 64
-NCU_DRAM_BYTES_PER_CONTEXT_TOKEN = (536_459_520 + 4_956_544) / 130_732   # profiles/paged_decode_bf16_c2.md
+# DRAM bytes read + written by one ncu-captured launch of the decode kernel over 130,732 context tokens
+NCU_DRAM_BYTES_PER_CONTEXT_TOKEN = (536_459_520 + 4_956_544) / 130_732
 
 
 def hbm_peak():

@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 2
+#define B200_ABI_VERSION 3
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -206,7 +206,7 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const flo
 
 /* ---------------------------------------------------------------------------------------------
  * MoE routing for inference (Gate.forward, model/architecture/moe.py:45-90, and the grouping by
- * expert that MOE.moe_infer does with argsort + bincount on the host, moe.py:297-307) in one launch.
+ * expert that MOE.moe_infer does with argsort + bincount on the host, moe.py:297-307), on the device.
  *   gate_logits [num_tokens, num_experts] in `dtype` (= x @ gate_weight^T), expert_bias fp32.
  *   scores = sigmoid(logits); top_k experts by logits + bias (ties to the lower index); weights =
  *   selected scores / (their sum + 1e-10) when top_k > 1; all rounded as the dtype would.
@@ -214,12 +214,36 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const flo
  *   sorted_token / sorted_expert int32 [num_tokens*top_k], sorted_weight `dtype` [num_tokens*top_k],
  *   expert_offsets int32 [num_experts] (exclusive end of every expert's rows),
  *   slot_to_row int32 [num_tokens, top_k]: row of token t's j-th expert in ascending expert order.
- * Limits: num_experts <= 32, top_k <= 8, num_tokens*top_k <= 65536 (else B200_ERR_UNSUPPORTED).
+ * One launch for num_tokens <= 256, two (count, scatter) above; `workspace` of
+ * b200_moe_route_workspace_bytes() bytes (0 for num_tokens <= 256) holds the per-CTA counts.
+ * Limits: num_experts <= 64, top_k <= 8, num_tokens <= 65536 (else B200_ERR_UNSUPPORTED).
  * ------------------------------------------------------------------------------------------- */
+size_t b200_moe_route_workspace_bytes(int32_t num_tokens, int32_t num_experts);
 int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t num_tokens,
                    int32_t num_experts, int32_t top_k, int32_t* sorted_token, int32_t* sorted_expert,
-                   void* sorted_weight, int32_t* expert_offsets, int32_t* slot_to_row, int32_t dtype,
-                   void* stream);
+                   void* sorted_weight, int32_t* expert_offsets, int32_t* slot_to_row, void* workspace,
+                   size_t workspace_bytes, int32_t dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SwiGLU of fused up-projection rows (model/architecture/mlp.py:61-67: w2(silu(w1 x) * w3 x)):
+ *   h [num_rows, 2*d_ff] = [w1 x | w3 x];  act [num_rows, d_ff] = silu(h1 + b1) * (h3 + b3).
+ * `bias` (may be NULL: already added by the GEMM) is [experts, 2*d_ff]; row r uses the bias row
+ * row_expert[r] (row 0 when row_expert is NULL).  Bias add, silu and product are each rounded to the
+ * dtype, like the tensor-op sequence they replace.
+ * ------------------------------------------------------------------------------------------- */
+int b200_swiglu(const void* h, const void* bias, const int32_t* row_expert, void* act, int64_t num_rows,
+                int32_t d_ff, int32_t dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * MoE combine (MOE.moe_infer, moe.py:312-339, and the shared expert, moe.py:272-273):
+ *   out[t] = sum_j round(round(expert_out[row] + bias[row_expert[row]]) * row_weight[row]),
+ *   row = slot_to_row[t, j], j ascending (= ascending expert id), every partial sum rounded to the
+ *   dtype as the reference's scatter_add_ in the activation dtype does; then + shared[t] if given.
+ * expert_out [num_tokens*top_k, d_model] in grouped (sorted) row order; bias [experts, d_model] or NULL.
+ * ------------------------------------------------------------------------------------------- */
+int b200_moe_combine(const void* expert_out, const void* bias, const int32_t* row_expert,
+                     const void* row_weight, const int32_t* slot_to_row, const void* shared, void* out,
+                     int64_t num_tokens, int32_t top_k, int32_t d_model, int32_t dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -10,8 +10,9 @@
 //                       rounded to the dtype; K (after norm + RoPE) and V (raw) are also scattered into
 //                       the paged cache through slot_mapping.
 //
-// One CTA per token row; rows are read once with 16-byte loads, reduced with warp shuffles + one
-// shared-memory exchange, and written once.
+// General kernels: one CTA per token row, reduced with warp shuffles + one shared-memory exchange.
+// bf16 rows whose widths are multiples of 256 take the fast kernels: one warp per row, 16-byte
+// loads and stores, warp shuffles only.
 #include "common.cuh"
 
 namespace b200 {
@@ -135,6 +136,139 @@ __global__ void __launch_bounds__(kThreads) qk_norm_rope_store_kernel(const QkAr
     for (int i = threadIdx.x; i < Wk; i += kThreads) vc[i] = vr[i];
 }
 
+
+// ---- bf16 fast paths: one warp per token row, 16-byte loads, no shared memory -------------------
+union Bf16x8 {
+  uint4 u;
+  __nv_bfloat16 b[8];
+};
+
+constexpr int kWarpRows = 4;   // rows (warps) per CTA
+
+// d % 256 == 0, d <= 2048: the row stays in registers between the reduction and the scaling
+template <int CHUNKS>
+__global__ void __launch_bounds__(kWarpRows * 32)
+add_rmsnorm_bf16_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                             const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                             __nv_bfloat16* __restrict__ res_out, int64_t rows, float eps) {
+  constexpr int d = CHUNKS * 256;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpRows + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * d;
+  float v[CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    Bf16x8 a, r;
+    a.u = *reinterpret_cast<const uint4*>(xr + c * 256 + lane * 8);
+    if (residual) r.u = *reinterpret_cast<const uint4*>(residual + row * d + c * 256 + lane * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float f = __bfloat162float(a.b[i]);
+      if (residual) f += __bfloat162float(r.b[i]);
+      v[c][i] = f;
+      ss += f * f;
+    }
+  }
+  const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(d) + eps);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const float4 w0 = *reinterpret_cast<const float4*>(w + c * 256 + lane * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(w + c * 256 + lane * 8 + 4);
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    Bf16x8 o, ro;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o.b[i] = __float2bfloat16(ww[i] * v[c][i] * inv);
+      ro.b[i] = __float2bfloat16(v[c][i]);
+    }
+    *reinterpret_cast<uint4*>(y + row * d + c * 256 + lane * 8) = o.u;
+    if (res_out) *reinterpret_cast<uint4*>(res_out + row * d + c * 256 + lane * 8) = ro.u;
+  }
+}
+
+// Hq*D and Hkv*D multiples of 256, D in {32, 64, 128, 256}: a lane's 8 elements and their RoPE
+// partners (half a head away) sit in the same 256-element chunk, (D/2)/8 lanes apart.
+__global__ void __launch_bounds__(kWarpRows * 32)
+qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
+  using T = __nv_bfloat16;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarpRows + (threadIdx.x >> 5);
+  if (t >= num_tokens) return;
+  const int Wq = a.Hq * a.D, Wk = a.Hkv * a.D, half = a.D / 2, partner = half / 8;
+  const T* qr = static_cast<const T*>(a.qkv) + t * a.qkv_stride;
+  const T* kr = qr + Wq;
+  const T* vr = kr + Wk;
+  float sq = 0.f, sk = 0.f;
+  for (int c = lane * 8; c < Wq; c += 256) {
+    Bf16x8 u;
+    u.u = *reinterpret_cast<const uint4*>(qr + c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = __bfloat162float(u.b[i]);
+      sq += f * f;
+    }
+  }
+  for (int c = lane * 8; c < Wk; c += 256) {
+    Bf16x8 u;
+    u.u = *reinterpret_cast<const uint4*>(kr + c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = __bfloat162float(u.b[i]);
+      sk += f * f;
+    }
+  }
+  const float iq = rsqrtf(warp_sum(sq) / static_cast<float>(Wq) + a.eps);
+  const float ik = rsqrtf(warp_sum(sk) / static_cast<float>(Wk) + a.eps);
+  int64_t pos = a.positions[t];
+  if (pos < 0 || pos >= a.max_pos) {
+    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
+    pos = pos < 0 ? 0 : a.max_pos - 1;
+  }
+  const float* cs = a.rope + pos * a.D;
+  int64_t slot = a.k_cache ? a.slots[t] : -1;
+  if (slot >= a.num_slots) {
+    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
+    slot = -1;
+  }
+  // one 256-element chunk of q or k: normalise, round, rotate, round
+  auto rotate = [&](const T* src, const float* nw, float inv, int c) -> uint4 {
+    Bf16x8 u, o;
+    u.u = *reinterpret_cast<const uint4*>(src + c);
+    const float4 w0 = *reinterpret_cast<const float4*>(nw + c), w1 = *reinterpret_cast<const float4*>(nw + c + 4);
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const int j = c % a.D;
+    const bool first = j < half;
+    const int jj = first ? j : j - half;
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + jj), c1 = *reinterpret_cast<const float4*>(cs + jj + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cs + half + jj);
+    const float4 s1 = *reinterpret_cast<const float4*>(cs + half + jj + 4);
+    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float xv = __bfloat162float(__float2bfloat16(__bfloat162float(u.b[i]) * inv * ww[i]));
+      const float pv = __shfl_xor_sync(0xffffffffu, xv, partner);
+      o.b[i] = __float2bfloat16(first ? xv * cc[i] - pv * sn[i] : xv * cc[i] + pv * sn[i]);
+    }
+    return o.u;
+  };
+  T* qo = static_cast<T*>(a.q_out) + t * Wq;
+  for (int c = lane * 8; c < Wq; c += 256) *reinterpret_cast<uint4*>(qo + c) = rotate(qr, a.q_norm_w, iq, c);
+  T* ko = static_cast<T*>(a.k_out) + t * Wk;
+  T* kc = slot >= 0 ? static_cast<T*>(a.k_cache) + slot * Wk : nullptr;
+  T* vc = slot >= 0 ? static_cast<T*>(a.v_cache) + slot * Wk : nullptr;
+  for (int c = lane * 8; c < Wk; c += 256) {
+    const uint4 o = rotate(kr, a.k_norm_w, ik, c);
+    *reinterpret_cast<uint4*>(ko + c) = o;
+    if (kc) {
+      *reinterpret_cast<uint4*>(kc + c) = o;
+      *reinterpret_cast<uint4*>(vc + c) = *reinterpret_cast<const uint4*>(vr + c);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -151,6 +285,23 @@ extern "C" int b200_add_rmsnorm(const void* x, const void* residual, const float
   if (num_rows > 2147483647) return B200_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = static_cast<int>(num_rows);
+  if (dtype == B200_DTYPE_BF16 && (!residual || residual_dtype == B200_DTYPE_BF16) && dim % 256 == 0 &&
+      dim <= 2048 && aligned16(x) && aligned16(y) && aligned16(weight) && (!residual || aligned16(residual)) &&
+      (!residual_out || aligned16(residual_out))) {
+    const int wgrid = static_cast<int>((num_rows + kWarpRows - 1) / kWarpRows);
+#define WARP_LAUNCH(C)                                                                               \
+  case C:                                                                                            \
+    add_rmsnorm_bf16_warp_kernel<C><<<wgrid, kWarpRows * 32, 0, s>>>(                                \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual), weight,   \
+        static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(residual_out), num_rows, eps);   \
+    break
+    switch (dim / 256) {
+      WARP_LAUNCH(1); WARP_LAUNCH(2); WARP_LAUNCH(3); WARP_LAUNCH(4);
+      WARP_LAUNCH(5); WARP_LAUNCH(6); WARP_LAUNCH(7); WARP_LAUNCH(8);
+    }
+#undef WARP_LAUNCH
+    return launch_result();
+  }
   const bool rf32 = !residual || residual_dtype == B200_DTYPE_F32;
 #define LAUNCH(T, R)                                                                               \
   add_rmsnorm_kernel<T, R><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x),                     \
@@ -207,6 +358,15 @@ extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride
   a.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = static_cast<int>(num_tokens);
+  const int Wq = num_q_heads * head_dim, Wk = num_kv_heads * head_dim;
+  const bool d_ok = head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256;
+  if (dtype == B200_DTYPE_BF16 && d_ok && Wq % 256 == 0 && Wk % 256 == 0 && qkv_token_stride % 8 == 0 &&
+      aligned16(qkv) && aligned16(q_norm_weight) && aligned16(k_norm_weight) && aligned16(rope_table) &&
+      aligned16(q_out) && aligned16(k_out) && (!k_cache || (aligned16(k_cache) && aligned16(v_cache)))) {
+    const int wgrid = static_cast<int>((num_tokens + kWarpRows - 1) / kWarpRows);
+    qk_norm_rope_store_bf16_warp_kernel<<<wgrid, kWarpRows * 32, 0, s>>>(a, num_tokens);
+    return launch_result();
+  }
   if (dtype == B200_DTYPE_F32)
     qk_norm_rope_store_kernel<float><<<grid, kThreads, 0, s>>>(a);
   else

@@ -1,23 +1,28 @@
-// MoE routing for inference in one launch: gate scores -> top-k experts per token -> renormalised
-// weights -> rows grouped by expert for a grouped GEMM, plus the inverse permutation for the combine.
+// MoE routing for inference: gate scores -> top-k experts per token -> renormalised weights -> rows
+// grouped by expert for a grouped GEMM, plus the inverse permutation for the combine.
 //
 // Arithmetic is Gate.forward of the reference (model/architecture/moe.py:45-90) with the roundings of
 // its dtype: scores = sigmoid(logits); selection by top-k of logits + expert_bias (bias cast to the
 // dtype first); weights = scores of the selected experts divided by (their sum + 1e-10).  Ties in
 // the biased logits go to the lower expert index.
 //
-// Output rows are ordered by (expert, token, expert rank within the token): a stable counting sort.
-// A single CTA does the whole batch (up to 65,536 (token, expert) rows): every thread ranks a
-// contiguous chunk of rows with a private per-expert histogram, one warp per expert scans the
-// histograms across threads, and each thread then scatters its rows to their final positions.
+// Output rows are ordered by (expert, token): a stable counting sort.  One thread owns one token and
+// a CTA owns 256 consecutive tokens.  A token selects an expert at most once, so "my token uses
+// expert e" is one bit per thread: a warp ballot per expert gives both the warp's count and the
+// thread's rank inside the warp.  With more than one CTA a first launch writes every CTA's
+// per-expert counts to the workspace; the scatter launch sums them (all CTAs -> expert totals,
+// earlier CTAs -> this CTA's first row of every expert) and writes the rows.  A batch that fits one
+// CTA (decode) needs the scatter launch only.
 #include "common.cuh"
 
 namespace b200 {
 namespace {
 
-constexpr int kThreads = 1024;
-constexpr int kMaxE = 32;   // 32 x 1024 int32 histogram = 128 KiB of shared memory
+constexpr int kTok = 256;     // tokens (= threads) per CTA
+constexpr int kWarps = kTok / 32;
+constexpr int kMaxE = 64;
 constexpr int kMaxK = 8;
+constexpr int kMaxTokens = 65536;
 
 template <typename T>
 __device__ __forceinline__ float round_to(float v) {
@@ -33,122 +38,283 @@ struct RouteArgs {
   void* sorted_weight;      // [T*K]  dtype, routing weight of sorted row i
   int32_t* offsets;         // [E]    end (exclusive) of each expert's rows
   int32_t* slot_to_row;     // [T, K] sorted-row index of token t's j-th expert in ascending expert order
+  int32_t* cta_counts;      // [gridDim.x, E] workspace (unused with one CTA)
 };
 
+// bit e set: token t routes to expert e
 template <typename T>
-__global__ void __launch_bounds__(kThreads) moe_route_kernel(const RouteArgs a) {
-  extern __shared__ uint8_t smem[];
-  // hist[e][thread]: rows of expert e owned by `thread`, later their exclusive prefix over threads
-  int32_t* hist = reinterpret_cast<int32_t*>(smem);                 // [E][kThreads]
-  int32_t* expert_base = hist + a.E * kThreads;                     // [E + 1]
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int NT = a.T, E = a.E, K = a.K;
-  const int per_thread = (NT + kThreads - 1) / kThreads;
-  const int t0 = tid * per_thread, t1 = min(NT, t0 + per_thread);
-
-  for (int e = 0; e < E; ++e) hist[e * kThreads + tid] = 0;
-  // pass 1: count.  The top-k is recomputed in pass 2 (cheap: E <= 32) instead of being stored.
-  auto select = [&](int t, int (&sel)[kMaxK], float (&wsel)[kMaxK]) {
-    const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * E;
-    float biased[kMaxE];
-    for (int e = 0; e < E; ++e) {
-      const float lg = to_float<T>(row[e]);
-      biased[e] = round_to<T>(lg + round_to<T>(a.bias[e]));
-    }
-    unsigned long long taken = 0ull;
-    for (int k = 0; k < K; ++k) {            // k maxima, lower index first among equals
-      int best = -1;
-      float bv = -INFINITY;
-      for (int e = 0; e < E; ++e)
-        if (!((taken >> e) & 1ull) && (best < 0 || biased[e] > bv)) {
-          best = e;
-          bv = biased[e];
-        }
-      taken |= 1ull << best;
-    }
-    float sum = 0.f;
-    int n = 0;
-    for (int e = 0; e < E; ++e)               // ascending expert order
-      if ((taken >> e) & 1ull) {
-        sel[n] = e;
-        wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
-        sum += wsel[n];
-        ++n;
+__device__ __forceinline__ unsigned long long select_mask(const RouteArgs& a, int t) {
+  const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * a.E;
+  float biased[kMaxE];
+#pragma unroll 4
+  for (int e = 0; e < a.E; ++e)
+    biased[e] = round_to<T>(to_float<T>(row[e]) + round_to<T>(a.bias[e]));
+  unsigned long long taken = 0ull;
+  for (int k = 0; k < a.K; ++k) {            // k maxima, lower index first among equals
+    int best = -1;
+    float bv = -INFINITY;
+    for (int e = 0; e < a.E; ++e)
+      if (!((taken >> e) & 1ull) && (best < 0 || biased[e] > bv)) {
+        best = e;
+        bv = biased[e];
       }
-    if (K > 1) {
-      const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
-      for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
-    }
-  };
-
-  for (int t = t0; t < t1; ++t) {
-    int sel[kMaxK];
-    float wsel[kMaxK];
-    select(t, sel, wsel);
-    for (int k = 0; k < K; ++k) hist[sel[k] * kThreads + tid] += 1;
+    taken |= 1ull << best;
   }
+  return taken;
+}
+
+// per-warp counts of every expert into warp_cnt[warp][e]; ranks[n] = number of lower lanes of the warp
+// that also use the n-th (ascending) expert of this thread's token
+__device__ __forceinline__ void warp_counts(unsigned long long taken, int E, int32_t (*warp_cnt)[kMaxE],
+                                            int* ranks) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  int n = 0;
+  for (int e = 0; e < E; ++e) {
+    const bool mine = (taken >> e) & 1ull;
+    const unsigned b = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) warp_cnt[warp][e] = __popc(b);
+    if (mine && n < kMaxK) ranks[n++] = __popc(b & lt);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTok) moe_count_kernel(const RouteArgs a) {
+  __shared__ int32_t warp_cnt[kWarps][kMaxE];
+  const int t = blockIdx.x * kTok + threadIdx.x;
+  const unsigned long long taken = t < a.T ? select_mask<T>(a, t) : 0ull;
+  int ranks[kMaxK];
+  warp_counts(taken, a.E, warp_cnt, ranks);
   __syncthreads();
-  // exclusive scan over threads, one warp per expert (round-robin), 32 threads' counts per trip
-  for (int e = warp; e < E; e += kThreads / 32) {
-    int carry = 0;
-    for (int base = 0; base < kThreads; base += 32) {
-      const int v = hist[e * kThreads + base + lane];
-      int x = v;
+  if (threadIdx.x < a.E) {
+    int s = 0;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x += y;
+    for (int w = 0; w < kWarps; ++w) s += warp_cnt[w][threadIdx.x];
+    a.cta_counts[blockIdx.x * a.E + threadIdx.x] = s;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
+  __shared__ int32_t warp_cnt[kWarps][kMaxE];
+  __shared__ int32_t part_total[kWarps][kMaxE], part_before[kWarps][kMaxE];
+  __shared__ int32_t base[kMaxE];     // first output row of this CTA's rows of expert e
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int E = a.E, K = a.K;
+  const int t = blockIdx.x * kTok + tid;
+  const unsigned long long taken = t < a.T ? select_mask<T>(a, t) : 0ull;
+  int ranks[kMaxK];
+  warp_counts(taken, E, warp_cnt, ranks);
+  // rows of every expert in all CTAs (total) and in the CTAs before this one (before)
+  if (gridDim.x > 1) {
+    for (int e = lane; e < E; e += 32) {
+      int tot = 0, bef = 0;
+      for (int c = warp; c < static_cast<int>(gridDim.x); c += kWarps) {
+        const int v = a.cta_counts[c * E + e];
+        tot += v;
+        if (c < static_cast<int>(blockIdx.x)) bef += v;
       }
-      hist[e * kThreads + base + lane] = carry + x - v;
-      carry += __shfl_sync(0xffffffffu, x, 31);
+      part_total[warp][e] = tot;
+      part_before[warp][e] = bef;
     }
-    if (lane == 0) expert_base[e + 1] = carry;   // rows of expert e
   }
   __syncthreads();
   if (tid == 0) {
-    expert_base[0] = 0;
+    int run = 0;
     for (int e = 0; e < E; ++e) {
-      expert_base[e + 1] += expert_base[e];
-      a.offsets[e] = expert_base[e + 1];
+      int tot = 0, bef = 0;
+      for (int w = 0; w < kWarps; ++w) {
+        if (gridDim.x > 1) {
+          tot += part_total[w][e];
+          bef += part_before[w][e];
+        } else {
+          tot += warp_cnt[w][e];
+        }
+      }
+      base[e] = run + bef;
+      run += tot;
+      if (blockIdx.x == 0) a.offsets[e] = run;
     }
   }
   __syncthreads();
-  // pass 2: scatter rows to expert_base[e] + (rows of e in earlier threads) + (earlier rows of this thread)
-  int local[kMaxE];
-  for (int e = 0; e < E; ++e) local[e] = 0;
+  if (t >= a.T) return;
+  // routing weights of the selected experts, ascending expert order
+  const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * E;
+  int sel[kMaxK];
+  float wsel[kMaxK];
+  float sum = 0.f;
+  int n = 0;
+  for (int e = 0; e < E; ++e)
+    if ((taken >> e) & 1ull) {
+      sel[n] = e;
+      wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
+      sum += wsel[n];
+      ++n;
+    }
+  if (K > 1) {
+    const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
+    for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
+  }
   T* wout = static_cast<T*>(a.sorted_weight);
-  for (int t = t0; t < t1; ++t) {
-    int sel[kMaxK];
-    float wsel[kMaxK];
-    select(t, sel, wsel);
-    for (int k = 0; k < K; ++k) {
-      const int e = sel[k];
-      const int pos = expert_base[e] + hist[e * kThreads + tid] + local[e]++;
-      a.sorted_token[pos] = t;
-      a.sorted_expert[pos] = e;
-      wout[pos] = from_float<T>(wsel[k]);
-      a.slot_to_row[t * K + k] = pos;
+  for (int k = 0; k < K; ++k) {
+    const int e = sel[k];
+    int pos = base[e] + ranks[k];
+    for (int w = 0; w < warp; ++w) pos += warp_cnt[w][e];
+    a.sorted_token[pos] = t;
+    a.sorted_expert[pos] = e;
+    wout[pos] = from_float<T>(wsel[k]);
+    a.slot_to_row[t * K + k] = pos;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU over fused up-projection rows: act[r, j] = silu(h[r, j] + b[e_r, j]) * (h[r, F + j] + b[e_r, F + j])
+// with every intermediate rounded to the dtype (bias add, silu, product), as the tensor-op sequence
+// add -> silu -> mul on dtype tensors rounds.
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const T* __restrict__ h, const T* __restrict__ bias, const int32_t* __restrict__ row_expert,
+              T* __restrict__ act, int64_t rows, int F) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * F) return;
+  const int64_t r = i / F;
+  const int j = static_cast<int>(i - r * F);
+  float g = to_float<T>(h[r * 2 * F + j]), u = to_float<T>(h[r * 2 * F + F + j]);
+  if (bias) {
+    const T* b = bias + static_cast<int64_t>(row_expert ? row_expert[r] : 0) * 2 * F;
+    g = round_to<T>(g + to_float<T>(b[j]));
+    u = round_to<T>(u + to_float<T>(b[F + j]));
+  }
+  const float s = round_to<T>(g / (1.f + expf(-g)));
+  act[r * F + j] = from_float<T>(s * u);
+}
+
+// bf16, F % 8 == 0: eight outputs per thread with 16-byte loads
+__global__ void __launch_bounds__(256)
+swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ bias,
+                     const int32_t* __restrict__ row_expert, __nv_bfloat16* __restrict__ act, int64_t rows,
+                     int F) {
+  const int F8 = F >> 3;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * F8) return;
+  const int64_t r = i / F8;
+  const int j = static_cast<int>(i - r * F8) << 3;
+  union V {
+    uint4 u;
+    __nv_bfloat16 b[8];
+  };
+  V g, u, bg, bu, o;
+  g.u = *reinterpret_cast<const uint4*>(h + r * 2 * F + j);
+  u.u = *reinterpret_cast<const uint4*>(h + r * 2 * F + F + j);
+  if (bias) {
+    const __nv_bfloat16* b = bias + static_cast<int64_t>(row_expert ? row_expert[r] : 0) * 2 * F;
+    bg.u = *reinterpret_cast<const uint4*>(b + j);
+    bu.u = *reinterpret_cast<const uint4*>(b + F + j);
+  }
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    float gv = __bfloat162float(g.b[x]), uv = __bfloat162float(u.b[x]);
+    if (bias) {
+      gv = round_to<__nv_bfloat16>(gv + __bfloat162float(bg.b[x]));
+      uv = round_to<__nv_bfloat16>(uv + __bfloat162float(bu.b[x]));
+    }
+    const float s = round_to<__nv_bfloat16>(gv / (1.f + expf(-gv)));
+    o.b[x] = __float2bfloat16(s * uv);
+  }
+  *reinterpret_cast<uint4*>(act + r * F + j) = o.u;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Combine: out[t] = sum over the token's K expert rows in ascending expert order of
+// round(round(y[row] + b2[e]) * w[row]), every partial sum rounded to the dtype (the reference
+// accumulates with scatter_add_ in the activation dtype, moe.py:312-339), then + shared[t].
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_kernel(const T* __restrict__ y, const T* __restrict__ bias, const int32_t* __restrict__ row_expert,
+               const T* __restrict__ row_weight, const int32_t* __restrict__ slot_to_row,
+               const T* __restrict__ shared, T* __restrict__ out, int64_t tokens, int K, int d) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= tokens * d) return;
+  const int64_t t = i / d;
+  const int j = static_cast<int>(i - t * d);
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int row = slot_to_row[t * K + k];
+    float v = to_float<T>(y[static_cast<int64_t>(row) * d + j]);
+    if (bias) v = round_to<T>(v + to_float<T>(bias[static_cast<int64_t>(row_expert[row]) * d + j]));
+    v = round_to<T>(v * to_float<T>(row_weight[row]));
+    acc = k == 0 ? v : round_to<T>(acc + v);
+  }
+  if (shared) acc = round_to<T>(acc + to_float<T>(shared[i]));
+  out[i] = from_float<T>(acc);
+}
+
+__global__ void __launch_bounds__(256)
+combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ bias,
+                      const int32_t* __restrict__ row_expert, const __nv_bfloat16* __restrict__ row_weight,
+                      const int32_t* __restrict__ slot_to_row, const __nv_bfloat16* __restrict__ shared,
+                      __nv_bfloat16* __restrict__ out, int64_t tokens, int K, int d) {
+  const int d8 = d >> 3;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= tokens * d8) return;
+  const int64_t t = i / d8;
+  const int j = static_cast<int>(i - t * d8) << 3;
+  union V {
+    uint4 u;
+    __nv_bfloat16 b[8];
+  };
+  float acc[8];
+  for (int k = 0; k < K; ++k) {
+    const int row = slot_to_row[t * K + k];
+    V v, b;
+    v.u = *reinterpret_cast<const uint4*>(y + static_cast<int64_t>(row) * d + j);
+    if (bias) b.u = *reinterpret_cast<const uint4*>(bias + static_cast<int64_t>(row_expert[row]) * d + j);
+    const float w = __bfloat162float(row_weight[row]);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      float f = __bfloat162float(v.b[x]);
+      if (bias) f = round_to<__nv_bfloat16>(f + __bfloat162float(b.b[x]));
+      f = round_to<__nv_bfloat16>(f * w);
+      acc[x] = k == 0 ? f : round_to<__nv_bfloat16>(acc[x] + f);
     }
   }
+  V o;
+  if (shared) {
+    V s;
+    s.u = *reinterpret_cast<const uint4*>(shared + t * d + j);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) acc[x] = acc[x] + __bfloat162float(s.b[x]);
+  }
+#pragma unroll
+  for (int x = 0; x < 8; ++x) o.b[x] = __float2bfloat16(acc[x]);
+  *reinterpret_cast<uint4*>(out + t * d + j) = o.u;
 }
 
 }  // namespace
 }  // namespace b200
 
+extern "C" size_t b200_moe_route_workspace_bytes(int32_t num_tokens, int32_t num_experts) {
+  if (num_tokens <= b200::kTok || num_experts <= 0) return 0;
+  const size_t ctas = (static_cast<size_t>(num_tokens) + b200::kTok - 1) / b200::kTok;
+  return ctas * static_cast<size_t>(num_experts) * sizeof(int32_t);
+}
+
 extern "C" int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t num_tokens,
                               int32_t num_experts, int32_t top_k, int32_t* sorted_token,
                               int32_t* sorted_expert, void* sorted_weight, int32_t* expert_offsets,
-                              int32_t* slot_to_row, int32_t dtype, void* stream) {
+                              int32_t* slot_to_row, void* workspace, size_t workspace_bytes, int32_t dtype,
+                              void* stream) {
   using namespace b200;
   if (num_tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts) return B200_ERR_ARG;
   if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
-  if (num_experts > kMaxE || top_k > kMaxK || static_cast<int64_t>(num_tokens) * top_k > 65536)
-    return B200_ERR_UNSUPPORTED;
+  if (num_experts > kMaxE || top_k > kMaxK || num_tokens > kMaxTokens) return B200_ERR_UNSUPPORTED;
   if (!expert_offsets) return B200_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (num_tokens > 0 &&
       (!gate_logits || !expert_bias || !sorted_token || !sorted_expert || !sorted_weight || !slot_to_row))
     return B200_ERR_ARG;
+  const size_t need = b200_moe_route_workspace_bytes(num_tokens, num_experts);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return B200_ERR_WORKSPACE;
   RouteArgs a{};
   a.logits = gate_logits;
   a.bias = expert_bias;
@@ -160,18 +326,77 @@ extern "C" int b200_moe_route(const void* gate_logits, const float* expert_bias,
   a.sorted_weight = sorted_weight;
   a.offsets = expert_offsets;
   a.slot_to_row = slot_to_row;
-  const size_t smem = (static_cast<size_t>(num_experts) * kThreads + num_experts + 1) * sizeof(int32_t);
-  static bool configured[64][2] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const int di = dtype == B200_DTYPE_F32 ? 0 : 1;
-  auto kern = di == 0 ? moe_route_kernel<float> : moe_route_kernel<__nv_bfloat16>;
-  if (dev >= 0 && dev < 64 && !configured[dev][di]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (kMaxE * kThreads + kMaxE + 1) * 4) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    configured[dev][di] = true;
+  a.cta_counts = static_cast<int32_t*>(workspace);
+  const int grid = num_tokens == 0 ? 1 : (num_tokens + kTok - 1) / kTok;   // 0 tokens: offsets = 0
+  if (dtype == B200_DTYPE_F32) {
+    if (grid > 1) moe_count_kernel<float><<<grid, kTok, 0, s>>>(a);
+    moe_scatter_kernel<float><<<grid, kTok, 0, s>>>(a);
+  } else {
+    if (grid > 1) moe_count_kernel<__nv_bfloat16><<<grid, kTok, 0, s>>>(a);
+    moe_scatter_kernel<__nv_bfloat16><<<grid, kTok, 0, s>>>(a);
   }
-  kern<<<1, kThreads, smem, s>>>(a);
+  return launch_result();
+}
+
+extern "C" int b200_swiglu(const void* h, const void* bias, const int32_t* row_expert, void* act,
+                           int64_t num_rows, int32_t d_ff, int32_t dtype, void* stream) {
+  using namespace b200;
+  if (num_rows < 0 || d_ff <= 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (num_rows == 0) return B200_OK;
+  if (!h || !act) return B200_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = dtype == B200_DTYPE_BF16 && d_ff % 8 == 0 && aligned16(h) && aligned16(act) &&
+                   (!bias || aligned16(bias));
+  const int64_t work = vec ? num_rows * (d_ff / 8) : num_rows * d_ff;
+  const int64_t grid = (work + 255) / 256;
+  if (grid > 2147483647) return B200_ERR_TOO_LARGE;
+  if (vec)
+    swiglu_bf16x8_kernel<<<static_cast<int>(grid), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(bias), row_expert,
+        static_cast<__nv_bfloat16*>(act), num_rows, d_ff);
+  else if (dtype == B200_DTYPE_BF16)
+    swiglu_kernel<__nv_bfloat16><<<static_cast<int>(grid), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(bias), row_expert,
+        static_cast<__nv_bfloat16*>(act), num_rows, d_ff);
+  else
+    swiglu_kernel<float><<<static_cast<int>(grid), 256, 0, s>>>(
+        static_cast<const float*>(h), static_cast<const float*>(bias), row_expert, static_cast<float*>(act),
+        num_rows, d_ff);
+  return launch_result();
+}
+
+extern "C" int b200_moe_combine(const void* expert_out, const void* bias, const int32_t* row_expert,
+                                const void* row_weight, const int32_t* slot_to_row, const void* shared,
+                                void* out, int64_t num_tokens, int32_t top_k, int32_t d_model,
+                                int32_t dtype, void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || top_k <= 0 || d_model <= 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (num_tokens == 0) return B200_OK;
+  if (!expert_out || !row_weight || !slot_to_row || !out || (bias && !row_expert)) return B200_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = dtype == B200_DTYPE_BF16 && d_model % 8 == 0 && aligned16(expert_out) &&
+                   aligned16(out) && (!bias || aligned16(bias)) && (!shared || aligned16(shared));
+  const int64_t work = vec ? num_tokens * (d_model / 8) : num_tokens * d_model;
+  const int64_t grid = (work + 255) / 256;
+  if (grid > 2147483647) return B200_ERR_TOO_LARGE;
+  if (vec)
+    combine_bf16x8_kernel<<<static_cast<int>(grid), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(expert_out), static_cast<const __nv_bfloat16*>(bias), row_expert,
+        static_cast<const __nv_bfloat16*>(row_weight), slot_to_row,
+        static_cast<const __nv_bfloat16*>(shared), static_cast<__nv_bfloat16*>(out), num_tokens, top_k,
+        d_model);
+  else if (dtype == B200_DTYPE_BF16)
+    combine_kernel<__nv_bfloat16><<<static_cast<int>(grid), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(expert_out), static_cast<const __nv_bfloat16*>(bias), row_expert,
+        static_cast<const __nv_bfloat16*>(row_weight), slot_to_row,
+        static_cast<const __nv_bfloat16*>(shared), static_cast<__nv_bfloat16*>(out), num_tokens, top_k,
+        d_model);
+  else
+    combine_kernel<float><<<static_cast<int>(grid), 256, 0, s>>>(
+        static_cast<const float*>(expert_out), static_cast<const float*>(bias), row_expert,
+        static_cast<const float*>(row_weight), slot_to_row, static_cast<const float*>(shared),
+        static_cast<float*>(out), num_tokens, top_k, d_model);
   return launch_result();
 }

@@ -73,6 +73,10 @@ class ModelRunner:
         self.max_num_seqs = _cfg(config, "max_num_sequences", "max_num_seqs", default=16)
         self.max_model_length = _cfg(config, "max_model_length", default=None)
         self.device = torch.device(_cfg(config, "device", default="cuda:0"))
+        # prefill batches are padded to a multiple of this many tokens (ids 0, slot -1, in no sequence):
+        # the GEMM library then meets a few dozen distinct row counts instead of a new one every step,
+        # and its per-shape algorithm selection (~0.1 ms per new shape per GEMM) is paid once
+        self.prefill_token_multiple = int(_cfg(config, "prefill_token_multiple", default=256))
         torch.cuda.set_device(self.device)
         dtype = _cfg(config, "dtype", default=torch.float32)
         self.dtype = getattr(torch, dtype) if isinstance(dtype, str) else dtype
@@ -137,6 +141,12 @@ class ModelRunner:
         if len(m.slot_mapping) != len(m.input_ids):
             raise RuntimeError("slot_mapping and input_ids disagree: Sequence.reference_exact must be off "
                                "when the model runs (it reproduces a reference defect at block multiples)")
+        mult = self.prefill_token_multiple
+        if m.is_prefill and mult > 1 and len(m.input_ids) % mult:
+            pad = mult - len(m.input_ids) % mult
+            arrays["input_ids"] = np.concatenate([m.input_ids, np.zeros(pad, dtype=m.input_ids.dtype)])
+            arrays["positions"] = np.concatenate([m.positions, np.zeros(pad, dtype=m.positions.dtype)])
+            arrays["slot_mapping"] = np.concatenate([m.slot_mapping, np.full(pad, -1, dtype=m.slot_mapping.dtype)])
         t = self.staging.upload(arrays)
         set_context(m.is_prefill, t.get("cu_seqlens_q"), t.get("cu_seqlens_k"), m.max_seqlen_q, m.max_seqlen_k,
                     t["slot_mapping"], t.get("context_lens"), t.get("block_tables"), t["positions"])

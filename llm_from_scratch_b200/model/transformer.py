@@ -95,6 +95,8 @@ class MLP(nn.Module):
 
     def forward(self, x):
         h = F.linear(x, self.w13, self.b13)
+        if h.dtype == torch.bfloat16 and h.is_cuda and h.dim() == 2:
+            return F.linear(ops.swiglu(h), self.w2, self.b2)     # silu(h1) * h3 in one kernel
         return F.linear(F.silu(h[..., :self.d_ff]) * h[..., self.d_ff:], self.w2, self.b2)
 
 
@@ -143,9 +145,8 @@ class MoE(nn.Module):
 
     def forward(self, x):
         if (x.dtype == torch.bfloat16 and self.use_grouped and self.E <= ops.MOE_ROUTE_MAX_EXPERTS
-                and self.K <= ops.MOE_ROUTE_MAX_TOPK and x.shape[0] * self.K <= ops.MOE_ROUTE_MAX_ROWS):
-            out = self.forward_routed(x)
-            return out + self.shared(x) if self.shared is not None else out
+                and self.K <= ops.MOE_ROUTE_MAX_TOPK and x.shape[0] <= ops.MOE_ROUTE_MAX_TOKENS):
+            return self.forward_routed(x)
         idx, wts = self.route(x)
         if x.dtype == torch.bfloat16 and self.use_grouped:
             out = self.forward_grouped(x, idx, wts)
@@ -175,20 +176,15 @@ class MoE(nn.Module):
         return out
 
     def forward_routed(self, x):
-        """bf16 fast path: one routing kernel (top-k, weights, grouping by expert), two grouped GEMMs,
-        and a gather-based combine that adds every token's K contributions in ascending expert order."""
-        T, K = x.shape[0], self.K
-        tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, K)
+        """bf16 fast path: routing kernel (top-k, weights, grouping by expert), two grouped GEMMs with
+        the bias + SwiGLU between them in one kernel, and one combine kernel that adds every token's
+        K contributions in ascending expert order and then the shared expert."""
+        tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K)
         xs = x.index_select(0, tok)
-        h = torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs) + self.b13.index_select(0, experts)
-        act = F.silu(h[:, :self.d_ff]) * h[:, self.d_ff:]
-        y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs) + self.b2.index_select(0, experts)
-        y = y * w.unsqueeze(1)
-        yt = y.index_select(0, inv.reshape(-1)).view(T, K, -1)
-        out = yt[:, 0]
-        for k in range(1, K):
-            out = out + yt[:, k]
-        return out
+        act = ops.swiglu(torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs), self.b13, experts)
+        y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs)
+        shared = self.shared(x) if self.shared is not None else None
+        return ops.moe_combine(y, self.b2, experts, w, inv, shared)
 
     def forward_grouped(self, x, idx, wts):
         """bf16: rows sorted by expert, two grouped GEMMs with device-side group offsets, then the
@@ -240,7 +236,7 @@ class GQAAttention(nn.Module):
         # views into the pool; set by ModelRunner.allocate_kv_cache (model_runner.py:186-190)
         self.k_cache = self.v_cache = torch.empty(0)
 
-    def forward(self, x, ctx, positions):
+    def forward(self, x, ctx, positions, out=None):
         T = x.shape[0]
         kvw = self.Hkv * self.hd
         qkv = F.linear(x.to(self.dtype), self.w_qkv, self.b_qkv)
@@ -259,10 +255,11 @@ class GQAAttention(nn.Module):
         if ctx.is_prefill:
             if ctx.block_tables is not None:   # part of the context is already cached
                 o = ops.prefill_varlen(q, None, None, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                       ctx.max_seqlen_k, self.scale, self.k_cache, self.v_cache, ctx.block_tables)
+                                       ctx.max_seqlen_k, self.scale, self.k_cache, self.v_cache, ctx.block_tables,
+                                       out=out)
             else:
                 o = ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                       ctx.max_seqlen_k, self.scale)
+                                       ctx.max_seqlen_k, self.scale, out=out)
         else:
             o = ops.paged_decode_gqa(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens, self.scale)
         return F.linear(o.view(T, self.d), self.w_o, self.b_o)
@@ -287,7 +284,7 @@ class MLAAttention(nn.Module):
         self.dtype = p.dtype
         self.latent_cache = torch.empty(0)   # [num_blocks, block_size, r + dr]; set by the runner
 
-    def forward(self, x, ctx, positions):
+    def forward(self, x, ctx, positions, out=None):
         T, H, hd, r, dr = x.shape[0], self.H, self.hd, self.r, self.dr
         x = x.to(self.dtype)
         qc = _vector_norm(F.linear(x, self.w_qd, self.b_qd), self.q_norm)
@@ -301,7 +298,7 @@ class MLAAttention(nn.Module):
         if self.latent_cache.numel():
             ops.store_rows(rows, self.latent_cache, ctx.slot_mapping)
         if ctx.is_prefill:
-            o = self._prefill(q_nope, q_rope, rows, ctx)
+            o = self._prefill(q_nope, q_rope, rows, ctx, out)
         else:
             q_abs = torch.einsum("thd,hdk->thk", q_nope, self.w_uk)          # absorb W_UK (MLA.py:153)
             lat = ops.mla_decode(q_abs.contiguous(), q_rope.contiguous(), self.latent_cache, ctx.block_tables,
@@ -309,7 +306,7 @@ class MLAAttention(nn.Module):
             o = torch.einsum("thk,hdk->thd", lat, self.w_uv)                 # absorb W_UV (MLA.py:178)
         return F.linear(o.reshape(T, H * hd), self.w_o, self.b_o)
 
-    def _prefill(self, q_nope, q_rope, rows, ctx):
+    def _prefill(self, q_nope, q_rope, rows, ctx, out=None):
         """Causal attention of the packed new tokens over their contexts.
 
         Prefill expands the latent rows once per step instead of absorbing the up-projections into
@@ -326,7 +323,7 @@ class MLAAttention(nn.Module):
         v = torch.einsum("tk,hdk->thd", c, self.w_uv).contiguous()
         q = torch.cat([q_nope, q_rope], dim=-1)
         return ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                  ctx.max_seqlen_k, self.scale)
+                                  ctx.max_seqlen_k, self.scale, out=out)
 
     def _gather_context_rows(self, ctx):
         """Packed latent rows of every sequence's full context, read back through the block tables."""
@@ -350,12 +347,12 @@ class DecoderLayer(nn.Module):
         self.att_norm, self.ffn_norm = p.f32(prefix + ".att_norm.weight"), p.f32(prefix + ".ffn_norm.weight")
         self.eps = cfg.rms_eps
 
-    def forward(self, x, residual, ctx, positions):
+    def forward(self, x, residual, ctx, positions, attn_out=None):
         if residual is None:
             h, residual = rms_norm(x, self.att_norm, self.eps), x
         else:
             h, residual = rms_norm(x, self.att_norm, self.eps, residual)
-        a = self.att(h, ctx, positions)
+        a = self.att(h, ctx, positions, attn_out)
         h, residual = rms_norm(a, self.ffn_norm, self.eps, residual)
         return self.ffn(h), residual
 
@@ -383,8 +380,15 @@ class EngineTransformerLM(nn.Module):
             positions = ctx.positions if ctx.positions is not None else ctx.context_lens - 1
         x = self.embed[input_ids]
         residual = None
+        attn_out = None
+        if ctx.is_prefill:
+            # one attention output buffer for all layers; rows of padding tokens (in no sequence) are
+            # never written by the kernel and stay zero
+            c = self.cfg
+            dv = c.head_dim
+            attn_out = torch.zeros(x.shape[0], c.num_heads, dv, dtype=self.dtype, device=x.device)
         for layer in self.layers:
-            x, residual = layer(x, residual, ctx, positions)
+            x, residual = layer(x, residual, ctx, positions, attn_out)
         h, _ = rms_norm(x, self.final_norm, self.cfg.rms_eps, residual)
         return h
 

@@ -293,7 +293,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torc
     return q, k, v
 
 
-MOE_ROUTE_MAX_EXPERTS, MOE_ROUTE_MAX_TOPK, MOE_ROUTE_MAX_ROWS = 32, 8, 65536
+MOE_ROUTE_MAX_EXPERTS, MOE_ROUTE_MAX_TOPK, MOE_ROUTE_MAX_TOKENS = 64, 8, 65536
 
 
 def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int):
@@ -309,10 +309,56 @@ def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int):
     w = torch.empty(n, dtype=gate_logits.dtype, device=dev)
     offs = torch.empty(E, dtype=torch.int32, device=dev)
     inv = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+    need = int(lib.b200_moe_route_workspace_bytes(T, E))
+    ws = workspace(dev, need, "moe_route") if need else None
     check(lib.b200_moe_route(gate_logits.data_ptr(), expert_bias.data_ptr(), T, E, top_k, tok.data_ptr(),
-                             exp.data_ptr(), w.data_ptr(), offs.data_ptr(), inv.data_ptr(), _dt(gate_logits),
-                             _stream()), "moe_route")
+                             exp.data_ptr(), w.data_ptr(), offs.data_ptr(), inv.data_ptr(),
+                             ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                             _dt(gate_logits), _stream()), "moe_route")
     return tok, exp, w, offs, inv
+
+
+def swiglu(h: torch.Tensor, bias: torch.Tensor | None = None, row_expert: torch.Tensor | None = None):
+    """act = silu(h[:, :F] + b1) * (h[:, F:] + b3) for h [rows, 2F]; ``bias`` [experts, 2F] is indexed by
+    ``row_expert`` [rows] int32 (row 0 without it); every intermediate is rounded to the dtype."""
+    _cuda(h, bias, row_expert)
+    rows, F2 = h.shape
+    if not h.is_contiguous() or F2 % 2:
+        raise ValueError("h must be contiguous [rows, 2*d_ff]")
+    if bias is not None and (bias.dtype != h.dtype or not bias.is_contiguous() or bias.shape[-1] != F2):
+        raise ValueError("bias must be contiguous [experts, 2*d_ff] in the dtype of h")
+    if row_expert is not None and (row_expert.dtype != torch.int32 or row_expert.numel() != rows):
+        raise ValueError("row_expert must be int32 [rows]")
+    act = torch.empty(rows, F2 // 2, dtype=h.dtype, device=h.device)
+    check(lib.b200_swiglu(h.data_ptr(), bias.data_ptr() if bias is not None else None,
+                          row_expert.data_ptr() if row_expert is not None else None, act.data_ptr(), rows,
+                          F2 // 2, _dt(h), _stream()), "swiglu")
+    return act
+
+
+def moe_combine(expert_out: torch.Tensor, bias: torch.Tensor | None, row_expert: torch.Tensor,
+                row_weight: torch.Tensor, slot_to_row: torch.Tensor, shared: torch.Tensor | None = None):
+    """Weighted sum of every token's expert rows in ascending expert order (+ bias, + shared expert),
+    rounding like the reference's accumulation in the activation dtype.  Returns [tokens, d]."""
+    _cuda(expert_out, bias, row_expert, row_weight, slot_to_row, shared)
+    T, K = slot_to_row.shape
+    rows, d = expert_out.shape
+    if rows != T * K or not expert_out.is_contiguous() or not slot_to_row.is_contiguous():
+        raise ValueError("expert_out must be contiguous [tokens*top_k, d] and slot_to_row [tokens, top_k]")
+    if row_weight.dtype != expert_out.dtype or row_weight.numel() != rows or row_expert.dtype != torch.int32:
+        raise ValueError("row_weight must match expert_out's dtype, row_expert must be int32, both [rows]")
+    if slot_to_row.dtype != torch.int32:
+        raise ValueError("slot_to_row must be int32")
+    for name, t, shape in (("bias", bias, None), ("shared", shared, (T, d))):
+        if t is not None and (t.dtype != expert_out.dtype or not t.is_contiguous() or t.shape[-1] != d
+                              or (shape is not None and tuple(t.shape) != shape)):
+            raise ValueError(f"{name} must be contiguous [..., {d}] in the dtype of expert_out")
+    out = torch.empty(T, d, dtype=expert_out.dtype, device=expert_out.device)
+    check(lib.b200_moe_combine(expert_out.data_ptr(), bias.data_ptr() if bias is not None else None,
+                               row_expert.data_ptr(), row_weight.data_ptr(), slot_to_row.data_ptr(),
+                               shared.data_ptr() if shared is not None else None, out.data_ptr(), T, K, d,
+                               _dt(expert_out), _stream()), "moe_combine")
+    return out
 
 
 def block_hash(token_ids, prefix: int = -1) -> int:

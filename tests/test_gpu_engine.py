@@ -137,8 +137,9 @@ def test_moe_grouped_gemm_path_matches_the_expert_loop_in_bf16():
             ref_w = wts.gather(1, idx.sort(dim=1).indices).float()
             got_w = w[rows.reshape(-1)].view(T, topk).float()
             assert (got_w[same] - ref_w[same]).abs().max().item() <= 8e-3
-            routed = moe.forward_routed(x).float()
-            assert (routed[same] - want[same]).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+            routed = moe.forward_routed(x).float()               # includes the shared expert
+            full = (moe.forward_sorted(x, idx, wts) + moe.shared(x)).float()
+            assert (routed[same] - full[same]).abs().max().item() <= 2e-2 * max(1.0, full.abs().max().item())
 
 
 def test_small_moe_decoder_bf16_tracks_reference_autocast():

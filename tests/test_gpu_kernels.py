@@ -439,11 +439,12 @@ def test_mla_decode_bf16_fewer_than_16_heads():
 
 
 # ----------------------------------------------------------------------------- fused glue kernels
+@pytest.mark.parametrize("dim", [512, 2048, 1000])      # bf16: 512 and 2048 take the warp-per-row kernel
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_add_rmsnorm_matches_oracle(dtype):
+def test_add_rmsnorm_matches_oracle(dtype, dim):
     ops, orc = _ops(), _oracle()
-    x, res = _randn((37, 512), 1, dtype), _randn((37, 512), 2, torch.float32)
-    w = _randn((512,), 3, torch.float32)
+    x, res = _randn((37, dim), 1, dtype), _randn((37, dim), 2, torch.float32)
+    w = _randn((dim,), 3, torch.float32)
     want = orc.rms_norm(x, w, 1e-5)
     got = ops.add_rmsnorm(x.cuda(), w.cuda(), 1e-5)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
@@ -456,12 +457,14 @@ def test_add_rmsnorm_matches_oracle(dtype):
         assert (gr.float().cpu() - wr.float()).abs().max().item() <= (1e-6 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 64), (8, 4, 64), (4, 2, 128), (16, 8, 32), (2, 1, 256)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype):
+def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype, Hq, Hkv, D):
     """Against the oracle's RMSNorm-over-the-whole-vector + RoPE (model/attention/GQA.py:81-94) and its
-    store_kvcache, including a padded (-1) slot."""
+    store_kvcache, including a padded (-1) slot.  Widths that are multiples of 256 take the
+    warp-per-token bf16 kernel, (8, 2, 64) and fp32 the general one."""
     ops, orc = _ops(), _oracle()
-    T, Hq, Hkv, D, bs, nb = 29, 8, 2, 64, 16, 4
+    T, bs, nb = 29, 16, 4
     qkv = _randn((T, (Hq + 2 * Hkv) * D), 5, dtype)
     qw, kw = _randn((Hq * D,), 6, torch.float32), _randn((Hkv * D,), 7, torch.float32)
     table = orc.rope_table(10000.0, D, 128)
@@ -491,6 +494,83 @@ def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype):
     assert torch.equal(vc.cpu(), vc_ref)
     assert torch.equal(kc.view(-1, Hkv, D)[slots[slots >= 0].cuda()].cpu(), gk.cpu()[slots >= 0])
     assert (kc.view(-1, Hkv, D).float().abs().sum(dim=(1, 2)) > 0).sum().item() == T - 1
+
+
+def _moe_rows(T, K, E, seed):
+    """A consistent grouping: every token picks K distinct experts; rows sorted by (expert, token)."""
+    rng = np.random.default_rng(seed)
+    sel = np.stack([np.sort(rng.choice(E, size=K, replace=False)) for _ in range(T)])        # [T, K]
+    flat_e, flat_t = sel.reshape(-1), np.repeat(np.arange(T), K)
+    order = np.lexsort((flat_t, flat_e))
+    inv = np.empty(T * K, dtype=np.int32)
+    inv[order] = np.arange(T * K, dtype=np.int32)
+    return (torch.from_numpy(flat_e[order].astype(np.int32)).cuda(), torch.from_numpy(inv.reshape(T, K)).cuda())
+
+
+@pytest.mark.parametrize("dtype,F", [(torch.bfloat16, 704), (torch.bfloat16, 100), (torch.float32, 96)])
+def test_swiglu_matches_the_tensor_op_sequence(dtype, F):
+    """silu(h1 + b1) * (h3 + b3) of mlp.py:61-67 with the roundings of add -> silu -> mul on tensors."""
+    import torch.nn.functional as Fn
+    ops = _ops()
+    rows, E = 333, 5
+    h = _randn((rows, 2 * F), 11, dtype).cuda()
+    bias = _randn((E, 2 * F), 12, dtype).cuda()
+    experts = torch.from_numpy(np.sort(np.random.default_rng(3).integers(0, E, size=rows)).astype(np.int32)).cuda()
+    for b, e in ((None, None), (bias, experts), (bias[:1].contiguous(), None)):
+        hb = h if b is None else h + (b[e.long()] if e is not None else b[0])
+        want = Fn.silu(hb[:, :F]) * hb[:, F:]
+        got = ops.swiglu(h, b, e)
+        assert got.shape == want.shape and got.dtype == dtype
+        err = (got.float() - want.float()).abs()
+        assert (err <= 1e-2 * want.float().abs() + 1e-5).all(), err.max().item()   # at most one rounding step
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 1024), (torch.bfloat16, 100), (torch.float32, 64)])
+def test_moe_combine_adds_in_ascending_expert_order(dtype, d):
+    """Bit-equal to: (y + b2[expert]) * w, regrouped per token, summed left to right in the dtype, + shared
+    (the accumulation order of moe.py:312-339 and 272-273)."""
+    ops = _ops()
+    T, K, E = 77, 3, 6
+    experts, inv = _moe_rows(T, K, E, 4)
+    y = _randn((T * K, d), 21, dtype).cuda()
+    b2 = _randn((E, d), 22, dtype).cuda()
+    w = torch.rand(T * K, generator=torch.Generator().manual_seed(23)).to(dtype).cuda()
+    shared = _randn((T, d), 24, dtype).cuda()
+    for bias, sh in ((b2, shared), (None, None), (b2, None)):
+        rows = y if bias is None else y + bias[experts.long()]
+        yt = (rows * w.unsqueeze(1))[inv.long().reshape(-1)].view(T, K, d)
+        want = yt[:, 0]
+        for k in range(1, K):
+            want = want + yt[:, k]
+        if sh is not None:
+            want = want + sh
+        got = ops.moe_combine(y, bias, experts, w, inv, sh)
+        if dtype == torch.bfloat16:
+            assert torch.equal(got, want)
+        else:
+            assert (got - want).abs().max().item() <= 1e-5
+
+
+def test_moe_route_many_ctas_is_a_stable_counting_sort():
+    """5,000 tokens (20 CTAs), 16 experts top-2, and 64 experts top-8: rows ordered by (expert, token),
+    offsets = cumulative counts, slot_to_row inverts the order; selection equals a host top-k."""
+    ops = _ops()
+    for T, E, K in ((5000, 16, 2), (1000, 64, 8), (256, 16, 2), (257, 3, 3)):
+        g = torch.Generator().manual_seed(T + E)
+        logits = torch.randn(T, E, generator=g).cuda()             # fp32: no ties
+        bias = (0.1 * torch.randn(E, generator=g)).cuda()
+        tok, experts, w, offs, inv = ops.moe_route(logits, bias, K)
+        ops.check_status()
+        assert torch.equal(offs, experts.bincount(minlength=E).cumsum(0).int())
+        key = experts.long() * T + tok.long()
+        assert (key[1:] > key[:-1]).all()
+        want_sel = torch.topk(logits + bias, K, dim=-1).indices.sort(dim=1).values
+        rows = inv.long().reshape(-1)
+        assert torch.equal(experts[rows].view(T, K).long(), want_sel)
+        assert torch.equal(tok[rows].view(T, K).long(), torch.arange(T, device="cuda").view(T, 1).expand(T, K))
+        scores = torch.sigmoid(logits).gather(1, want_sel)
+        want_w = scores / (scores.sum(-1, keepdim=True) + 1e-10) if K > 1 else scores
+        assert (w[rows].view(T, K) - want_w).abs().max().item() <= 1e-6
 
 
 # ----------------------------------------------------------------------------- empty inputs
