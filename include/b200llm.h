@@ -245,6 +245,22 @@ int b200_moe_combine(const void* expert_out, const void* bias, const int32_t* ro
                      const void* row_weight, const int32_t* slot_to_row, const void* shared, void* out,
                      int64_t num_tokens, int32_t top_k, int32_t d_model, int32_t dtype, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Grouped GEMM over rows grouped by expert (the per-expert loop of MOE.moe_infer, moe.py:299-339),
+ * bf16, fp32 accumulation on the tensor cores.  Expert e owns rows [offsets[e-1], offsets[e]) of
+ * x [num_rows, k_dim] (expert_offsets as b200_moe_route writes them; read on the device).
+ *   mode 0: out [num_rows, n_out] = x . W_e^T (+ bias[e] if given), w [experts, n_out, k_dim].
+ *   mode 1: out [num_rows, n_out] = silu(x . W1_e^T + b1) * (x . W3_e^T + b3), n_out = d_ff,
+ *           w [experts, 2*d_ff, k_dim] = rows of w1 then rows of w3, bias [experts, 2*d_ff] or NULL
+ *           (mlp.py:61-67); GEMM result, bias add, silu and product are each rounded to bf16.
+ * Requires k_dim % 8 == 0 and 16-byte aligned x, w (B200_ERR_ALIGN).  A wait that runs out inside
+ * the kernel sets *status to B200_ERR_TIMEOUT.
+ * ------------------------------------------------------------------------------------------- */
+int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* out,
+                          const int32_t* expert_offsets, int64_t num_rows, int32_t num_experts,
+                          int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype, int32_t* status,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,20 +41,22 @@ struct RouteArgs {
   int32_t* cta_counts;      // [gridDim.x, E] workspace (unused with one CTA)
 };
 
-// bit e set: token t routes to expert e
-template <typename T>
+// bit e set: token t routes to expert e.  EMAX (>= E) is a compile-time bound so that the biased
+// logits live in registers.
+template <typename T, int EMAX>
 __device__ __forceinline__ unsigned long long select_mask(const RouteArgs& a, int t) {
   const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * a.E;
-  float biased[kMaxE];
-#pragma unroll 4
-  for (int e = 0; e < a.E; ++e)
-    biased[e] = round_to<T>(to_float<T>(row[e]) + round_to<T>(a.bias[e]));
+  float biased[EMAX];
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e)
+    biased[e] = e < a.E ? round_to<T>(to_float<T>(row[e]) + round_to<T>(a.bias[e])) : 0.f;
   unsigned long long taken = 0ull;
   for (int k = 0; k < a.K; ++k) {            // k maxima, lower index first among equals
     int best = -1;
     float bv = -INFINITY;
-    for (int e = 0; e < a.E; ++e)
-      if (!((taken >> e) & 1ull) && (best < 0 || biased[e] > bv)) {
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e)
+      if (e < a.E && !((taken >> e) & 1ull) && (best < 0 || biased[e] > bv)) {
         best = e;
         bv = biased[e];
       }
@@ -78,11 +80,11 @@ __device__ __forceinline__ void warp_counts(unsigned long long taken, int E, int
   }
 }
 
-template <typename T>
+template <typename T, int EMAX>
 __global__ void __launch_bounds__(kTok) moe_count_kernel(const RouteArgs a) {
   __shared__ int32_t warp_cnt[kWarps][kMaxE];
   const int t = blockIdx.x * kTok + threadIdx.x;
-  const unsigned long long taken = t < a.T ? select_mask<T>(a, t) : 0ull;
+  const unsigned long long taken = t < a.T ? select_mask<T, EMAX>(a, t) : 0ull;
   int ranks[kMaxK];
   warp_counts(taken, a.E, warp_cnt, ranks);
   __syncthreads();
@@ -94,72 +96,85 @@ __global__ void __launch_bounds__(kTok) moe_count_kernel(const RouteArgs a) {
   }
 }
 
-template <typename T>
+template <typename T, int EMAX>
 __global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
-  __shared__ int32_t warp_cnt[kWarps][kMaxE];
-  __shared__ int32_t part_total[kWarps][kMaxE], part_before[kWarps][kMaxE];
-  __shared__ int32_t base[kMaxE];     // first output row of this CTA's rows of expert e
+  __shared__ int32_t warp_cnt[kWarps][kMaxE];   // rows of expert e owned by warp w
+  __shared__ int32_t warp_pre[kWarps][kMaxE];   // ... by the warps before w
+  __shared__ int32_t tot_s[kMaxE], bef_s[kMaxE];
+  __shared__ int32_t base[kMaxE];               // first output row of this CTA's rows of expert e
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int E = a.E, K = a.K;
   const int t = blockIdx.x * kTok + tid;
-  const unsigned long long taken = t < a.T ? select_mask<T>(a, t) : 0ull;
+  const unsigned long long taken = t < a.T ? select_mask<T, EMAX>(a, t) : 0ull;
   int ranks[kMaxK];
   warp_counts(taken, E, warp_cnt, ranks);
-  // rows of every expert in all CTAs (total) and in the CTAs before this one (before)
-  if (gridDim.x > 1) {
-    for (int e = lane; e < E; e += 32) {
-      int tot = 0, bef = 0;
-      for (int c = warp; c < static_cast<int>(gridDim.x); c += kWarps) {
-        const int v = a.cta_counts[c * E + e];
-        tot += v;
-        if (c < static_cast<int>(blockIdx.x)) bef += v;
+  // routing weights of the selected experts, ascending expert order (before the barrier: independent of it)
+  int sel[kMaxK];
+  float wsel[kMaxK];
+  if (t < a.T) {
+    const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * E;
+    float sum = 0.f;
+    int n = 0;
+    for (int e = 0; e < E; ++e)
+      if (((taken >> e) & 1ull) && n < kMaxK) {
+        sel[n] = e;
+        wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
+        sum += wsel[n];
+        ++n;
       }
-      part_total[warp][e] = tot;
-      part_before[warp][e] = bef;
+    if (K > 1) {
+      const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
+      for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
     }
   }
   __syncthreads();
-  if (tid == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) {
-      int tot = 0, bef = 0;
-      for (int w = 0; w < kWarps; ++w) {
-        if (gridDim.x > 1) {
-          tot += part_total[w][e];
-          bef += part_before[w][e];
-        } else {
-          tot += warp_cnt[w][e];
-        }
+  // rows of every expert in all CTAs (tot) and in the CTAs before this one (bef); prefix over warps
+  for (int i = tid; i < kWarps * E; i += kTok) {
+    const int w = i / E, e = i - w * E;
+    int pre = 0;
+    for (int x = 0; x < w; ++x) pre += warp_cnt[x][e];
+    warp_pre[w][e] = pre;
+  }
+  if (tid < E) {
+    int tot = 0, bef = 0;
+    if (gridDim.x > 1) {
+      for (int c = 0; c < static_cast<int>(gridDim.x); ++c) {
+        const int v = a.cta_counts[c * E + tid];
+        tot += v;
+        if (c < static_cast<int>(blockIdx.x)) bef += v;
       }
-      base[e] = run + bef;
-      run += tot;
-      if (blockIdx.x == 0) a.offsets[e] = run;
+    } else {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) tot += warp_cnt[w][tid];
+    }
+    tot_s[tid] = tot;
+    bef_s[tid] = bef;
+  }
+  __syncthreads();
+  if (warp == 0) {       // exclusive scan of the expert totals, 32 experts per trip
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int v = e < E ? tot_s[e] : 0;
+      int x = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (e < E) {
+        base[e] = carry + x - v + bef_s[e];
+        if (blockIdx.x == 0) a.offsets[e] = carry + x;
+      }
+      carry += __shfl_sync(0xffffffffu, x, 31);
     }
   }
   __syncthreads();
   if (t >= a.T) return;
-  // routing weights of the selected experts, ascending expert order
-  const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * E;
-  int sel[kMaxK];
-  float wsel[kMaxK];
-  float sum = 0.f;
-  int n = 0;
-  for (int e = 0; e < E; ++e)
-    if ((taken >> e) & 1ull) {
-      sel[n] = e;
-      wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
-      sum += wsel[n];
-      ++n;
-    }
-  if (K > 1) {
-    const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
-    for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
-  }
   T* wout = static_cast<T*>(a.sorted_weight);
   for (int k = 0; k < K; ++k) {
     const int e = sel[k];
-    int pos = base[e] + ranks[k];
-    for (int w = 0; w < warp; ++w) pos += warp_cnt[w][e];
+    const int pos = base[e] + warp_pre[warp][e] + ranks[k];
     a.sorted_token[pos] = t;
     a.sorted_expert[pos] = e;
     wout[pos] = from_float<T>(wsel[k]);
@@ -328,13 +343,21 @@ extern "C" int b200_moe_route(const void* gate_logits, const float* expert_bias,
   a.slot_to_row = slot_to_row;
   a.cta_counts = static_cast<int32_t*>(workspace);
   const int grid = num_tokens == 0 ? 1 : (num_tokens + kTok - 1) / kTok;   // 0 tokens: offsets = 0
+#define ROUTE_LAUNCH(T, EMAX)                                                       \
+  do {                                                                              \
+    if (grid > 1) moe_count_kernel<T, EMAX><<<grid, kTok, 0, s>>>(a);               \
+    moe_scatter_kernel<T, EMAX><<<grid, kTok, 0, s>>>(a);                           \
+  } while (0)
   if (dtype == B200_DTYPE_F32) {
-    if (grid > 1) moe_count_kernel<float><<<grid, kTok, 0, s>>>(a);
-    moe_scatter_kernel<float><<<grid, kTok, 0, s>>>(a);
+    if (num_experts <= 16) ROUTE_LAUNCH(float, 16);
+    else if (num_experts <= 32) ROUTE_LAUNCH(float, 32);
+    else ROUTE_LAUNCH(float, 64);
   } else {
-    if (grid > 1) moe_count_kernel<__nv_bfloat16><<<grid, kTok, 0, s>>>(a);
-    moe_scatter_kernel<__nv_bfloat16><<<grid, kTok, 0, s>>>(a);
+    if (num_experts <= 16) ROUTE_LAUNCH(__nv_bfloat16, 16);
+    else if (num_experts <= 32) ROUTE_LAUNCH(__nv_bfloat16, 32);
+    else ROUTE_LAUNCH(__nv_bfloat16, 64);
   }
+#undef ROUTE_LAUNCH
   return launch_result();
 }
 

@@ -115,7 +115,8 @@ class MoE(nn.Module):
     """
 
     dense_max_tokens = 512
-    use_grouped = True     # bf16: library grouped GEMM over tokens sorted by expert (no host sync)
+    use_grouped = True     # bf16: grouped GEMMs over tokens sorted by expert (no host sync)
+    own_gemm_max_rows_per_expert = 64   # average rows per expert up to which the weight-streaming kernel is used
 
     def __init__(self, p: _Params, prefix: str, cfg: ModelConfig):
         super().__init__()
@@ -177,12 +178,19 @@ class MoE(nn.Module):
 
     def forward_routed(self, x):
         """bf16 fast path: routing kernel (top-k, weights, grouping by expert), two grouped GEMMs with
-        the bias + SwiGLU between them in one kernel, and one combine kernel that adds every token's
-        K contributions in ascending expert order and then the shared expert."""
+        the bias + SwiGLU between them, and one combine kernel that adds every token's K contributions
+        in ascending expert order and then the shared expert.  Batches with few rows per expert
+        (decode) are bound by streaming the expert weights and use the tcgen05 grouped GEMM of this
+        package (SwiGLU in its epilogue); large prefill batches are compute-bound and go to the
+        library grouped GEMM."""
         tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K)
         xs = x.index_select(0, tok)
-        act = ops.swiglu(torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs), self.b13, experts)
-        y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs)
+        if xs.shape[0] <= self.own_gemm_max_rows_per_expert * self.E and xs.shape[1] % 8 == 0 and self.d_ff % 8 == 0:
+            act = ops.moe_grouped_gemm(xs, self.w13, offs, self.b13, swiglu=True)
+            y = ops.moe_grouped_gemm(act, self.w2, offs)
+        else:
+            act = ops.swiglu(torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs), self.b13, experts)
+            y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs)
         shared = self.shared(x) if self.shared is not None else None
         return ops.moe_combine(y, self.b2, experts, w, inv, shared)
 

@@ -336,6 +336,28 @@ def swiglu(h: torch.Tensor, bias: torch.Tensor | None = None, row_expert: torch.
     return act
 
 
+def moe_grouped_gemm(x: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
+                     bias: torch.Tensor | None = None, swiglu: bool = False) -> torch.Tensor:
+    """Rows of x [R, k] grouped by expert (expert_offsets int32 [E], exclusive ends) times the expert's
+    weight: w [E, n, k] -> [R, n]; with ``swiglu`` w is [E, 2*d_ff, k] = [w1 | w3], bias [E, 2*d_ff],
+    and the result is silu(x w1^T + b1) * (x w3^T + b3) [R, d_ff].  bf16, tcgen05 tensor cores."""
+    _cuda(x, w, expert_offsets, bias)
+    R, k = x.shape
+    E, n, k2 = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous():
+        raise ValueError("x and w must be contiguous bfloat16")
+    if k2 != k or expert_offsets.dtype != torch.int32 or expert_offsets.numel() != E or (swiglu and n % 2):
+        raise ValueError("w must be [E, n, k] with k = x.shape[1]; expert_offsets int32 [E]")
+    n_out = n // 2 if swiglu else n
+    if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous() or tuple(bias.shape) != (E, n)):
+        raise ValueError("bias must be contiguous bfloat16 [E, n]")
+    out = torch.empty(R, n_out, dtype=torch.bfloat16, device=x.device)
+    check(lib.b200_moe_grouped_gemm(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                    out.data_ptr(), expert_offsets.data_ptr(), R, E, n_out, k, 1 if swiglu else 0,
+                                    _dt(x), status_word(x.device).data_ptr(), _stream()), "moe_grouped_gemm")
+    return out
+
+
 def moe_combine(expert_out: torch.Tensor, bias: torch.Tensor | None, row_expert: torch.Tensor,
                 row_weight: torch.Tensor, slot_to_row: torch.Tensor, shared: torch.Tensor | None = None):
     """Weighted sum of every token's expert rows in ascending expert order (+ bias, + shared expert),

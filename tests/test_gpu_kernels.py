@@ -573,6 +573,51 @@ def test_moe_route_many_ctas_is_a_stable_counting_sort():
         assert (w[rows].view(T, K) - want_w).abs().max().item() <= 1e-6
 
 
+def _grouped_reference(x, w, offs, bias, swiglu):
+    """Per-expert fp32 matmuls with the bf16 roundings of the tensor-op sequence."""
+    import torch.nn.functional as Fn
+    E = w.shape[0]
+    n_out = w.shape[1] // 2 if swiglu else w.shape[1]
+    out = torch.zeros(x.shape[0], n_out, dtype=torch.bfloat16, device=x.device)
+    lo = 0
+    for e in range(E):
+        hi = int(offs[e])
+        if hi > lo:
+            h = (x[lo:hi].float() @ w[e].float().t()).bfloat16()
+            if bias is not None:
+                h = h + bias[e]
+            out[lo:hi] = Fn.silu(h[:, :n_out]) * h[:, n_out:] if swiglu else h
+        lo = hi
+    return out
+
+
+@pytest.mark.parametrize("counts,k,n,swiglu", [
+    ([12, 0, 31, 7, 16, 1, 64, 25], 1024, 704, True),        # decode-like: one pass per expert
+    ([12, 0, 31, 7, 16, 1, 64, 25], 704, 1024, False),
+    ([150, 3, 0, 0, 70, 9], 256, 200, True),                 # > 64 rows in the small configuration: several passes
+    ([150, 3, 0, 0, 70, 9], 200, 1000, False),               # ragged K (200 = 3 slabs + 8) and ragged n_out
+    ([700, 90, 300, 10], 512, 192, True),                    # large batch: 256 rows per pass, several passes
+    ([700, 90, 300, 10], 192, 520, False),
+    ([0, 0, 5], 64, 64, False),
+])
+def test_moe_grouped_gemm_matches_per_expert_matmuls(counts, k, n, swiglu):
+    ops = _ops()
+    E, R = len(counts), sum(counts)
+    offs = torch.tensor(np.cumsum(counts), dtype=torch.int32, device="cuda")
+    x = _randn((R, k), 31, torch.bfloat16).cuda()
+    w = (_randn((E, 2 * n if swiglu else n, k), 32, torch.float32) * k ** -0.5).bfloat16().cuda()
+    bias = _randn((E, 2 * n if swiglu else n), 33, torch.bfloat16).cuda()
+    for b in (bias, None):
+        got = ops.moe_grouped_gemm(x, w, offs, b, swiglu=swiglu)
+        ops.check_status()
+        want = _grouped_reference(x, w, offs, b, swiglu)
+        assert got.shape == want.shape
+        err = (got.float() - want.float()).abs()
+        assert (err <= 2e-2 * want.float().abs() + 2e-2).all(), err.max().item()
+    again = ops.moe_grouped_gemm(x, w, offs, bias, swiglu=swiglu)
+    assert torch.equal(again, ops.moe_grouped_gemm(x, w, offs, bias, swiglu=swiglu))
+
+
 # ----------------------------------------------------------------------------- empty inputs
 def test_empty_inputs_are_no_ops():
     """Zero tokens / zero sequences through every entry point: success, nothing launched or written."""
