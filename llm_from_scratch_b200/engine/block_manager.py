@@ -27,6 +27,8 @@ revived by a later prefix hit, and ``can_append`` asks for a free block on the s
 """
 from __future__ import annotations
 
+from collections import OrderedDict
+
 from .sequence import Sequence
 from .. import ops
 
@@ -56,7 +58,9 @@ class BlockManager:
         self.reference_exact = reference_exact
         self.blocks = [Block(i) for i in range(num_blocks)]
         self.hash_to_block_id: dict[int, int] = {}
-        self._free: dict[int, None] = dict.fromkeys(range(num_blocks))  # ordered set, oldest first
+        # ordered set, oldest first.  OrderedDict, not dict: a plain dict whose oldest keys keep being
+        # deleted makes next(iter(d)) scan the deleted slots, which is linear in the pool size
+        self._free: OrderedDict[int, None] = OrderedDict.fromkeys(range(num_blocks))
         self.used_block_ids: set[int] = set()
 
     # ------------------------------------------------------------------ views

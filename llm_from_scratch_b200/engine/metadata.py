@@ -31,11 +31,33 @@ class StepMetadata:
     last_token_index: Optional[np.ndarray] = None  # int64 [n]  row of each sequence's last token
 
 
-def pad_block_tables(seqs: list[Sequence]) -> np.ndarray:
-    width = max(len(s.block_table) for s in seqs)
-    out = np.full((len(seqs), max(width, 1)), -1, dtype=np.int32)
-    for i, s in enumerate(seqs):
-        out[i, :len(s.block_table)] = s.block_table
+def block_table_array(s: Sequence) -> np.ndarray:
+    """int32 copy of ``s.block_table`` kept on the sequence between steps.  The block manager only ever
+    appends to the list or replaces it by a new list (deallocate), so the copy is extended by the new
+    entries when the list object is the same and rebuilt when it is not."""
+    bt = s.block_table
+    n = len(bt)
+    c = s._bt_cache
+    if c is not None and c[0] is bt and c[2] <= n <= c[1].size:
+        if c[2] < n:
+            c[1][c[2]:n] = bt[c[2]:]
+            c[2] = n
+        return c[1][:n]
+    buf = np.empty(max(64, 2 * n), dtype=np.int32)
+    buf[:n] = bt
+    s._bt_cache = [bt, buf, n]
+    return buf[:n]
+
+
+def pad_block_tables(seqs: list[Sequence], out: np.ndarray | None = None) -> np.ndarray:
+    """[n, width] int32, -1 beyond every sequence's table (``out``: write into rows [:n] of a wider
+    preallocated array instead, leaving its other entries as they are)."""
+    arrays = [block_table_array(s) for s in seqs]
+    if out is None:
+        width = max(a.size for a in arrays)
+        out = np.full((len(seqs), max(width, 1)), -1, dtype=np.int32)
+    for i, a in enumerate(arrays):
+        out[i, :a.size] = a
     return out
 
 
@@ -75,8 +97,10 @@ def prepare_prefill(seqs: list[Sequence], block_size: int) -> StepMetadata:
         last_token_index=(cu_q[1:] - 1).astype(np.int64))
 
 
-def prepare_decode(seqs: list[Sequence], block_size: int) -> StepMetadata:
-    """One token per running sequence (model_runner.py:253-278)."""
+def prepare_decode(seqs: list[Sequence], block_size: int, tables_out: np.ndarray | None = None) -> StepMetadata:
+    """One token per running sequence (model_runner.py:253-278).  With ``tables_out`` (a preallocated
+    [>= n, >= widest table] int32 array) the block tables are written into its first n rows, entries
+    beyond a sequence's table keep their old values, and ``block_tables`` is that row range."""
     n = len(seqs)
     lens = np.fromiter((s.num_tokens for s in seqs), dtype=np.int64, count=n)
     slots = np.fromiter((s.block_table[-1] * block_size + s.last_block_num_tokens - 1 for s in seqs),
@@ -85,4 +109,5 @@ def prepare_decode(seqs: list[Sequence], block_size: int) -> StepMetadata:
         is_prefill=False,
         input_ids=np.fromiter((s.last_token for s in seqs), dtype=np.int64, count=n),
         slot_mapping=slots, positions=lens - 1, context_lens=lens,
-        block_tables=pad_block_tables(seqs), last_token_index=np.arange(n, dtype=np.int64))
+        block_tables=pad_block_tables(seqs) if tables_out is None else pad_block_tables(seqs, tables_out)[:n],
+        last_token_index=np.arange(n, dtype=np.int64))

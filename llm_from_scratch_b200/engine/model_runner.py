@@ -183,12 +183,36 @@ class ModelRunner:
         return self.model.compute_logits(v["outputs"][:bs])
 
     def run(self, seqs: list[Sequence], is_prefill: bool) -> list[int]:
-        input_ids = self.prepare_prefill(seqs) if is_prefill else self.prepare_decode(seqs)
-        logits = self.run_model(input_ids, is_prefill)
+        if not is_prefill and self.graphs and not self.enforce_eager and len(seqs) <= max(self.graphs):
+            logits = self._replay_decode(seqs)
+        else:
+            input_ids = self.prepare_prefill(seqs) if is_prefill else self.prepare_decode(seqs)
+            logits = self.run_model(input_ids, is_prefill)
         with torch.inference_mode():
             token_ids = self.sampler(logits, self.prepare_sample(seqs)).tolist()
         reset_context()
         return token_ids
+
+    @torch.inference_mode()
+    def _replay_decode(self, seqs: list[Sequence]) -> torch.Tensor:
+        """Decode step from a captured graph.  The graph's inputs live in one device buffer mirrored by
+        one pinned host buffer: the step's metadata is written straight into the host mirror (padding
+        rows: slot -1, context 0) and shipped with a single copy; nothing else runs before the replay."""
+        n = len(seqs)
+        bucket = next(b for b in sorted(self.graphs) if b >= n)
+        h, v = self.graph_host_np, self.graph_vars
+        m = md.prepare_decode(seqs, self.block_size, tables_out=h["block_tables"])
+        h["input_ids"][:n] = m.input_ids
+        h["slot_mapping"][:n] = m.slot_mapping
+        h["slot_mapping"][n:bucket] = -1
+        h["context_lens"][:n] = m.context_lens
+        h["context_lens"][n:bucket] = 0
+        nbytes = self.graph_tables_offset + bucket * h["block_tables"].shape[1] * 4
+        self.graph_dev[:nbytes].copy_(self.graph_host[:nbytes], non_blocking=True)
+        set_context(False, slot_mapping=v["slot_mapping"][:n], context_lens=v["context_lens"][:n],
+                    block_tables=v["block_tables"][:n])
+        self.graphs[bucket].replay()
+        return self.model.compute_logits(v["outputs"][:n])
 
     @torch.inference_mode()
     def run_logits(self, seqs: list[Sequence], is_prefill: bool) -> torch.Tensor:
@@ -204,13 +228,27 @@ class ModelRunner:
         max_bs = min(self.max_num_seqs, 512)
         max_blocks = (self.max_model_length + self.block_size - 1) // self.block_size
         dev = self.device
-        v = dict(
-            input_ids=torch.zeros(max_bs, dtype=torch.int64, device=dev),
-            slot_mapping=torch.full((max_bs,), -1, dtype=torch.int64, device=dev),
-            context_lens=torch.zeros(max_bs, dtype=torch.int64, device=dev),
-            block_tables=torch.zeros(max_bs, max_blocks, dtype=torch.int32, device=dev),
-            outputs=torch.zeros(max_bs, self.model_config.d_model, dtype=self.dtype, device=dev),
-        )
+        # all graph inputs in one device buffer with a pinned host mirror (block tables last, so that a
+        # step copies only the prefix its batch bucket uses)
+        fields = (("input_ids", np.int64, torch.int64, (max_bs,)), ("slot_mapping", np.int64, torch.int64, (max_bs,)),
+                  ("context_lens", np.int64, torch.int64, (max_bs,)),
+                  ("block_tables", np.int32, torch.int32, (max_bs, max_blocks)))
+        offsets, total = {}, 0
+        for name, npdt, _, shape in fields:
+            offsets[name] = total
+            total += (int(np.prod(shape)) * np.dtype(npdt).itemsize + 15) & ~15
+        self.graph_dev = torch.zeros(total, dtype=torch.uint8, device=dev)
+        self.graph_host = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        self.graph_tables_offset = offsets["block_tables"]
+        host_bytes = self.graph_host.numpy()
+        v, self.graph_host_np = {}, {}
+        for name, npdt, tdt, shape in fields:
+            nbytes = int(np.prod(shape)) * np.dtype(npdt).itemsize
+            v[name] = self.graph_dev[offsets[name]:offsets[name] + nbytes].view(tdt).view(*shape)
+            self.graph_host_np[name] = host_bytes[offsets[name]:offsets[name] + nbytes].view(npdt).reshape(shape)
+        v["slot_mapping"].fill_(-1)
+        self.graph_host_np["slot_mapping"][:] = -1
+        v["outputs"] = torch.zeros(max_bs, self.model_config.d_model, dtype=self.dtype, device=dev)
         buckets = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
         if max_bs not in buckets:
             buckets.append(max_bs)

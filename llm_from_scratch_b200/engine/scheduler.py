@@ -59,6 +59,8 @@ class Scheduler:
 
     def _grow_running(self) -> list[Sequence]:
         bm, batch = self.block_manager, []
+        block_size = bm.block_size
+        limit = min(self.max_num_sequences, self.max_num_batched_tokens)
         while self.running:
             seq = self.running.popleft()
             if self.reference_exact:
@@ -70,6 +72,15 @@ class Scheduler:
                         break
                     continue
             else:
+                rem = seq.num_tokens % block_size
+                if rem > 1:
+                    # mid-block: no block is opened or sealed this step (BlockManager.append would
+                    # only assert); the batch limits below still apply
+                    if len(batch) >= limit:
+                        self.running.appendleft(seq)
+                        break
+                    batch.append(seq)
+                    continue
                 evicted_self = False
                 while not bm.can_append(seq):
                     if self.running:
