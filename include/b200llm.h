@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 3
+#define B200_ABI_VERSION 4
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -146,8 +146,14 @@ int b200_paged_decode_gqa_static(const void* q, const void* k_cache, const void*
  *       read from k_cache/v_cache through block_tables [num_seqs, bt_stride] and k/v are ignored
  *       (the caller has already stored the new tokens with b200_store_kvcache);
  *   out [total_q, Hq, Dv] contiguous.
- *   total_q_tokens / total_k_tokens are the row counts of q and of k/v (= cu_seqlens[num_seqs],
+ *   total_q_tokens / total_k_tokens are the row counts of q and of k/v (>= cu_seqlens[num_seqs],
  *   which the host knows from its tensors): they bound the TMA tensor maps built over q/k/v.
+ *   plan (may be NULL): a tile list written by b200_prefill_plan for the same cu_seqlens_q, with its
+ *   tile_rows and capacity.  With a plan the tiled kernels launch one CTA per listed tile (longest
+ *   first) instead of num_seqs x ceil(max_seqlen_q / tile) CTAs, and neither num_seqs nor max_seqlen_q
+ *   shapes the grid any more, so a step with fixed buffer sizes can be captured in a CUDA graph:
+ *   pass num_seqs = the capacity of cu_seqlens (unused trailing sequences have length 0).
+ *   A plan whose tile_rows does not match the kernel chosen for the shape is ignored.
  * ------------------------------------------------------------------------------------------- */
 int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                         int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
@@ -157,7 +163,23 @@ int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                         int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
                         int32_t head_dim_v, float scale, const void* k_cache, const void* v_cache,
                         const int32_t* block_tables, int64_t bt_stride, int32_t block_size,
-                        int64_t num_blocks, int32_t dtype, int32_t* status, void* stream);
+                        int64_t num_blocks, const int32_t* plan, int32_t plan_tile_rows,
+                        int32_t plan_capacity, int32_t dtype, int32_t* status, void* stream);
+
+/* Tile list for b200_prefill_varlen, computed on the device from cu_seqlens_q (one small launch per
+ * step; all layers of the step reuse it).
+ *   b200_prefill_tile_rows: query rows per tile of the kernel that serves this shape (128 tcgen05,
+ *     64 mma.sync), or 0 when only the general kernel applies (no plan then).
+ *   b200_prefill_plan_bytes: size of `plan` for up to total_q_tokens rows in up to num_seqs sequences;
+ *     its capacity in tiles is bytes / 4 - 4.
+ *   b200_prefill_plan: max_seqlen_q is a host-side upper bound of the longest sequence
+ *     (more than 4096 tiles in one sequence: B200_ERR_UNSUPPORTED).  Layout: int32 header
+ *     {tiles, tile_rows, capacity, 0}, then (sequence << 16 | tile) per tile, highest tiles first. */
+int32_t b200_prefill_tile_rows(int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
+                               int32_t head_dim_v, int32_t dtype);
+size_t b200_prefill_plan_bytes(int64_t total_q_tokens, int32_t num_seqs, int32_t tile_rows);
+int b200_prefill_plan(const int32_t* cu_seqlens_q, int32_t num_seqs, int32_t max_seqlen_q,
+                      int32_t tile_rows, int32_t* plan, size_t plan_bytes, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * MLA latent-cache decode (absorbed form).  Arithmetic = MultiHeadLatentAttention.forward cache

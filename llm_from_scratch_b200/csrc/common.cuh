@@ -115,6 +115,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Prefill tile list (b200_prefill_plan): int32 header {tile count, rows per tile, capacity, 0} followed
+// by one entry per query tile, (sequence << 16) | tile index, heaviest tiles first.
+constexpr int kPlanHeader = 4;
+
 __device__ __forceinline__ void report(int32_t* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }

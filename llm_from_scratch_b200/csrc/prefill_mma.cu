@@ -29,6 +29,7 @@ struct MmaArgs {
   const int32_t* cu_q;
   const int32_t* cu_k;
   int Hq, Hkv, ntiles_max;
+  const int32_t* plan;   // tile list (see b200_prefill_plan) or null: grid (head, seq, tile rank)
   float scale_log2;
   const __nv_bfloat16* kc;
   const __nv_bfloat16* vc;
@@ -53,8 +54,17 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
   constexpr int NV = DV / 8;     // n-tiles of O
   constexpr int QB = BM * DQK * 2, KB = BN * DQK * 2, VB = BN * DV * 2;
 
-  const int head = blockIdx.x, seq = blockIdx.y;
-  const int tile = a.ntiles_max - 1 - blockIdx.z;
+  const int head = blockIdx.x;
+  int seq, tile;
+  if (a.plan) {                                   // grid (head, tile-list slot)
+    if (static_cast<int>(blockIdx.y) >= a.plan[0]) return;
+    const uint32_t entry = static_cast<uint32_t>(a.plan[kPlanHeader + blockIdx.y]);
+    seq = entry >> 16;
+    tile = entry & 0xffffu;
+  } else {
+    seq = blockIdx.y;
+    tile = a.ntiles_max - 1 - blockIdx.z;
+  }
   const int q0 = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q0;
   const int k0 = a.cu_k[seq], k_len = a.cu_k[seq + 1] - k0;
   const int m0 = tile * BM;
@@ -272,7 +282,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
 }
 
 template <int DQK, int DV>
-int launch(const MmaArgs& a, int num_seqs, bool paged, cudaStream_t s) {
+int launch(const MmaArgs& a, int num_seqs, int plan_capacity, bool paged, cudaStream_t s) {
   constexpr size_t smem = size_t(BM) * DQK * 2 + 2 * size_t(BN) * DQK * 2 + 2 * size_t(BN) * DV * 2;
   static bool configured[64][2] = {};
   int dev = 0;
@@ -285,6 +295,7 @@ int launch(const MmaArgs& a, int num_seqs, bool paged, cudaStream_t s) {
     configured[dev][paged] = true;
   }
   dim3 grid(a.Hq, num_seqs, a.ntiles_max);
+  if (a.plan) grid = dim3(a.Hq, plan_capacity, 1);
   kern<<<grid, kThreads, smem, s>>>(a);
   return launch_result();
 }
@@ -296,7 +307,8 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv,
                        int Dqk, int Dv, float scale, const void* kc, const void* vc,
                        const int32_t* bt, int64_t bt_stride, int bs, int64_t num_blocks,
-                       int32_t* status, cudaStream_t s) {
+                       const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
+                       cudaStream_t s) {
   const bool paged = bt != nullptr;
   const bool shape_ok = (Dqk == Dv && (Dqk == 32 || Dqk == 64 || Dqk == 128)) ||
                         (Dqk == 192 && Dv == 128);
@@ -323,6 +335,7 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
   a.Hq = Hq;
   a.Hkv = Hkv;
   a.ntiles_max = ntiles;
+  a.plan = (plan != nullptr && plan_tile_rows == BM && plan_capacity > 0 && plan_capacity <= 65535) ? plan : nullptr;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.kc = static_cast<const __nv_bfloat16*>(kc);
   a.vc = static_cast<const __nv_bfloat16*>(vc);
@@ -331,10 +344,10 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
   a.bs = bs;
   a.num_blocks = num_blocks;
   a.status = status;
-  if (Dqk == 192) return launch<192, 128>(a, num_seqs, paged, s);
-  if (Dqk == 128) return launch<128, 128>(a, num_seqs, paged, s);
-  if (Dqk == 64) return launch<64, 64>(a, num_seqs, paged, s);
-  return launch<32, 32>(a, num_seqs, paged, s);
+  if (Dqk == 192) return launch<192, 128>(a, num_seqs, plan_capacity, paged, s);
+  if (Dqk == 128) return launch<128, 128>(a, num_seqs, plan_capacity, paged, s);
+  if (Dqk == 64) return launch<64, 64>(a, num_seqs, plan_capacity, paged, s);
+  return launch<32, 32>(a, num_seqs, plan_capacity, paged, s);
 }
 
 }  // namespace b200

@@ -60,6 +60,7 @@ struct UmmaArgs {
   const int32_t* cu_q;
   const int32_t* cu_k;
   int Hq, Hkv, ntiles_max;
+  const int32_t* plan;   // tile list (see b200_prefill_plan) or null: grid (head pair, seq, tile rank)
   float scale_log2;
   const __nv_bfloat16* kc;
   const __nv_bfloat16* vc;
@@ -88,8 +89,17 @@ prefill_umma_kernel(const UmmaArgs a, const __grid_constant__ CUtensorMap tm_q,
   auto bar = [&](int i) -> uint32_t { return sb + OFF_BAR + i * 8; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int pair = blockIdx.x, seq = blockIdx.y;
-  const int tile = a.ntiles_max - 1 - blockIdx.z;
+  const int pair = blockIdx.x;
+  int seq, tile;
+  if (a.plan) {                                  // grid (head pair, tile-list slot)
+    if (static_cast<int>(blockIdx.y) >= a.plan[0]) return;
+    const uint32_t entry = static_cast<uint32_t>(a.plan[kPlanHeader + blockIdx.y]);
+    seq = entry >> 16;
+    tile = entry & 0xffffu;
+  } else {
+    seq = blockIdx.y;
+    tile = a.ntiles_max - 1 - blockIdx.z;
+  }
   const int q0 = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q0;
   const int k0 = a.cu_k[seq], k_len = a.cu_k[seq + 1] - k0;
   const int m0 = tile * BM;
@@ -468,7 +478,8 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
                         int64_t k_stride, int64_t v_stride, int64_t total_q, int64_t total_k,
                         const int32_t* cu_q, const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv, float scale,
                         const void* kc, const void* vc, const int32_t* bt, int64_t bt_stride, int bs,
-                        int64_t num_blocks, int32_t* status, cudaStream_t s) {
+                        int64_t num_blocks, const int32_t* plan, int plan_tile_rows, int plan_capacity,
+                        int32_t* status, cudaStream_t s) {
   const bool paged = bt != nullptr;
   if (Dqk != D || Dv != D || Hkv <= 0 || Hq % Hkv != 0 || ((Hq / Hkv) & 1)) return B200_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200_ERR_UNSUPPORTED;   // the row maximum is taken before scaling
@@ -491,6 +502,7 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
   a.Hq = Hq;
   a.Hkv = Hkv;
   a.ntiles_max = ntiles;
+  a.plan = (plan != nullptr && plan_tile_rows == BM && plan_capacity > 0 && plan_capacity <= 65535) ? plan : nullptr;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.kc = static_cast<const __nv_bfloat16*>(kc);
   a.vc = static_cast<const __nv_bfloat16*>(vc);
@@ -519,6 +531,7 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
       return B200_ERR_UNSUPPORTED;   // falls back to the mma.sync kernel
   }
   dim3 grid(Hq / 2, num_seqs, ntiles);
+  if (a.plan) grid = dim3(Hq / 2, plan_capacity, 1);
   kern<<<grid, kThreads, SMEM_BYTES, s>>>(a, tm_q, tm_k, tm_v);
   return launch_result();
 }

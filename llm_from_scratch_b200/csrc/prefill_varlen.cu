@@ -109,7 +109,8 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv,
                        int Dqk, int Dv, float scale, const void* kc, const void* vc,
                        const int32_t* bt, int64_t bt_stride, int bs, int64_t num_blocks,
-                       int32_t* status, cudaStream_t s);
+                       const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
+                       cudaStream_t s);
 
 // tcgen05 path (prefill_umma.cu): head_dim 128, even group size
 int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
@@ -117,9 +118,131 @@ int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, 
                         const int32_t* cu_q, const int32_t* cu_k,
                         int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv, float scale,
                         const void* kc, const void* vc, const int32_t* bt, int64_t bt_stride, int bs,
-                        int64_t num_blocks, int32_t* status, cudaStream_t s);
+                        int64_t num_blocks, const int32_t* plan, int plan_tile_rows, int plan_capacity,
+                        int32_t* status, cudaStream_t s);
 
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Tile list for the tiled prefill kernels: every (sequence, query tile) pair once, tiles with the
+// highest index (most keys under the causal mask) first, so that the long tiles start early and the
+// grid holds no CTA without work.  One CTA: cnt(r) = number of sequences with more than r tiles comes
+// from a difference array (+1 at 0, -1 at n_s) and a prefix sum; tiles of rank r then occupy the
+// positions [sum_{r' > r} cnt(r'), ...) in arbitrary order (an atomic cursor per rank).
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanRanks = 4096;     // most tiles one sequence may have
+
+__device__ __forceinline__ void plan_block_scan(int32_t* v, int32_t* warp_tot) {
+  // inclusive prefix sum of v[0..kPlanRanks) in place; 4 consecutive entries per thread
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int x[4];
+  int sum = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    sum += v[tid * 4 + i];
+    x[i] = sum;
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_tot[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += y;
+    }
+    warp_tot[lane] = w;
+  }
+  __syncthreads();
+  const int base = incl - sum + (warp ? warp_tot[warp - 1] : 0);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[tid * 4 + i] = base + x[i];
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+prefill_plan_kernel(const int32_t* __restrict__ cu_q, int num_seqs, int tile_rows, int32_t* __restrict__ plan,
+                    int capacity, int32_t* status) {
+  __shared__ int32_t first[kPlanRanks];    // difference array -> cnt(r) -> tiles of rank <= r
+  __shared__ int32_t cursor[kPlanRanks];
+  __shared__ int32_t warp_tot[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < kPlanRanks; i += kPlanThreads) first[i] = cursor[i] = 0;
+  __syncthreads();
+  auto tiles_of = [&](int s) {
+    const int len = cu_q[s + 1] - cu_q[s];
+    int n = len > 0 ? (len + tile_rows - 1) / tile_rows : 0;
+    if (n > kPlanRanks) {                  // the host bounds this with max_seqlen_q; a longer row is an error
+      report(status, B200_ERR_BOUNDS);
+      n = kPlanRanks;
+    }
+    return n;
+  };
+  for (int s = tid; s < num_seqs; s += kPlanThreads) {
+    const int n = tiles_of(s);
+    if (n > 0) {
+      atomicAdd(&first[0], 1);
+      if (n < kPlanRanks) atomicAdd(&first[n], -1);
+    }
+  }
+  __syncthreads();
+  plan_block_scan(first, warp_tot);        // cnt(r)
+  plan_block_scan(first, warp_tot);        // tiles of rank <= r
+  const int total = first[kPlanRanks - 1];
+  if (tid == 0) {
+    plan[0] = min(total, capacity);
+    plan[1] = tile_rows;
+    plan[2] = capacity;
+    plan[3] = 0;
+    if (total > capacity) report(status, B200_ERR_WORKSPACE);
+  }
+  for (int s = warp; s < num_seqs; s += kPlanThreads / 32) {
+    const int n = tiles_of(s);
+    for (int r = lane; r < n; r += 32) {
+      const int pos = total - first[r] + atomicAdd(&cursor[r], 1);   // ranks above r come first
+      if (pos < capacity) plan[kPlanHeader + pos] = static_cast<int32_t>((static_cast<uint32_t>(s) << 16) | r);
+    }
+  }
+}
+
+}  // namespace
 }  // namespace b200
+
+extern "C" int32_t b200_prefill_tile_rows(int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
+                                          int32_t head_dim_v, int32_t dtype) {
+  if (dtype != B200_DTYPE_BF16 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return 0;
+  if (head_dim_qk == 128 && head_dim_v == 128 && ((num_q_heads / num_kv_heads) & 1) == 0) return 128;
+  const bool mma = (head_dim_qk == head_dim_v && (head_dim_qk == 32 || head_dim_qk == 64 || head_dim_qk == 128)) ||
+                   (head_dim_qk == 192 && head_dim_v == 128);
+  return mma ? 64 : 0;
+}
+
+extern "C" size_t b200_prefill_plan_bytes(int64_t total_q_tokens, int32_t num_seqs, int32_t tile_rows) {
+  if (total_q_tokens < 0 || num_seqs < 0 || tile_rows <= 0) return 0;
+  const int64_t capacity = (total_q_tokens + tile_rows - 1) / tile_rows + num_seqs;
+  return static_cast<size_t>(b200::kPlanHeader + capacity) * sizeof(int32_t);
+}
+
+extern "C" int b200_prefill_plan(const int32_t* cu_seqlens_q, int32_t num_seqs, int32_t max_seqlen_q,
+                                 int32_t tile_rows, int32_t* plan, size_t plan_bytes, int32_t* status,
+                                 void* stream) {
+  using namespace b200;
+  if (num_seqs < 0 || tile_rows <= 0 || max_seqlen_q < 0 || !plan) return B200_ERR_ARG;
+  if (plan_bytes < (kPlanHeader + 1) * sizeof(int32_t)) return B200_ERR_WORKSPACE;
+  if (num_seqs > 65535 || (max_seqlen_q + tile_rows - 1) / tile_rows > kPlanRanks) return B200_ERR_UNSUPPORTED;
+  if (num_seqs > 0 && !cu_seqlens_q) return B200_ERR_ARG;
+  const int64_t capacity = static_cast<int64_t>(plan_bytes / sizeof(int32_t)) - kPlanHeader;
+  prefill_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      cu_seqlens_q, num_seqs, tile_rows, plan, static_cast<int>(capacity > 2147483647 ? 2147483647 : capacity),
+      status);
+  return launch_result();
+}
 
 extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                                    int64_t q_token_stride, int64_t k_token_stride,
@@ -131,6 +254,7 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
                                    int32_t head_dim_v, float scale, const void* k_cache,
                                    const void* v_cache, const int32_t* block_tables,
                                    int64_t bt_stride, int32_t block_size, int64_t num_blocks,
+                                   const int32_t* plan, int32_t plan_tile_rows, int32_t plan_capacity,
                                    int32_t dtype, int32_t* status, void* stream) {
   using namespace b200;
   if (num_seqs < 0 || max_seqlen_q < 0 || max_seqlen_k < 0 || num_q_heads <= 0 ||
@@ -153,13 +277,14 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
     const int rcu = prefill_umma_launch(q, k, v, out, q_token_stride, k_token_stride, v_token_stride,
                                         total_q_tokens, total_k_tokens, cu_seqlens_q, cu_seqlens_k, num_seqs, max_seqlen_q, num_q_heads,
                                         num_kv_heads, head_dim_qk, head_dim_v, scale, k_cache, v_cache,
-                                        block_tables, bt_stride, block_size, num_blocks, status, s);
+                                        block_tables, bt_stride, block_size, num_blocks, plan, plan_tile_rows,
+                                        plan_capacity, status, s);
     if (rcu != B200_ERR_UNSUPPORTED) return rcu;
     const int rc = prefill_mma_launch(q, k, v, out, q_token_stride, k_token_stride,
                                       v_token_stride, cu_seqlens_q, cu_seqlens_k, num_seqs,
                                       max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk,
                                       head_dim_v, scale, k_cache, v_cache, block_tables, bt_stride,
-                                      block_size, num_blocks, status, s);
+                                      block_size, num_blocks, plan, plan_tile_rows, plan_capacity, status, s);
     if (rc != B200_ERR_UNSUPPORTED) return rc;
   }
 

@@ -77,6 +77,7 @@ class ModelRunner:
         # the GEMM library then meets a few dozen distinct row counts instead of a new one every step,
         # and its per-shape algorithm selection (~0.1 ms per new shape per GEMM) is paid once
         self.prefill_token_multiple = int(_cfg(config, "prefill_token_multiple", default=256))
+        self.max_num_batched_tokens = int(_cfg(config, "max_num_batched_tokens", "max_num_batch_tokens", default=1024))
         torch.cuda.set_device(self.device)
         dtype = _cfg(config, "dtype", default=torch.float32)
         self.dtype = getattr(torch, dtype) if isinstance(dtype, str) else dtype
@@ -93,9 +94,19 @@ class ModelRunner:
         self.staging = _Staging(self.device)
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_vars: dict[str, torch.Tensor] = {}
+        self.prefill_graphs: dict[int, tuple] = {}
+        c = self.model_config
+        if c.attention_type == "MLA":    # prefill runs the expanded form: 192-wide keys, 128-wide values
+            self.prefill_tile_rows = ops.prefill_tile_rows(c.num_heads, c.num_heads, c.head_dim + c.rope_dim,
+                                                           c.head_dim, self.dtype)
+        else:
+            self.prefill_tile_rows = ops.prefill_tile_rows(c.num_heads, c.num_kv_heads, c.head_dim, c.head_dim,
+                                                           self.dtype)
         self.allocate_kv_cache()
         if not self.enforce_eager:
             self.capture_cudagraph()
+            if self.prefill_tile_rows and _cfg(config, "prefill_graphs", default=True):
+                self.capture_prefill_graphs()
 
     # ------------------------------------------------------------------ KV pool
     def kv_block_bytes(self) -> int:
@@ -148,8 +159,12 @@ class ModelRunner:
             arrays["positions"] = np.concatenate([m.positions, np.zeros(pad, dtype=m.positions.dtype)])
             arrays["slot_mapping"] = np.concatenate([m.slot_mapping, np.full(pad, -1, dtype=m.slot_mapping.dtype)])
         t = self.staging.upload(arrays)
+        plan = None
+        if m.is_prefill and self.prefill_tile_rows:
+            # one tile list per step, shared by the attention calls of all layers
+            plan = ops.prefill_plan(t["cu_seqlens_q"], len(arrays["input_ids"]), m.max_seqlen_q, self.prefill_tile_rows)
         set_context(m.is_prefill, t.get("cu_seqlens_q"), t.get("cu_seqlens_k"), m.max_seqlen_q, m.max_seqlen_k,
-                    t["slot_mapping"], t.get("context_lens"), t.get("block_tables"), t["positions"])
+                    t["slot_mapping"], t.get("context_lens"), t.get("block_tables"), t["positions"], plan)
         return t["input_ids"]
 
     def prepare_prefill(self, seqs: list[Sequence]) -> torch.Tensor:
@@ -185,6 +200,8 @@ class ModelRunner:
     def run(self, seqs: list[Sequence], is_prefill: bool) -> list[int]:
         if not is_prefill and self.graphs and not self.enforce_eager and len(seqs) <= max(self.graphs):
             logits = self._replay_decode(seqs)
+        elif is_prefill and self.prefill_graphs and (logits := self._replay_prefill(seqs)) is not None:
+            pass
         else:
             input_ids = self.prepare_prefill(seqs) if is_prefill else self.prepare_decode(seqs)
             logits = self.run_model(input_ids, is_prefill)
@@ -221,6 +238,92 @@ class ModelRunner:
         logits = self.run_model(input_ids, is_prefill).float().clone()
         reset_context()
         return logits
+
+    # ------------------------------------------------------------------ CUDA graphs for prefill
+    def _prefill_layout(self, tokens: int):
+        """Byte offsets of (cu_seqlens, input_ids, positions, slot_mapping) of a padded prefill batch in
+        the prefill staging buffer: one contiguous run, so a step is one host-to-device copy."""
+        n_cu = self.max_num_seqs + 1
+        o_ids = (n_cu * 4 + 15) & ~15
+        return 0, o_ids, o_ids + tokens * 8, o_ids + 2 * tokens * 8, o_ids + 3 * tokens * 8
+
+    @torch.inference_mode()
+    def capture_prefill_graphs(self) -> None:
+        """One graph per padded token count (multiples of ``prefill_token_multiple`` up to
+        ``max_num_batched_tokens``).  The buffers have fixed sizes — cu_seqlens for ``max_num_seqs``
+        sequences (unused ones have length 0), token arrays padded with slot -1 — and the attention
+        grid comes from the step's tile list, so nothing in the launch sequence depends on the batch."""
+        mult = max(self.prefill_token_multiple, 1)
+        buckets = list(range(mult, self.max_num_batched_tokens + 1, mult))
+        if not buckets or len(buckets) > 64:
+            return
+        dev, tmax, n_cu = self.device, buckets[-1], self.max_num_seqs + 1
+        total = self._prefill_layout(tmax)[-1]
+        self.prefill_dev = torch.zeros(total, dtype=torch.uint8, device=dev)
+        self.prefill_host = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        self.prefill_out = torch.zeros(tmax, self.model_config.d_model, dtype=self.dtype, device=dev)
+        plan_entries = ops.lib.b200_prefill_plan_bytes(tmax, self.max_num_seqs, self.prefill_tile_rows) // 4
+        self.prefill_plan_buffer = torch.zeros(plan_entries, dtype=torch.int32, device=dev)
+        pool = self.graphs[max(self.graphs)].pool() if self.graphs else None
+        for tokens in reversed(buckets):
+            o_cu, o_ids, o_pos, o_slot, _end = self._prefill_layout(tokens)
+            view = lambda off, n, dt: self.prefill_dev[off:off + n * dt.itemsize].view(dt)
+            cu = view(o_cu, n_cu, torch.int32)
+            ids, pos, slots = (view(o, tokens, torch.int64) for o in (o_ids, o_pos, o_slot))
+            slots.fill_(-1)
+            cu.zero_()
+
+            def body():
+                plan = ops.prefill_plan(cu, tokens, tokens, self.prefill_tile_rows, buffer=self.prefill_plan_buffer)
+                set_context(True, cu, cu, tokens, tokens, slots, None, None, pos, plan)
+                self.prefill_out[:tokens] = self.model(ids)
+
+            body()                                   # warm-up: allocates workspaces, selects GEMM algorithms
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool):
+                body()
+            if pool is None:
+                pool = g.pool()
+            self.prefill_graphs[tokens] = (g, cu, ids, pos, slots)
+            torch.cuda.synchronize()
+            reset_context()
+
+    @torch.inference_mode()
+    def _replay_prefill(self, seqs: list[Sequence]):
+        """Prefill step from a captured graph, or None when the batch does not fit one (a cached
+        prefix, which needs block tables, or more tokens / sequences than were captured)."""
+        if len(seqs) > self.max_num_seqs:
+            return None
+        m = md.prepare_prefill(seqs, self.block_size)
+        if m.block_tables is not None:
+            return None
+        T, n = len(m.input_ids), len(seqs)
+        if len(m.slot_mapping) != T:
+            raise RuntimeError("slot_mapping and input_ids disagree: Sequence.reference_exact must be off "
+                               "when the model runs (it reproduces a reference defect at block multiples)")
+        mult = self.prefill_token_multiple
+        tokens = max((T + mult - 1) // mult * mult, mult)
+        entry = self.prefill_graphs.get(tokens)
+        if entry is None:
+            return None
+        g, cu, ids, pos, slots = entry
+        o_cu, o_ids, o_pos, o_slot, end = self._prefill_layout(tokens)
+        hb = self.prefill_host.numpy()
+        h_cu = hb[o_cu:o_cu + (self.max_num_seqs + 1) * 4].view(np.int32)
+        h_ids, h_pos, h_slot = (hb[o:o + tokens * 8].view(np.int64) for o in (o_ids, o_pos, o_slot))
+        h_cu[:n + 1] = m.cu_seqlens_q
+        h_cu[n + 1:] = T
+        h_ids[:T] = m.input_ids
+        h_ids[T:] = 0
+        h_pos[:T] = m.positions
+        h_pos[T:] = 0
+        h_slot[:T] = m.slot_mapping
+        h_slot[T:] = -1
+        self.prefill_dev[:end].copy_(self.prefill_host[:end], non_blocking=True)
+        g.replay()
+        set_context(True, cu[:n + 1], cu[:n + 1], m.max_seqlen_q, m.max_seqlen_k, slots, None, None, pos)
+        return self.model.compute_logits(self.prefill_out[:tokens])
 
     # ------------------------------------------------------------------ CUDA graphs for decode
     @torch.inference_mode()
@@ -274,4 +377,5 @@ class ModelRunner:
     def exit(self) -> None:
         self.graphs.clear()
         self.graph_vars.clear()
+        self.prefill_graphs.clear()
         torch.cuda.synchronize()

@@ -83,16 +83,51 @@ def store(steps: int = 50, warmup: int = 5, tokens: int = 262144) -> dict:
                 ms=ms, tokens=tokens, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, launches_per_call=1)
 
 
+def moe_experts(steps: int = 20, warmup: int = 3, tokens: int = 256, layers: int = 12) -> dict:
+    """Expert GEMMs of the GQA+MoE decoder at decode size: ``tokens`` tokens routed top-2 over 16 experts
+    (d_model 1024, d_ff 704, bf16); per layer the grouped up-projection + SwiGLU and the grouped
+    down-projection stream 69 MB of expert weights.  ``layers`` distinct weight sets (0.83 GB) are run
+    back to back from one CUDA graph, so no weight stays in L2 between uses, as in the model."""
+    E, d, dff, K = 16, 1024, 704, 2
+    g = torch.Generator(device="cuda").manual_seed(6)
+    w13 = [(torch.randn(E, 2 * dff, d, generator=g, device="cuda") * d ** -0.5).bfloat16() for _ in range(layers)]
+    w2 = [(torch.randn(E, d, dff, generator=g, device="cuda") * dff ** -0.5).bfloat16() for _ in range(layers)]
+    b13 = torch.randn(E, 2 * dff, generator=g, device="cuda").bfloat16()
+    logits = torch.randn(tokens, E, generator=g, device="cuda").bfloat16()
+    _tok, _experts, _w, offs, _inv = ops.moe_route(logits, torch.zeros(E, device="cuda"), K)
+    xs = torch.randn(tokens * K, d, generator=g, device="cuda").bfloat16()
+
+    def all_layers():
+        for i in range(layers):
+            ops.moe_grouped_gemm(ops.moe_grouped_gemm(xs, w13[i], offs, b13, swiglu=True), w2[i], offs)
+
+    all_layers()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        all_layers()
+    ms = _time(graph.replay, steps, warmup) / layers
+    ops.check_status()
+    nbytes = (w13[0].numel() + w2[0].numel()) * 2 + tokens * K * (d + 2 * dff + d) * 2
+    return dict(workload=f"MoE expert GEMMs, decode size: {tokens} tokens top-2 over 16 experts, d 1024, d_ff 704, "
+                         f"bf16; {layers} layers from one CUDA graph", ms=ms, us_per_layer=ms * 1e3,
+                algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, launches_per_call=2)
+
+
 C3_MODEL = dict(vocab_size=32000, context_length=2048, d_model=1024, num_layers=16, num_heads=16, num_kv_heads=4,
                 d_ff=704, attention_type="GQA", use_moe=True, n_routed_experts=16, num_experts_per_tok=2,
                 n_shared_experts=1)
 
 
-def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None = None) -> dict:
+def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None = None,
+           pool_blocks: int = 110000) -> dict:
     """End-to-end continuous batching, GQA+MoE decoder (d_model 1024, 16 layers, 16/4 heads, head_dim 64,
     16 experts top-2 + shared, d_ff 704, vocab 32000), bf16, random init (seed 0): ``batch`` requests,
     prompts uniform [64,1024], outputs geometric(mean 256) capped at 1024, max 256 sequences and 8192
     batched tokens per step, KV block 16; arrivals Poisson with ``rate`` requests/s, or all at t = 0.
+    The KV pool holds ``pool_blocks`` blocks of 256 KiB (110,000 = 27 GB: the cumulative demand of the
+    2048 requests, so no request is preempted and re-prefilled; the scheduler admits waiting requests
+    before it decodes, whatever the number already running, and fills any smaller pool).
     Under torchrun every rank is an independent replica serving requests rank, rank + N, ...; the
     aggregate is tokens of all replicas / the slowest replica's wall time.  ``steps``/``warmup`` unused."""
     import itertools
@@ -116,7 +151,7 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
     def make_engine(rank):
         Sequence.counter = itertools.count()
         cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
-                   max_num_batched_tokens=8192, max_cached_blocks=40000, eos=-1, device=f"cuda:{local_rank}",
+                   max_num_batched_tokens=8192, max_cached_blocks=pool_blocks, eos=-1, device=f"cuda:{local_rank}",
                    max_model_length=2048, seed=0)
         t0 = time.perf_counter()
         built["engine"] = LLMEngine(cfg)
@@ -146,4 +181,4 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
                 replicas=world, requests=batch, generated_tokens=gen, prompt_tokens=prompt_tokens, wall_s=wall,
                 replica_wall_s=[r.wall_s for r in reports], steps=[r.steps for r in reports],
                 output_tokens_per_s=gen / wall, total_tokens_per_s=(gen + prompt_tokens) / wall,
-                engine_build_s=built["build_s"], cuda_graphs=graphs, rank0_timing=timing)
+                engine_build_s=built["build_s"], cuda_graphs=graphs, kv_pool_blocks=pool_blocks, rank0_timing=timing)

@@ -264,10 +264,10 @@ class GQAAttention(nn.Module):
             if ctx.block_tables is not None:   # part of the context is already cached
                 o = ops.prefill_varlen(q, None, None, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
                                        ctx.max_seqlen_k, self.scale, self.k_cache, self.v_cache, ctx.block_tables,
-                                       out=out)
+                                       out=out, plan=ctx.prefill_plan)
             else:
                 o = ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                       ctx.max_seqlen_k, self.scale, out=out)
+                                       ctx.max_seqlen_k, self.scale, out=out, plan=ctx.prefill_plan)
         else:
             o = ops.paged_decode_gqa(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens, self.scale)
         return F.linear(o.view(T, self.d), self.w_o, self.b_o)
@@ -331,7 +331,7 @@ class MLAAttention(nn.Module):
         v = torch.einsum("tk,hdk->thd", c, self.w_uv).contiguous()
         q = torch.cat([q_nope, q_rope], dim=-1)
         return ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                  ctx.max_seqlen_k, self.scale, out=out)
+                                  ctx.max_seqlen_k, self.scale, out=out, plan=ctx.prefill_plan)
 
     def _gather_context_rows(self, ctx):
         """Packed latent rows of every sequence's full context, read back through the block tables."""

@@ -152,12 +152,13 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
                    cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int,
                    max_seqlen_k: int, scale: float, k_cache: torch.Tensor | None = None,
                    v_cache: torch.Tensor | None = None, block_tables: torch.Tensor | None = None,
-                   out: torch.Tensor | None = None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, plan: "PrefillPlan | None" = None) -> torch.Tensor:
     """Causal attention over packed ragged sequences.
 
     q: [Tq, Hq, Dqk].  Without ``block_tables``: k [Tk, Hkv, Dqk], v [Tk, Hkv, Dv] are the packed
     keys/values.  With ``block_tables`` (a cached prefix exists) keys/values are read from the
-    paged caches [num_blocks, block_size, Hkv, D*].  Returns out [Tq, Hq, Dv].
+    paged caches [num_blocks, block_size, Hkv, D*].  Returns out [Tq, Hq, Dv].  ``plan``: a tile list from
+    ``prefill_plan`` for the same ``cu_seqlens_q`` (one CTA per real tile, longest first).
     """
     dev = _cuda(q, k, v, cu_seqlens_q, cu_seqlens_k, k_cache, v_cache, block_tables, out)
     Tq, Hq, Dqk = q.shape
@@ -202,9 +203,49 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
     check(lib.b200_prefill_varlen(q.data_ptr(), kp, vp, out.data_ptr(), q.stride(0), ks, vs, Tq, total_k,
                                   cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
                                   int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, Dqk, Dv,
-                                  float(scale), kcp, vcp, btp, bts, bs, nb, _dt(q),
+                                  float(scale), kcp, vcp, btp, bts, bs, nb,
+                                  plan.buffer.data_ptr() if plan is not None else None,
+                                  plan.tile_rows if plan is not None else 0,
+                                  plan.capacity if plan is not None else 0, _dt(q),
                                   status_word(dev).data_ptr(), _stream()), "prefill_varlen")
     return out
+
+
+class PrefillPlan:
+    """Device-side tile list shared by all prefill attention calls of one step (``prefill_plan``)."""
+
+    __slots__ = ("buffer", "tile_rows", "capacity")
+
+    def __init__(self, buffer: torch.Tensor, tile_rows: int, capacity: int):
+        self.buffer, self.tile_rows, self.capacity = buffer, tile_rows, capacity
+
+
+def prefill_tile_rows(Hq: int, Hkv: int, Dqk: int, Dv: int, dtype: torch.dtype) -> int:
+    """Query rows per tile of the prefill kernel serving this shape; 0 = no tiled kernel (no plan)."""
+    if dtype not in _DTYPES:
+        return 0
+    return int(lib.b200_prefill_tile_rows(Hq, Hkv, Dqk, Dv, _DTYPES[dtype]))
+
+
+def prefill_plan(cu_seqlens_q: torch.Tensor, total_q_tokens: int, max_seqlen_q: int, tile_rows: int,
+                 buffer: torch.Tensor | None = None) -> PrefillPlan | None:
+    """Builds the tile list of a prefill step on the device (one small launch).  ``total_q_tokens`` and
+    ``max_seqlen_q`` are host-side upper bounds; ``buffer`` (int32) may be supplied to keep the plan
+    at a fixed address (graph capture).  Returns None when no tiled kernel applies (tile_rows == 0)."""
+    if tile_rows <= 0:
+        return None
+    dev = _cuda(cu_seqlens_q, buffer)
+    if cu_seqlens_q.dtype != torch.int32:
+        raise ValueError("cu_seqlens must be int32")
+    num_seqs = cu_seqlens_q.numel() - 1
+    nbytes = int(lib.b200_prefill_plan_bytes(total_q_tokens, num_seqs, tile_rows))
+    if buffer is None:
+        buffer = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
+    elif buffer.dtype != torch.int32 or buffer.numel() * 4 < nbytes or not buffer.is_contiguous():
+        raise ValueError(f"plan buffer must be contiguous int32 with at least {nbytes // 4} entries")
+    check(lib.b200_prefill_plan(cu_seqlens_q.data_ptr(), num_seqs, int(max_seqlen_q), tile_rows, buffer.data_ptr(),
+                                buffer.numel() * 4, status_word(dev).data_ptr(), _stream()), "prefill_plan")
+    return PrefillPlan(buffer, tile_rows, buffer.numel() - 4)
 
 
 def mla_decode(q_abs: torch.Tensor, q_rope: torch.Tensor, latent_cache: torch.Tensor,

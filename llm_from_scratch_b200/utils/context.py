@@ -23,6 +23,7 @@ class Context:
     block_tables: Optional[torch.Tensor] = None   # int32 [batch, max_blocks], -1 padded
     # not in the reference (its runner builds no positions although the model needs them for RoPE):
     positions: Optional[torch.Tensor] = None      # int64 [num_tokens]; None in decode = context_lens - 1
+    prefill_plan: object = None                   # ops.PrefillPlan of this step's cu_seqlens_q, or None
 
 
 _current = Context()
@@ -33,10 +34,11 @@ def get_context() -> Context:
 
 
 def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
-                slot_mapping=None, context_lens=None, block_tables=None, positions=None) -> None:
+                slot_mapping=None, context_lens=None, block_tables=None, positions=None,
+                prefill_plan=None) -> None:
     global _current
     _current = Context(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                       slot_mapping, context_lens, block_tables, positions)
+                       slot_mapping, context_lens, block_tables, positions, prefill_plan)
 
 
 def reset_context() -> None:

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} declared in b200llm.h but not exported"
     assert set(_lib.SIGNATURES) == set(declared_functions())
-    assert _lib.lib.b200_abi_version() == 3
+    assert _lib.lib.b200_abi_version() == 4
     assert _lib.lib.b200_strerror(-3) == b"unsupported shape or dtype"
 
 
@@ -40,7 +40,12 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.b200_paged_decode_gqa(None, None, None, None, None, 0, None, 1, 7, 2, 64, 16, 1, 1.0,
                                      None, 0, 1, None, None) == -1  # 7 heads not divisible by 2
     assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, 1, 1, None, None, 1, 1, 1, 4, 4, 64, 64,
-                                   1.0, None, None, None, 0, 0, 0, 5, None, None) == -3  # bad dtype
+                                   1.0, None, None, None, 0, 0, 0, None, 0, 0, 5, None, None) == -3  # bad dtype
+    assert lib.b200_prefill_tile_rows(32, 8, 128, 128, 1) == 128      # tcgen05 kernel
+    assert lib.b200_prefill_tile_rows(16, 4, 64, 64, 1) == 64         # mma.sync kernel
+    assert lib.b200_prefill_tile_rows(16, 4, 64, 64, 0) == 0          # fp32: general kernel only
+    assert lib.b200_prefill_plan_bytes(1000, 7, 64) == (4 + 16 + 7) * 4
+    assert lib.b200_prefill_plan(None, 1, 10, 64, None, 0, None, None) == -1
     assert lib.b200_mla_decode(None, None, None, None, None, 0, None, 1, 16, 512, 64, 16, 1, 1.0,
                                None, 0, 1, None, None) == -1  # bt_stride 0
 

@@ -252,6 +252,42 @@ def test_prefill_varlen_matches_oracle(dtype, Hq, Hkv, D):
     assert_close(got, want, dtype)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(16, 4, 64), (32, 8, 128), (4, 4, 32)])
+def test_prefill_plan_lists_every_tile_once_and_gives_identical_output(Hq, Hkv, D):
+    """The tile list holds every (sequence, tile) pair exactly once, highest tiles first; attention
+    launched from it is bit-identical to the (sequence x tile rank) grid, also when cu_seqlens has
+    unused trailing sequences and q has padding rows (the fixed-size buffers of a captured step)."""
+    ops = _ops()
+    lens = [300, 0, 1, 64, 65, 700, 128, 5]
+    q, k, v, cu = _prefill_inputs(lens, Hq, Hkv, D, D, torch.bfloat16, seed=77)
+    q, k, v, cu = q.cuda(), k.cuda(), v.cuda(), cu.cuda()
+    scale = D ** -0.5
+    rows = ops.prefill_tile_rows(Hq, Hkv, D, D, torch.bfloat16)
+    assert rows == (128 if D == 128 else 64)
+    plan = ops.prefill_plan(cu, sum(lens), max(lens), rows)
+    ops.check_status()
+    buf = plan.buffer.cpu().numpy()
+    want_tiles = sorted((s, t) for s, L in enumerate(lens) for t in range((L + rows - 1) // rows))
+    assert buf[0] == len(want_tiles) and buf[1] == rows and buf[2] == plan.capacity
+    entries = buf[4:4 + buf[0]].astype(np.uint32)
+    assert sorted((int(e >> 16), int(e & 0xffff)) for e in entries) == want_tiles
+    ranks = (entries & 0xffff).astype(np.int64)
+    assert (ranks[1:] <= ranks[:-1]).all()
+    base = ops.prefill_varlen(q, k, v, cu, cu, max(lens), max(lens), scale)
+    planned = ops.prefill_varlen(q, k, v, cu, cu, max(lens), max(lens), scale, plan=plan)
+    ops.check_status()
+    assert torch.equal(base, planned)
+    # fixed-size buffers: 3 unused sequences, 100 padding rows, bounds instead of exact sizes
+    T = sum(lens)
+    pad = lambda x: torch.cat([x, torch.zeros(100, *x.shape[1:], dtype=x.dtype, device="cuda")])
+    cu_pad = torch.cat([cu, cu[-1:].expand(3)]).contiguous()
+    plan2 = ops.prefill_plan(cu_pad, T + 100, T + 100, rows)
+    out = torch.zeros(T + 100, Hq, D, dtype=torch.bfloat16, device="cuda")
+    ops.prefill_varlen(pad(q), pad(k), pad(v), cu_pad, cu_pad, T + 100, T + 100, scale, out=out, plan=plan2)
+    ops.check_status()
+    assert torch.equal(out[:T], base) and (out[T:] == 0).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prefill_varlen_with_cached_prefix_through_block_tables(dtype):
     ops, orc = _ops(), _oracle()
@@ -635,7 +671,7 @@ def test_empty_inputs_are_no_ops():
     assert lib.b200_mla_decode(None, None, None, None, None, 1, None, 0, 16, 512, 64, 16, 2, 0.07, None, 0,
                                DTYPE_BF16, None, s) == 0
     assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, 0, 0, None, None, 0, 0, 0, 8, 2, 64, 64, 0.125,
-                                   None, None, None, 0, 0, 0, DTYPE_BF16, None, s) == 0
+                                   None, None, None, 0, 0, 0, None, 0, 0, DTYPE_BF16, None, s) == 0
     # a batch whose contexts are all empty: zero rows, no block is read
     q = torch.randn(3, 8, 64, device=dev).bfloat16()
     bt = torch.full((3, 4), -1, dtype=torch.int32, device=dev)
