@@ -279,28 +279,40 @@ def main():
     ms_step = ms_total / args.steps
 
     # ---------------------------------------------------------------- end-to-end with host inputs
-    hq = torch.randn(BATCH, HQ, D).to(torch.bfloat16).pin_memory()
-    hk = torch.randn(BATCH, HKV, D).to(torch.bfloat16).pin_memory()
-    hv = torch.randn(BATCH, HKV, D).to(torch.bfloat16).pin_memory()
-    hslots = torch.from_numpy(case.slot_mapping).pin_memory()
-    hbt = torch.from_numpy(case.block_tables).pin_memory()
-    hcl = torch.from_numpy(case.context_lens).pin_memory()
+    # The step's inputs live in one pinned host buffer and are shipped with a single copy (as the engine's
+    # model runner does with its step metadata); typed views of the device copy go to the kernels.
+    fields = [("q", torch.bfloat16, (BATCH, HQ, D)), ("k", torch.bfloat16, (BATCH, HKV, D)),
+              ("v", torch.bfloat16, (BATCH, HKV, D)), ("slots", torch.int64, (BATCH,)),
+              ("cl", torch.int64, (BATCH,)), ("bt", torch.int32, tuple(case.block_tables.shape))]
+    offs, total = {}, 0
+    for name, dt, shape in fields:
+        offs[name] = total
+        total += (int(np.prod(shape)) * torch.empty(0, dtype=dt).element_size() + 255) & ~255
+    hbuf = torch.empty(total, dtype=torch.uint8).pin_memory()
+    dbuf = torch.empty(total, dtype=torch.uint8, device=dev)
+
+    def views(buf):
+        out_ = {}
+        for name, dt, shape in fields:
+            n = int(np.prod(shape)) * torch.empty(0, dtype=dt).element_size()
+            out_[name] = buf[offs[name]:offs[name] + n].view(dt).view(*shape)
+        return out_
+
+    hv_, dv_ = views(hbuf), views(dbuf)
+    hv_["q"].copy_(torch.randn(BATCH, HQ, D).to(torch.bfloat16))
+    hv_["k"].copy_(torch.randn(BATCH, HKV, D).to(torch.bfloat16))
+    hv_["v"].copy_(torch.randn(BATCH, HKV, D).to(torch.bfloat16))
+    hv_["slots"].copy_(torch.from_numpy(case.slot_mapping))
+    hv_["cl"].copy_(torch.from_numpy(case.context_lens))
+    hv_["bt"].copy_(torch.from_numpy(case.block_tables))
     hout = torch.empty(BATCH, HQ, D, dtype=torch.bfloat16).pin_memory()
-    dq, dk, dv = torch.empty_like(q), torch.empty(BATCH, HKV, D, dtype=torch.bfloat16, device=dev), \
-        torch.empty(BATCH, HKV, D, dtype=torch.bfloat16, device=dev)
-    dslots, dbt, dcl = torch.empty_like(cl), torch.empty_like(bt), torch.empty_like(cl)
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hslots, hbt, hcl))
+    h2d = sum(t.numel() * t.element_size() for t in hv_.values())
     d2h = hout.numel() * hout.element_size()
 
     def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        dslots.copy_(hslots, non_blocking=True)
-        dbt.copy_(hbt, non_blocking=True)
-        dcl.copy_(hcl, non_blocking=True)
-        ops.store_kvcache(dk, dv, kc, vc, dslots)
-        ops.paged_decode_gqa(dq, kc, vc, dbt, dcl, scale, out=out)
+        dbuf.copy_(hbuf, non_blocking=True)
+        ops.store_kvcache(dv_["k"], dv_["v"], kc, vc, dv_["slots"])
+        ops.paged_decode_gqa(dv_["q"], kc, vc, dv_["bt"], dv_["cl"], scale, out=out)
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
