@@ -84,7 +84,12 @@ class ModelRunner:
         if model is None:
             mc = config["model"]
             mc = mc if isinstance(mc, ModelConfig) else ModelConfig.from_dict(mc)
-            weights = _cfg(config, "weights", default=None) or init_reference_order(mc, _cfg(config, "seed", default=0))
+            weights = _cfg(config, "weights", "model_path", default=None)
+            if isinstance(weights, (str, bytes)) or hasattr(weights, "__fspath__"):
+                from ..utils.loader import load_weights     # a checkpoint in one of the reference's formats
+                weights = load_weights(str(weights))
+            if weights is None:
+                weights = init_reference_order(mc, _cfg(config, "seed", default=0))
             model = EngineTransformerLM(mc, weights, self.device, self.dtype)
         self.model = model
         self.model_config = model.cfg

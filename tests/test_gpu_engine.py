@@ -193,3 +193,40 @@ def test_generate_api_and_temperature_sampling():
     out = eng.generate(prompts, [SamplingParams(temperature=0.8, max_tokens=6, ignore_eos=True)] * 3)
     assert [len(t) for t in out["token_ids"]] == [5, 5, 5]
     assert all(0 <= t < 10000 for s in out["token_ids"] for t in s)
+
+
+def test_engine_loads_a_training_checkpoint_from_disk(tmp_path):
+    """``weights`` given as a path in the reference's checkpoint format: same streams as the dict."""
+    from llm_from_scratch_b200.engine import SamplingParams
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    z = load("c1_model.npz")
+    weights = init_reference_order(ModelConfig.from_dict(C1), 0)
+    torch.save({"model_state_dict": {"_orig_mod." + k: v for k, v in weights.items()}, "iteration": 10},
+               tmp_path / "final_model.pt")
+    eng = make_engine(C1, str(tmp_path), eager=True)
+    out = eng.generate(prompts_of(z)[:2], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert out["token_ids"] == [s[:5] for s in z["streams"].tolist()[:2]]
+
+
+def test_bf16_moe_engine_prefill_and_decode_graphs_match_eager():
+    """bf16 GQA+MoE decoder: steps replayed from CUDA graphs (prefill per padded token count with the
+    device-built tile list, decode per batch bucket) give the same greedy streams as eager launches."""
+    from llm_from_scratch_b200.engine import SamplingParams
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    cfg = dict(vocab_size=500, context_length=256, d_model=256, num_layers=2, num_heads=4, num_kv_heads=2, d_ff=192,
+               attention_type="GQA", use_moe=True, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1)
+    weights = init_reference_order(ModelConfig.from_dict(cfg), 5)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 500, (int(n),), generator=g).tolist() for n in (5, 64, 17, 130, 33, 1, 96)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    streams = {}
+    for eager in (True, False):
+        eng = make_engine(cfg, weights, dtype=torch.bfloat16, eager=eager, max_num_batched_tokens=512)
+        if not eager:
+            assert eng.model_runner.prefill_graphs and eng.model_runner.graphs
+        streams[eager] = eng.generate(prompts, sp)["token_ids"]
+        if not eager:
+            assert eng.timing["prefill_steps"] >= 1
+        eng.exit()
+    same = sum(a == b for a, b in zip(streams[True], streams[False]))
+    assert same == len(prompts), (streams[True], streams[False])
