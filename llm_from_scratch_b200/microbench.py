@@ -188,3 +188,70 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
                 replica_wall_s=[r.wall_s for r in reports], steps=[r.steps for r in reports],
                 output_tokens_per_s=gen / wall, total_tokens_per_s=(gen + prompt_tokens) / wall,
                 engine_build_s=built["build_s"], cuda_graphs=graphs, kv_pool_blocks=pool_blocks, rank0_timing=timing)
+
+
+C4_MODEL = dict(vocab_size=32000, context_length=16640, d_model=2048, num_layers=12, num_heads=16, d_ff=1024,
+                attention_type="MLA", kv_lora_rank=512, q_lora_rank=1024, rope_dim=64, use_moe=True,
+                n_routed_experts=32, num_experts_per_tok=4, n_shared_experts=1)
+
+
+def engine_mla(steps: int = 10, warmup: int = 3, batch: int = 240, prefills: int = 16) -> dict:
+    """Mixed ragged steps of the MLA+MoE decoder (d_model 2048, 12 layers, 16 heads, latent 512 + 64,
+    q_lora 1024, 32 experts top-4 + shared, d_ff 1024, vocab 32000; bf16, random init seed 0) through the
+    engine: every step is one prefill call of ``prefills`` new prompts (lengths uniform [256,4096]) and one
+    decode call of ``batch`` running sequences (contexts uniform [512,16384]); the scheduler never mixes
+    the two in one call.  The decode sequences enter with their blocks allocated and a latent cache of
+    random rows (their contexts are not prefilled: 2 M tokens of set-up that the step does not contain)."""
+    import itertools
+    import time
+
+    from .engine import SamplingParams, Sequence
+    from .engine.llm_engine import LLMEngine
+    from .engine.sequence import SequenceStatus
+    steps = min(steps, 20)
+    rng = np.random.default_rng(4)
+    ctx = rng.integers(512, 16384 + 1, size=batch)
+    plens = rng.integers(256, 4096 + 1, size=(steps + warmup, prefills))
+    need = int(sum((int(c) + steps + warmup + 15) // 16 + 1 for c in ctx)) + prefills * 257 + 64
+    Sequence.counter = itertools.count()
+    cfg = dict(model=C4_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
+               max_num_batched_tokens=prefills * 4096, max_cached_blocks=need, eos=-1, device="cuda:0",
+               max_model_length=16640, seed=0, prefill_graphs=False)
+    t0 = time.perf_counter()
+    eng = LLMEngine(cfg)
+    build_s = time.perf_counter() - t0
+    eng.model_runner.kv_cache.normal_(0.0, 0.3)
+    sched = eng.scheduler
+    for c in ctx:            # running sequences in the state a prefill leaves: c - 1 tokens cached, one sampled
+        seq = Sequence(rng.integers(0, 32000, size=int(c) - 1).tolist(),
+                       SamplingParams(temperature=0.0, max_tokens=1 << 20, ignore_eos=True))
+        sched.block_manager.allocate(seq)
+        seq.append_token(int(rng.integers(0, 32000)))
+        seq.status = SequenceStatus.RUNNING
+        sched.running.append(seq)
+    times = dict(prefill=[], decode=[])
+    tokens = dict(prefill=0, decode=0)
+    for it in range(steps + warmup):
+        for n in plens[it]:  # finish right after their first token, freeing their blocks
+            eng.add_request(rng.integers(0, 32000, size=int(n)).tolist(),
+                            SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+        for kind in ("prefill", "decode"):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            _out, n, is_prefill = eng.step()
+            torch.cuda.synchronize()
+            assert is_prefill == (kind == "prefill"), (kind, is_prefill)
+            if it >= warmup:
+                times[kind].append(time.perf_counter() - t0)
+                tokens[kind] += n
+    ops.check_status()
+    graphs = bool(eng.model_runner.graphs)
+    eng.exit()
+    pre, dec = float(np.mean(times["prefill"])), float(np.mean(times["decode"]))
+    return dict(workload=f"MLA+MoE decoder, mixed steps: {prefills} prefills U[256,4096] + {batch} decodes with "
+                         "contexts U[512,16384] per step, bf16", ms=(pre + dec) * 1e3, prefill_ms=pre * 1e3,
+                decode_ms=dec * 1e3, prefill_tokens_per_step=tokens["prefill"] / steps,
+                decode_tokens_per_step=tokens["decode"] / steps,
+                tokens_per_s=(tokens["prefill"] + tokens["decode"]) / steps / (pre + dec),
+                decode_tokens_per_s=tokens["decode"] / steps / dec, prefill_tokens_per_s=tokens["prefill"] / steps / pre,
+                context_tokens=int(ctx.sum()), engine_build_s=build_s, cuda_graphs=graphs)
