@@ -4,8 +4,6 @@
 //
 // Generic path: one CTA per (sequence, head), 4 warps striding over the tokens, a lane owning the
 // row elements lane, lane+32, ...; fp32 online softmax, warps merged through shared memory.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace b200 {
@@ -114,11 +112,6 @@ int mla_decode_mma_launch(const void* q_abs, const void* q_rope, const void* lat
                           void* workspace, size_t workspace_bytes, int32_t* status,
                           cudaStream_t s);
 size_t mla_decode_mma_workspace(int batch, int H, int r, int dr);
-// tcgen05 path (mla_decode_umma.cu), same shapes and workspace
-int mla_decode_umma_launch(const void* q_abs, const void* q_rope, const void* lat, void* out,
-                           const int32_t* bt, int64_t bt_stride, const int64_t* lens, int batch, int H,
-                           int r, int dr, int bs, int64_t num_blocks, float scale, void* workspace,
-                           size_t workspace_bytes, int32_t* status, cudaStream_t s);
 }  // namespace b200
 
 extern "C" size_t b200_mla_decode_workspace_bytes(int32_t batch, int32_t num_heads,
@@ -148,16 +141,6 @@ extern "C" int b200_mla_decode(const void* q_abs, const void* q_rope, const void
   if (num_blocks > 0 && !latent_cache) return B200_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == B200_DTYPE_BF16) {
-    static const bool use_umma = [] {              // TEMPORARY A/B switch
-      const char* e = getenv("B200_MLA_KERNEL");
-      return e && e[0] == 'u';
-    }();
-    if (use_umma) {
-      const int rcu = mla_decode_umma_launch(q_abs, q_rope, latent_cache, out_latent, block_tables, bt_stride,
-                                             context_lens, batch, num_heads, kv_lora_rank, rope_dim, block_size,
-                                             num_blocks, scale, workspace, workspace_bytes, status, s);
-      if (rcu != B200_ERR_UNSUPPORTED) return rcu;
-    }
     const int rc = mla_decode_mma_launch(q_abs, q_rope, latent_cache, out_latent, block_tables,
                                          bt_stride, context_lens, batch, num_heads, kv_lora_rank,
                                          rope_dim, block_size, num_blocks, scale, workspace,
