@@ -47,7 +47,9 @@ def mla_decode(steps: int = 50, warmup: int = 5, batch: int = 240) -> dict:
 
 
 def prefill(steps: int = 5, warmup: int = 2, total: int = 262144) -> dict:
-    """Ragged causal prefill: 64 sequences, Zipf(1.2) lengths in [1,16384], 32/8 heads, head_dim 128."""
+    """Ragged causal prefill: 64 sequences, Zipf(1.2) lengths in [1,16384], 32/8 heads, head_dim 128,
+    together with the store_kvcache scatter of the same tokens into a block-16 pool through a shuffled
+    slot mapping (seed 2).  One call = scatter + tile list + attention; the attention alone is also timed."""
     lens = c5_prefill_lengths(total=total)
     T, Hq, Hkv, D = int(lens.sum()), 32, 8, 128
     g = torch.Generator(device="cuda").manual_seed(2)
@@ -59,16 +61,29 @@ def prefill(steps: int = 5, warmup: int = 2, total: int = 262144) -> dict:
     mx = int(lens.max())
     rows = ops.prefill_tile_rows(Hq, Hkv, D, D, torch.bfloat16)
 
-    def call():   # the tile list is per-step work (shared by the layers of a model): timed with the attention
+    bs = 16
+    nblk = (T + bs - 1) // bs
+    perm = torch.randperm(nblk, generator=g, device="cuda")
+    slots = (perm.repeat_interleave(bs) * bs + torch.arange(bs, device="cuda").repeat(nblk))[:T].to(torch.int64)
+    kc = torch.zeros(nblk, bs, Hkv, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+
+    def attention():   # the tile list is per-step work (shared by the layers of a model): timed with the attention
         plan = ops.prefill_plan(cu, T, mx, rows)
         ops.prefill_varlen(q, k, v, cu, cu, mx, mx, D ** -0.5, out=out, plan=plan)
 
+    def call():
+        ops.store_kvcache(k, v, kc, vc, slots)
+        attention()
+
+    ms_att = _time(attention, steps, warmup)
     ms = _time(call, steps, warmup)
     ops.check_status()
     flops = prefill_flops(lens, Hq, D, D)
     return dict(workload=f"ragged causal prefill: 64 seqs, Zipf(1.2) lengths in [1,16384], {T} tokens, 32/8 heads, "
                          "head_dim 128, bf16", ms=ms, tokens=T, lengths=sorted(lens.tolist(), reverse=True),
-                flops=flops, tflops=flops / ms / 1e9, launches_per_call=2)
+                flops=flops, tflops=flops / ms / 1e9, attention_only_ms=ms_att, attention_only_tflops=flops / ms_att / 1e9,
+                scatter_bytes=T * (2 * Hkv * D * 2 * 2 + 8), launches_per_call=3)
 
 
 def store(steps: int = 50, warmup: int = 5, tokens: int = 262144) -> dict:
