@@ -200,11 +200,16 @@ class ModelRunner:
         v["context_lens"][:bs].copy_(ctx.context_lens)
         v["block_tables"][:bs, :ctx.block_tables.size(1)].copy_(ctx.block_tables)
         self.graphs[bucket].replay()
-        return self.model.compute_logits(v["outputs"][:bs])
+        return v["logits"][:bs]
 
     def run(self, seqs: list[Sequence], is_prefill: bool) -> list[int]:
         if not is_prefill and self.graphs and not self.enforce_eager and len(seqs) <= max(self.graphs):
             logits = self._replay_decode(seqs)
+            if not any(s.temperature for s in seqs):
+                # all greedy: the argmax was part of the graph; reading it is the step's only sync
+                token_ids = self.graph_vars["greedy"][:len(seqs)].tolist()
+                reset_context()
+                return token_ids
         elif is_prefill and self.prefill_graphs and (logits := self._replay_prefill(seqs)) is not None:
             pass
         else:
@@ -234,7 +239,7 @@ class ModelRunner:
         set_context(False, slot_mapping=v["slot_mapping"][:n], context_lens=v["context_lens"][:n],
                     block_tables=v["block_tables"][:n])
         self.graphs[bucket].replay()
-        return self.model.compute_logits(v["outputs"][:n])
+        return v["logits"][:n]
 
     @torch.inference_mode()
     def run_logits(self, seqs: list[Sequence], is_prefill: bool) -> torch.Tensor:
@@ -357,6 +362,9 @@ class ModelRunner:
         v["slot_mapping"].fill_(-1)
         self.graph_host_np["slot_mapping"][:] = -1
         v["outputs"] = torch.zeros(max_bs, self.model_config.d_model, dtype=self.dtype, device=dev)
+        # the graph also holds the lm_head GEMM and the greedy argmax, so a greedy step launches nothing else
+        v["logits"] = torch.zeros(max_bs, self.model_config.vocab_size, dtype=self.dtype, device=dev)
+        v["greedy"] = torch.zeros(max_bs, dtype=torch.int64, device=dev)
         buckets = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
         if max_bs not in buckets:
             buckets.append(max_bs)
@@ -367,11 +375,14 @@ class ModelRunner:
                         block_tables=v["block_tables"][:b])
             positions = (v["context_lens"][:b] - 1).clamp_min(0)
             v["outputs"][:b] = self.model(v["input_ids"][:b], positions)       # warm-up, allocates workspaces
+            v["logits"][:b] = self.model.compute_logits(v["outputs"][:b])
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool):
                 positions = (v["context_lens"][:b] - 1).clamp_min(0)
                 v["outputs"][:b] = self.model(v["input_ids"][:b], positions)
+                v["logits"][:b] = self.model.compute_logits(v["outputs"][:b])
+                torch.argmax(v["logits"][:b], dim=-1, out=v["greedy"][:b])
             if pool is None:
                 pool = g.pool()
             self.graphs[b] = g
