@@ -41,39 +41,54 @@ struct RouteArgs {
   int32_t* cta_counts;      // [gridDim.x, E] workspace (unused with one CTA)
 };
 
+// 32-bit expert masks up to 32 experts, 64-bit above: the selection loops are all shifts and tests
+template <int EMAX>
+struct MaskOf {
+  using type = uint32_t;
+};
+template <>
+struct MaskOf<64> {
+  using type = unsigned long long;
+};
+__device__ __forceinline__ int lowest_bit(uint32_t m) { return __ffs(static_cast<int>(m)) - 1; }
+__device__ __forceinline__ int lowest_bit(unsigned long long m) { return __ffsll(static_cast<long long>(m)) - 1; }
+
 // bit e set: token t routes to expert e.  EMAX (>= E) is a compile-time bound so that the biased
 // logits live in registers.
 template <typename T, int EMAX>
-__device__ __forceinline__ unsigned long long select_mask(const RouteArgs& a, int t) {
+__device__ __forceinline__ typename MaskOf<EMAX>::type select_mask(const RouteArgs& a, int t) {
+  using M = typename MaskOf<EMAX>::type;
   const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * a.E;
   float biased[EMAX];
 #pragma unroll
   for (int e = 0; e < EMAX; ++e)
-    biased[e] = e < a.E ? round_to<T>(to_float<T>(row[e]) + round_to<T>(a.bias[e])) : 0.f;
-  unsigned long long taken = 0ull;
+    biased[e] = e < a.E ? round_to<T>(to_float<T>(row[e]) + round_to<T>(a.bias[e])) : -INFINITY;
+  M taken = 0;
   for (int k = 0; k < a.K; ++k) {            // k maxima, lower index first among equals
     int best = -1;
     float bv = -INFINITY;
 #pragma unroll
-    for (int e = 0; e < EMAX; ++e)
-      if (e < a.E && !((taken >> e) & 1ull) && (best < 0 || biased[e] > bv)) {
+    for (int e = 0; e < EMAX; ++e) {
+      const bool open = e < a.E && !((taken >> e) & M(1));
+      if (open && (best < 0 || biased[e] > bv)) {
         best = e;
         bv = biased[e];
       }
-    taken |= 1ull << best;
+    }
+    taken |= M(1) << best;
   }
   return taken;
 }
 
 // per-warp counts of every expert into warp_cnt[warp][e]; ranks[n] = number of lower lanes of the warp
 // that also use the n-th (ascending) expert of this thread's token
-__device__ __forceinline__ void warp_counts(unsigned long long taken, int E, int32_t (*warp_cnt)[kMaxE],
-                                            int* ranks) {
+template <typename M>
+__device__ __forceinline__ void warp_counts(M taken, int E, int32_t (*warp_cnt)[kMaxE], int* ranks) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned lt = (1u << lane) - 1u;
   int n = 0;
   for (int e = 0; e < E; ++e) {
-    const bool mine = (taken >> e) & 1ull;
+    const bool mine = (taken >> e) & M(1);
     const unsigned b = __ballot_sync(0xffffffffu, mine);
     if (lane == 0) warp_cnt[warp][e] = __popc(b);
     if (mine && n < kMaxK) ranks[n++] = __popc(b & lt);
@@ -84,7 +99,8 @@ template <typename T, int EMAX>
 __global__ void __launch_bounds__(kTok) moe_count_kernel(const RouteArgs a) {
   __shared__ int32_t warp_cnt[kWarps][kMaxE];
   const int t = blockIdx.x * kTok + threadIdx.x;
-  const unsigned long long taken = t < a.T ? select_mask<T, EMAX>(a, t) : 0ull;
+  using M = typename MaskOf<EMAX>::type;
+  const M taken = t < a.T ? select_mask<T, EMAX>(a, t) : M(0);
   int ranks[kMaxK];
   warp_counts(taken, a.E, warp_cnt, ranks);
   __syncthreads();
@@ -105,7 +121,8 @@ __global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int E = a.E, K = a.K;
   const int t = blockIdx.x * kTok + tid;
-  const unsigned long long taken = t < a.T ? select_mask<T, EMAX>(a, t) : 0ull;
+  using M = typename MaskOf<EMAX>::type;
+  const M taken = t < a.T ? select_mask<T, EMAX>(a, t) : M(0);
   int ranks[kMaxK];
   warp_counts(taken, E, warp_cnt, ranks);
   // routing weights of the selected experts, ascending expert order (before the barrier: independent of it)
@@ -115,13 +132,12 @@ __global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
     const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * E;
     float sum = 0.f;
     int n = 0;
-    for (int e = 0; e < E; ++e)
-      if (((taken >> e) & 1ull) && n < kMaxK) {
-        sel[n] = e;
-        wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
-        sum += wsel[n];
-        ++n;
-      }
+    for (M rest = taken; rest != 0 && n < kMaxK; rest &= rest - 1, ++n) {   // set bits, ascending
+      const int e = lowest_bit(rest);
+      sel[n] = e;
+      wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
+      sum += wsel[n];
+    }
     if (K > 1) {
       const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
       for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
