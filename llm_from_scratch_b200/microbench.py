@@ -190,6 +190,9 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
     eng = built["engine"]
     graphs, timing = bool(eng.model_runner.graphs), dict(eng.timing)
     eng.exit()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if tokens is None:            # not rank 0
         return {}
     gen = sum(len(t) for t in tokens)
