@@ -111,3 +111,77 @@ def prepare_decode(seqs: list[Sequence], block_size: int, tables_out: np.ndarray
         slot_mapping=slots, positions=lens - 1, context_lens=lens,
         block_tables=pad_block_tables(seqs) if tables_out is None else pad_block_tables(seqs, tables_out)[:n],
         last_token_index=np.arange(n, dtype=np.int64))
+
+
+class DecodeBatchBuilder:
+    """Decode-step metadata without a per-sequence rebuild: every sequence owns a row of a host table that
+    mirrors its block table and is only touched when the table changes (a block is appended once in
+    ``block_size`` steps; a prefill rewrites it), so a step costs four passes over the batch in the
+    interpreter plus a few numpy gathers.  ``build`` writes exactly what ``prepare_decode`` returns
+    (input_ids, slot_mapping, context_lens, block_tables) into caller-owned arrays.
+
+    The owner must call ``invalidate`` for every sequence that goes through a prefill (its block table
+    may have been replaced by one of the same length after a preemption)."""
+
+    def __init__(self, block_size: int, max_blocks: int, rows: int = 1024):
+        self.block_size = block_size
+        self.tables = np.zeros((rows, max_blocks), dtype=np.int32)
+        self.row_blocks = np.full(rows, -1, dtype=np.int64)     # valid entries per row, -1 = rebuild
+        self.row_seq: list = [None] * rows
+        self.row_owner = np.zeros(rows, dtype=np.int64)         # id() of the owning sequence, 0 = none
+        self.free = list(range(rows - 1, -1, -1))
+
+    def invalidate(self, seqs) -> None:
+        for s in seqs:
+            if s._row is not None and self.row_seq[s._row] is s:
+                self.row_blocks[s._row] = -1
+
+    def _assign(self, s) -> int:
+        if not self.free:
+            # reclaim rows of sequences that are finished or were handed another row; else grow
+            for r, owner in enumerate(self.row_seq):
+                if owner is not None and (owner.is_finished or owner._row != r):
+                    self.row_seq[r] = None
+                    self.row_owner[r] = 0
+                    self.free.append(r)
+            if not self.free:
+                old = self.tables.shape[0]
+                self.tables = np.concatenate([self.tables, np.zeros_like(self.tables)])
+                self.row_blocks = np.concatenate([self.row_blocks, np.full(old, -1, dtype=np.int64)])
+                self.row_owner = np.concatenate([self.row_owner, np.zeros(old, dtype=np.int64)])
+                self.row_seq.extend([None] * old)
+                self.free = list(range(2 * old - 1, old - 1, -1))
+        r = self.free.pop()
+        self.row_seq[r] = s
+        self.row_owner[r] = id(s)
+        self.row_blocks[r] = -1
+        s._row = r
+        return r
+
+    def build(self, seqs, out_ids: np.ndarray, out_slots: np.ndarray, out_lens: np.ndarray,
+              out_tables: np.ndarray) -> None:
+        n, bs = len(seqs), self.block_size
+        rows_l = [s._row for s in seqs]
+        ids = np.array([id(s) for s in seqs], dtype=np.int64)
+        # a row is this sequence's only if the table says so (rows are reclaimed; a sequence may come
+        # from another builder): one vectorised check, the slow path only for the newcomers
+        if None in rows_l or not np.array_equal(self.row_owner[np.array(rows_l, dtype=np.int64)], ids):
+            row_seq = self.row_seq
+            rows_l = [s._row if s._row is not None and s._row < len(row_seq) and row_seq[s._row] is s
+                      else self._assign(s) for s in seqs]
+        rows = np.array(rows_l, dtype=np.int64)
+        lens = np.array([s.num_tokens for s in seqs], dtype=np.int64)
+        nblk = np.array([len(s.block_table) for s in seqs], dtype=np.int64)
+        have = self.row_blocks[rows]
+        for i in np.nonzero(have != nblk)[0].tolist():
+            r, bt = rows_l[i], seqs[i].block_table
+            k = int(have[i])
+            if k < 0 or k > len(bt):
+                k = 0
+            self.tables[r, k:len(bt)] = bt[k:]
+            self.row_blocks[r] = len(bt)
+        width = int(nblk.max())
+        out_tables[:n, :width] = self.tables[rows, :width]
+        out_ids[:n] = [s.last_token for s in seqs]
+        out_lens[:n] = lens
+        out_slots[:n] = self.tables[rows, nblk - 1].astype(np.int64) * bs + (lens - 1) % bs

@@ -100,6 +100,7 @@ class ModelRunner:
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_vars: dict[str, torch.Tensor] = {}
         self.prefill_graphs: dict[int, tuple] = {}
+        self.decode_builder = None
         c = self.model_config
         if c.attention_type == "MLA":    # prefill runs the expanded form: 192-wide keys, 128-wide values
             self.prefill_tile_rows = ops.prefill_tile_rows(c.num_heads, c.num_heads, c.head_dim + c.rope_dim,
@@ -211,8 +212,10 @@ class ModelRunner:
                 reset_context()
                 return token_ids
         elif is_prefill and self.prefill_graphs and (logits := self._replay_prefill(seqs)) is not None:
-            pass
+            self.decode_builder.invalidate(seqs)
         else:
+            if is_prefill and self.decode_builder is not None:
+                self.decode_builder.invalidate(seqs)
             input_ids = self.prepare_prefill(seqs) if is_prefill else self.prepare_decode(seqs)
             logits = self.run_model(input_ids, is_prefill)
         with torch.inference_mode():
@@ -228,11 +231,8 @@ class ModelRunner:
         n = len(seqs)
         bucket = next(b for b in sorted(self.graphs) if b >= n)
         h, v = self.graph_host_np, self.graph_vars
-        m = md.prepare_decode(seqs, self.block_size, tables_out=h["block_tables"])
-        h["input_ids"][:n] = m.input_ids
-        h["slot_mapping"][:n] = m.slot_mapping
+        self.decode_builder.build(seqs, h["input_ids"], h["slot_mapping"], h["context_lens"], h["block_tables"])
         h["slot_mapping"][n:bucket] = -1
-        h["context_lens"][:n] = m.context_lens
         h["context_lens"][n:bucket] = 0
         nbytes = self.graph_tables_offset + bucket * h["block_tables"].shape[1] * 4
         self.graph_dev[:nbytes].copy_(self.graph_host[:nbytes], non_blocking=True)
@@ -361,6 +361,7 @@ class ModelRunner:
             self.graph_host_np[name] = host_bytes[offsets[name]:offsets[name] + nbytes].view(npdt).reshape(shape)
         v["slot_mapping"].fill_(-1)
         self.graph_host_np["slot_mapping"][:] = -1
+        self.decode_builder = md.DecodeBatchBuilder(self.block_size, max_blocks, rows=4 * max_bs)
         v["outputs"] = torch.zeros(max_bs, self.model_config.d_model, dtype=self.dtype, device=dev)
         # the graph also holds the lm_head GEMM and the greedy argmax, so a greedy step launches nothing else
         v["logits"] = torch.zeros(max_bs, self.model_config.vocab_size, dtype=self.dtype, device=dev)

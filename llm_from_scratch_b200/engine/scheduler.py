@@ -13,6 +13,7 @@ The stop rule is the reference's in both modes.
 """
 from __future__ import annotations
 
+import itertools
 from collections import deque
 
 from .block_manager import BlockManager
@@ -58,9 +59,26 @@ class Scheduler:
         return batch
 
     def _grow_running(self) -> list[Sequence]:
-        bm, batch = self.block_manager, []
+        bm = self.block_manager
         block_size = bm.block_size
         limit = min(self.max_num_sequences, self.max_num_batched_tokens)
+        if not self.reference_exact:
+            # Common case, no queue surgery: the first `limit` running sequences decode, those at a
+            # block boundary get their block opened (n % bs == 1) or sealed (== 0) in order, and
+            # nobody has to be preempted because the free list covers every block to be opened.
+            # Exactly what the general loop below does in that case.
+            batch = list(itertools.islice(self.running, limit))
+            edge = [s for s in batch if s.num_tokens % block_size <= 1]
+            opening = sum(1 for s in edge if s.num_tokens % block_size == 1)
+            if opening <= bm.num_free_blocks:
+                for s in edge:
+                    bm.append(s)
+                return batch
+        return self._grow_running_general(limit)
+
+    def _grow_running_general(self, limit: int) -> list[Sequence]:
+        bm, batch = self.block_manager, []
+        block_size = bm.block_size
         while self.running:
             seq = self.running.popleft()
             if self.reference_exact:
@@ -108,11 +126,15 @@ class Scheduler:
 
     # ------------------------------------------------------------------ after the model ran
     def postprocess(self, seqs: list[Sequence], token_ids: list[int]) -> None:
+        eos = self.eos
         for seq, token_id in zip(seqs, token_ids):
-            seq.append_token(token_id)
-            hit_eos = token_id == self.eos and not seq.ignore_eos
-            hit_max_tokens = 1 + seq.num_completion_tokens >= seq.max_tokens
-            hit_max_length = seq.max_model_length is not None and seq.num_tokens >= seq.max_model_length
+            # Sequence.append_token, inlined (this loop runs once per generated token)
+            seq.token_ids.append(token_id)
+            seq.last_token = token_id
+            n = seq.num_tokens = seq.num_tokens + 1
+            hit_eos = token_id == eos and not seq.ignore_eos
+            hit_max_tokens = 1 + n - seq.num_prompt_tokens >= seq.max_tokens
+            hit_max_length = seq.max_model_length is not None and n >= seq.max_model_length
             if hit_eos or hit_max_tokens or hit_max_length:
                 seq.status = SequenceStatus.FINISHED
                 self.block_manager.deallocate(seq)

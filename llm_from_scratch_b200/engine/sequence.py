@@ -32,7 +32,7 @@ class Sequence:
 
     __slots__ = ("seq_id", "status", "token_ids", "last_token", "num_tokens", "num_prompt_tokens",
                  "num_cached_tokens", "block_table", "temperature", "max_tokens", "ignore_eos",
-                 "max_model_length", "_bt_cache")
+                 "max_model_length", "_bt_cache", "_row")
 
     def __init__(self, token_ids, sampling_params: SamplingParams | None = None):
         sp = sampling_params if sampling_params is not None else SamplingParams()
@@ -44,6 +44,7 @@ class Sequence:
         self.num_cached_tokens = 0
         self.block_table: list[int] = []
         self._bt_cache = None     # [list object, int32 buffer, entries valid]: see metadata.block_table_array
+        self._row = None          # row of this sequence in a metadata.DecodeBatchBuilder table
         self.temperature = sp.temperature
         self.max_tokens = sp.max_tokens
         self.ignore_eos = sp.ignore_eos
@@ -109,5 +110,6 @@ class Sequence:
     def __setstate__(self, state):
         self.num_tokens, self.num_prompt_tokens, self.num_cached_tokens, self.block_table, payload = state
         self._bt_cache = None
+        self._row = None
         self.token_ids = payload if self.num_tokens == self.num_prompt_tokens else [payload]
         self.last_token = self.token_ids[-1] if self.token_ids else None

@@ -1,0 +1,99 @@
+"""The interpreter-level fast paths of the host layer give exactly what the plain code gives:
+scheduler decode rounds without queue surgery, and decode metadata from per-sequence table rows."""
+import itertools
+import random
+
+import numpy as np
+import pytest
+
+from llm_from_scratch_b200.engine import SamplingParams, Sequence, metadata as md
+from llm_from_scratch_b200.engine.llm_engine import LLMEngine
+from llm_from_scratch_b200.engine.scheduler import Scheduler
+
+
+class _Runner:
+    """Stands in for the GPU: samples pseudo-random tokens, records what it was asked to run."""
+
+    def __init__(self, blocks, block_size, check_builder=False):
+        self.num_kv_blocks, self.block_size = blocks, block_size
+        self.rng = random.Random(7)
+        self.log = []
+        self.builder = md.DecodeBatchBuilder(block_size, 64, rows=8) if check_builder else None
+
+    def run(self, seqs, is_prefill):
+        self.log.append((is_prefill, [s.seq_id for s in seqs], [list(s.block_table) for s in seqs]))
+        if self.builder is not None:
+            if is_prefill:
+                self.builder.invalidate(seqs)
+            else:
+                want = md.prepare_decode(seqs, self.block_size)
+                n = len(seqs)
+                ids, slots, lens = (np.full(n + 3, -7, dtype=np.int64) for _ in range(3))
+                tables = np.full((n + 3, 64), -7, dtype=np.int32)
+                self.builder.build(seqs, ids, slots, lens, tables)
+                assert np.array_equal(ids[:n], want.input_ids) and np.array_equal(slots[:n], want.slot_mapping)
+                assert np.array_equal(lens[:n], want.context_lens)
+                for i, s in enumerate(seqs):      # entries past a sequence's table are not part of the contract
+                    k = len(s.block_table)
+                    assert np.array_equal(tables[i, :k], want.block_tables[i, :k])
+                assert (ids[n:] == -7).all() and (tables[n:] == -7).all()
+        return [self.rng.randrange(50) for _ in seqs]
+
+    def exit(self):
+        pass
+
+
+def _serve(blocks, general_only=False, check_builder=False, n_req=40, seed=3):
+    Sequence.counter = itertools.count()
+    rng = random.Random(seed)
+    runner = _Runner(blocks, 4, check_builder)
+    eng = LLMEngine(dict(block_size=4, max_num_sequences=6, max_num_batched_tokens=64, eos=-1), runner=runner)
+    if general_only:
+        sched = eng.scheduler
+        limit = min(sched.max_num_sequences, sched.max_num_batched_tokens)
+        sched._grow_running = lambda: Scheduler._grow_running_general(sched, limit)
+    pending = [[rng.randrange(50) for _ in range(rng.randrange(1, 30))] for _ in range(n_req)]
+    outs = {}
+    while pending or not eng.is_finished():
+        for _ in range(rng.randrange(0, 3)):          # requests trickle in while others decode
+            if pending:
+                eng.add_request(pending.pop(), SamplingParams(temperature=0.0, max_tokens=rng.randrange(2, 25),
+                                                              ignore_eos=True))
+        done, _n, _p = eng.step()
+        outs.update(done)
+    return runner.log, outs
+
+
+@pytest.mark.parametrize("blocks", [400, 24, 14])      # ample pool, and pools small enough to preempt
+def test_decode_round_fast_path_equals_the_general_loop(blocks):
+    fast_log, fast_out = _serve(blocks)
+    slow_log, slow_out = _serve(blocks, general_only=True)
+    assert fast_log == slow_log and fast_out == slow_out
+    assert any(not p for p, _, _ in fast_log) and any(p for p, _, _ in fast_log)
+
+
+@pytest.mark.parametrize("blocks", [400, 14])
+def test_decode_batch_builder_equals_prepare_decode(blocks):
+    """Rows are reused (8 rows at first, 6 running sequences, 40 requests), tables grow, and with the
+    small pool sequences are preempted and prefilled again into different blocks."""
+    log, _ = _serve(blocks, check_builder=True)
+    assert sum(1 for p, _, _ in log if not p) > 20
+
+
+def test_decode_batch_builder_rejects_rows_of_another_builder():
+    Sequence.block_size = 4
+    a, b = md.DecodeBatchBuilder(4, 8, rows=4), md.DecodeBatchBuilder(4, 8, rows=4)
+    seqs = []
+    for i in range(3):
+        s = Sequence(list(range(5 + i)), SamplingParams())
+        s.block_table = [10 * i, 10 * i + 1]
+        seqs.append(s)
+    outs = lambda: (np.zeros(3, np.int64), np.zeros(3, np.int64), np.zeros(3, np.int64), np.zeros((3, 8), np.int32))
+    oa, ob = outs(), outs()
+    a.build(seqs, *oa)
+    b.build(list(reversed(seqs)), *ob)             # same sequences, rows assigned in another order
+    want = md.prepare_decode(list(reversed(seqs)), 4)
+    assert np.array_equal(ob[1], want.slot_mapping) and np.array_equal(ob[3][:, :2], want.block_tables)
+    a.build(seqs, *oa)                              # a's rows are no longer the sequences' rows: reassigned
+    want = md.prepare_decode(seqs, 4)
+    assert np.array_equal(oa[1], want.slot_mapping) and np.array_equal(oa[3][:, :2], want.block_tables)
