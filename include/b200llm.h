@@ -69,6 +69,10 @@ int b200_read_status(int32_t* status, int32_t* status_host, void* stream);
 uint64_t b200_xxh64(const void* data_host, size_t len, uint64_t seed);
 uint64_t b200_block_hash(const int32_t* token_ids_host, int32_t num_tokens, uint64_t prefix_hash,
                          int32_t has_prefix);
+/* The whole chain at once: out_hashes[i] for every full block i of the token list (prefix of block 0:
+ * none, of block i: out_hashes[i-1]).  Returns the number of full blocks, or -1 on a bad argument. */
+int64_t b200_block_hash_chain(const int32_t* token_ids_host, int64_t num_tokens, int32_t block_size,
+                              uint64_t* out_hashes);
 
 /* ---------------------------------------------------------------------------------------------
  * store_kvcache: k_cache[slot_mapping[t], :, :] = k[t, :, :] (same for v); slot < 0 is skipped.

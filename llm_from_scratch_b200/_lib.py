@@ -24,6 +24,7 @@ SIGNATURES = {
     "b200_read_status": (_i32, [_vp, _vp, _vp]),
     "b200_xxh64": (_u64, [_vp, _sz, _u64]),
     "b200_block_hash": (_u64, [_vp, _i32, _u64, _i32]),
+    "b200_block_hash_chain": (_i64, [_vp, _i64, _i32, _vp]),
     "b200_store_kvcache": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i64,
                                   _i32, _vp, _vp]),
     "b200_paged_decode_gqa_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),

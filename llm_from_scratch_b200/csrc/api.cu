@@ -174,4 +174,22 @@ uint64_t b200_block_hash(const int32_t* token_ids_host, int32_t num_tokens, uint
   return h.digest();
 }
 
+// Chained hashes of every full block of a token list: out[i] = XXH64([out[i-1] if i > 0] || ids of block i),
+// the values BlockManager.allocate computes block by block (engine/block_manager.py:85-101).
+int64_t b200_block_hash_chain(const int32_t* token_ids_host, int64_t num_tokens, int32_t block_size,
+                              uint64_t* out_hashes) {
+  if (num_tokens < 0 || block_size <= 0 || (num_tokens > 0 && !token_ids_host)) return -1;
+  const int64_t full = num_tokens / block_size;
+  if (full > 0 && !out_hashes) return -1;
+  uint64_t prev = 0;
+  for (int64_t i = 0; i < full; ++i) {
+    b200::Xxh64 h(0);
+    if (i > 0) h.update(&prev, 8);
+    h.update(token_ids_host + i * block_size, static_cast<size_t>(block_size) * 4);
+    prev = h.digest();
+    out_hashes[i] = prev;
+  }
+  return full;
+}
+
 }  // extern "C"

@@ -118,9 +118,14 @@ class BlockManager:
         token ids match (block_manager.py:85-114)."""
         h = -1
         bs = self.block_size
+        # default mode: all full-block hashes of the prompt in one native call (same chain of values)
+        chain = None if self.reference_exact else ops.block_hash_chain(seq.token_ids, bs)
         for i in range(seq.num_blocks):
             token_ids = seq.block(i)
-            h = self.compute_hash(token_ids, h) if len(token_ids) == bs else -1
+            if chain is not None:
+                h = chain[i] if len(token_ids) == bs else -1
+            else:
+                h = self.compute_hash(token_ids, h) if len(token_ids) == bs else -1
             block_id = self.hash_to_block_id.get(h, -1)
             hit = block_id != -1 and self.blocks[block_id].token_ids == token_ids
             if hit:

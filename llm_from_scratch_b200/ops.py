@@ -429,3 +429,15 @@ def block_hash(token_ids, prefix: int = -1) -> int:
     buf = array.array("i", token_ids)
     addr, n = buf.buffer_info()
     return int(lib.b200_block_hash(addr, n, 0 if prefix == -1 else prefix, 0 if prefix == -1 else 1))
+
+
+def block_hash_chain(token_ids, block_size: int) -> list[int]:
+    """Chained XXH64 hashes of every full block of ``token_ids`` in one native call: element i is what
+    ``block_hash(block i, prefix = element i-1)`` returns."""
+    buf = array.array("i", token_ids)
+    addr, n = buf.buffer_info()
+    out = array.array("Q", bytes(8 * (n // block_size)))
+    got = int(lib.b200_block_hash_chain(addr, n, block_size, out.buffer_info()[0]))
+    if got != len(out):
+        raise RuntimeError("b200_block_hash_chain failed")
+    return out.tolist()

@@ -97,3 +97,15 @@ def test_decode_batch_builder_rejects_rows_of_another_builder():
     a.build(seqs, *oa)                              # a's rows are no longer the sequences' rows: reassigned
     want = md.prepare_decode(seqs, 4)
     assert np.array_equal(oa[1], want.slot_mapping) and np.array_equal(oa[3][:, :2], want.block_tables)
+
+
+def test_block_hash_chain_equals_block_by_block_hashing():
+    from llm_from_scratch_b200 import ops
+    rng = random.Random(1)
+    for n in (0, 1, 15, 16, 17, 100, 160):
+        ids = [rng.randrange(32000) for _ in range(n)]
+        h, want = -1, []
+        for i in range(n // 16):
+            h = ops.block_hash(ids[i * 16:(i + 1) * 16], h)
+            want.append(h)
+        assert ops.block_hash_chain(ids, 16) == want
