@@ -287,6 +287,19 @@ int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* 
                           int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype, int32_t* status,
                           void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Token sampling (Sampler.forward, utils/sampler.py:35-52; greedy argmax of generate.py:62), one launch.
+ *   logits [num_rows, >= vocab_size] (row stride in elements) in `dtype`; temperatures fp32 [num_rows] or
+ *   NULL (= all greedy).  Row r with temperature T > 0: a draw from softmax(logits[r] / T) as the
+ *   exponential race argmax_i (logits_i / T - log E_i), E_i ~ Exp(1) clamped at 1e-10 like the reference;
+ *   T <= 0: argmax of the logits, lowest index among equal maxima.  out_tokens int64 [num_rows].
+ *   The uniforms are a counter-based function of (seed, offset, row, element): pass a fresh `offset` per
+ *   step.  The stream differs from torch's, so only the distribution matches the reference.
+ * ------------------------------------------------------------------------------------------- */
+int b200_sample(const void* logits, int64_t row_stride, const float* temperatures, int64_t num_rows,
+                int32_t vocab_size, uint64_t seed, uint64_t offset, int64_t* out_tokens, int32_t dtype,
+                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -441,3 +441,24 @@ def block_hash_chain(token_ids, block_size: int) -> list[int]:
     if got != len(out):
         raise RuntimeError("b200_block_hash_chain failed")
     return out.tolist()
+
+
+def sample(logits: torch.Tensor, temperatures: torch.Tensor | None, seed: int, offset: int,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of ``logits`` [B, V]: greedy where the temperature is <= 0 (or ``temperatures`` is
+    None), else a draw from softmax(logits / T).  ``seed`` / ``offset`` select the random stream."""
+    _cuda(logits, temperatures, out)
+    B, V = logits.shape
+    if logits.stride(1) != 1:
+        raise ValueError("logits rows must be contiguous")
+    if temperatures is not None and (temperatures.dtype != torch.float32 or temperatures.numel() != B
+                                     or not temperatures.is_contiguous()):
+        raise ValueError("temperatures must be contiguous float32 [B]")
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    elif out.dtype != torch.int64 or out.numel() != B or not out.is_contiguous():
+        raise ValueError("out must be contiguous int64 [B]")
+    check(lib.b200_sample(logits.data_ptr(), logits.stride(0), temperatures.data_ptr() if temperatures is not None
+                          else None, B, V, seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, out.data_ptr(),
+                          _dt(logits), _stream()), "sample")
+    return out

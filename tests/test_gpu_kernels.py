@@ -678,3 +678,42 @@ def test_empty_inputs_are_no_ops():
     out = ops.paged_decode_gqa(q, kc, vc, bt, torch.zeros(3, dtype=torch.int64, device=dev), 0.125)
     ops.check_status()
     assert (out == 0).all()
+
+
+# ----------------------------------------------------------------------------- sampler
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sample_greedy_is_argmax_with_first_maximum(dtype):
+    ops = _ops()
+    logits = _randn((37, 1000), 91, dtype).cuda()
+    logits[3, 10] = logits[3, 700] = 50.0            # a tie: the lower index wins
+    logits[5] = 0.0                                   # a whole row of equal values
+    got = ops.sample(logits, None, seed=1, offset=1)
+    assert torch.equal(got, logits.float().argmax(dim=-1)) and got[3].item() == 10 and got[5].item() == 0
+    temps = torch.zeros(37, device="cuda")
+    assert torch.equal(ops.sample(logits, temps, seed=1, offset=2), got)      # T = 0 rows are greedy too
+    wide = torch.full((4, 1500), -1.0, dtype=dtype, device="cuda")            # rows with a stride
+    view = wide[:, :1000]
+    view[:, 123] = 2.0
+    assert ops.sample(view, None, 0, 0).tolist() == [123] * 4
+
+
+def test_sample_with_temperature_follows_the_softmax_distribution():
+    """20,000 rows with the same 8 logits: the draw frequencies match softmax(logits / T) within four
+    standard deviations (the reference's exponential race, utils/sampler.py:48-51, has that law); the
+    stream is a function of (seed, offset) only."""
+    ops = _ops()
+    n, T = 20000, 0.7
+    base = torch.tensor([2.0, 1.0, 0.5, 0.0, -0.5, -1.0, 3.0, -4.0])
+    logits = base.repeat(n, 1).cuda()
+    temps = torch.full((n,), T, device="cuda")
+    got = ops.sample(logits, temps, seed=123, offset=7)
+    freq = torch.bincount(got.cpu(), minlength=8).double() / n
+    p = torch.softmax(base.double() / T, dim=0)
+    sigma = (p * (1 - p) / n).sqrt()
+    assert ((freq - p).abs() <= 4 * sigma + 1e-4).all(), (freq, p)
+    assert torch.equal(got, ops.sample(logits, temps, seed=123, offset=7))
+    assert not torch.equal(got, ops.sample(logits, temps, seed=123, offset=8))
+    mixed = temps.clone()
+    mixed[::2] = 0.0                                                          # greedy and sampled rows together
+    out = ops.sample(logits, mixed, seed=5, offset=1)
+    assert (out[::2] == 6).all() and (out[1::2] != 6).any()
