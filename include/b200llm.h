@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 4
+#define B200_ABI_VERSION 5
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -240,6 +240,8 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const flo
  *   sorted_token / sorted_expert int32 [num_tokens*top_k], sorted_weight `dtype` [num_tokens*top_k],
  *   expert_offsets int32 [num_experts] (exclusive end of every expert's rows),
  *   slot_to_row int32 [num_tokens, top_k]: row of token t's j-th expert in ascending expert order.
+ * identity_tail != 0: sorted_token has num_tokens*top_k + num_tokens entries and the last num_tokens are
+ *   0, 1, 2, ...: one gather then also yields the rows of a shared expert (see b200_moe_grouped_gemm).
  * One launch for num_tokens <= 256, two (count, scatter) above; `workspace` of
  * b200_moe_route_workspace_bytes() bytes (0 for num_tokens <= 256) holds the per-CTA counts.
  * Limits: num_experts <= 64, top_k <= 8, num_tokens <= 65536 (else B200_ERR_UNSUPPORTED).
@@ -247,8 +249,9 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const flo
 size_t b200_moe_route_workspace_bytes(int32_t num_tokens, int32_t num_experts);
 int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t num_tokens,
                    int32_t num_experts, int32_t top_k, int32_t* sorted_token, int32_t* sorted_expert,
-                   void* sorted_weight, int32_t* expert_offsets, int32_t* slot_to_row, void* workspace,
-                   size_t workspace_bytes, int32_t dtype, void* stream);
+                   void* sorted_weight, int32_t* expert_offsets, int32_t* slot_to_row,
+                   int32_t identity_tail, void* workspace, size_t workspace_bytes, int32_t dtype,
+                   void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * SwiGLU of fused up-projection rows (model/architecture/mlp.py:61-67: w2(silu(w1 x) * w3 x)):
@@ -279,13 +282,16 @@ int b200_moe_combine(const void* expert_out, const void* bias, const int32_t* ro
  *   mode 1: out [num_rows, n_out] = silu(x . W1_e^T + b1) * (x . W3_e^T + b3), n_out = d_ff,
  *           w [experts, 2*d_ff, k_dim] = rows of w1 then rows of w3, bias [experts, 2*d_ff] or NULL
  *           (mlp.py:61-67); GEMM result, bias add, silu and product are each rounded to bf16.
+ * dense_rows > 0: the last dense_rows of the num_rows rows are not grouped: they all use weight set
+ *   number num_experts (w and bias then hold num_experts + 1 sets) — a shared expert applied to every token
+ *   (moe.py:272-273) computed by the same launch, in chunks that cost a CTA what an expert's rows cost.
  * Requires k_dim % 8 == 0 and 16-byte aligned x, w (B200_ERR_ALIGN).  A wait that runs out inside
  * the kernel sets *status to B200_ERR_TIMEOUT.
  * ------------------------------------------------------------------------------------------- */
 int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* out,
                           const int32_t* expert_offsets, int64_t num_rows, int32_t num_experts,
-                          int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype, int32_t* status,
-                          void* stream);
+                          int32_t dense_rows, int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype,
+                          int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Token sampling (Sampler.forward, utils/sampler.py:35-52; greedy argmax of generate.py:62), one launch.

@@ -43,6 +43,8 @@ struct GemmArgs {
   __nv_bfloat16* out;       // [R, n_out]
   const __nv_bfloat16* bias;  // mode 0: [E, n_out]; mode 1: [E, 2*n_out]; or null
   int32_t* status;
+  int num_experts;          // routed experts; groups past them are chunks of the dense tail
+  int dense_rows;           // rows after the grouped ones that all use weight set `num_experts`
 };
 
 template <int NPASS, int STAGES>
@@ -89,13 +91,23 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
   constexpr int FULL = 0, EMPTY = STAGES, ACC_FULL = 2 * STAGES, ACC_EMPTY = 2 * STAGES + 1;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int e = blockIdx.y, tile = blockIdx.x;
+  const int tile = blockIdx.x;
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tm_w)) : "memory");
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tm_x)) : "memory");
   }
-  const int row0 = e ? a.offsets[e - 1] : 0;
-  const int rows = a.offsets[e] - row0;
+  int e = blockIdx.y, row0, rows;
+  if (e < a.num_experts) {
+    row0 = e ? a.offsets[e - 1] : 0;
+    rows = a.offsets[e] - row0;
+  } else {
+    // dense tail (a shared expert applied to every token): chunk (e - num_experts) of NPASS rows after the
+    // grouped rows, weight set num_experts; one pass per CTA, so these CTAs cost what the others cost
+    const int chunk = e - a.num_experts;
+    row0 = a.offsets[a.num_experts - 1] + chunk * NPASS;
+    rows = min(NPASS, a.dense_rows - chunk * NPASS);
+    e = a.num_experts;
+  }
   if (rows <= 0) return;                                   // uniform, before any barrier / allocation
   const int npass = (rows + NPASS - 1) / NPASS;
   const int num_k = (a.k_dim + BK - 1) / BK;               // a ragged K tail is zero-filled by TMA
@@ -347,17 +359,19 @@ int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3
 
 extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* out,
                                      const int32_t* expert_offsets, int64_t num_rows, int32_t num_experts,
-                                     int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype,
-                                     int32_t* status, void* stream) {
+                                     int32_t dense_rows, int32_t n_out, int32_t k_dim, int32_t mode,
+                                     int32_t dtype, int32_t* status, void* stream) {
   using namespace b200;
-  if (num_rows < 0 || num_experts <= 0 || n_out <= 0 || k_dim <= 0 || (mode != 0 && mode != 1))
+  if (num_rows < 0 || num_experts <= 0 || n_out <= 0 || k_dim <= 0 || (mode != 0 && mode != 1) ||
+      dense_rows < 0 || dense_rows > num_rows)
     return B200_ERR_ARG;
   if (dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
   if (num_rows == 0) return B200_OK;
   if (!x || !w || !out || !expert_offsets) return B200_ERR_ARG;
   if (k_dim % 8 != 0 || !aligned16(x) || !aligned16(w)) return B200_ERR_ALIGN;   // TMA: 16-byte rows
   if (num_experts > 65535 || num_rows > 2147483647) return B200_ERR_TOO_LARGE;
-  const int64_t w_rows = static_cast<int64_t>(num_experts) * (mode == 1 ? 2 : 1) * n_out;
+  const int64_t w_sets = num_experts + (dense_rows > 0 ? 1 : 0);
+  const int64_t w_rows = w_sets * (mode == 1 ? 2 : 1) * n_out;
   if (w_rows > 2147483647) return B200_ERR_TOO_LARGE;
   CUtensorMap tw, tx;
   if (!make_map(&tw, w, w_rows, k_dim, mode == 1 ? 64 : BM) || !make_map(&tx, x, num_rows, k_dim, XBOX))
@@ -370,10 +384,16 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* b
   a.out = static_cast<__nv_bfloat16*>(out);
   a.bias = static_cast<const __nv_bfloat16*>(bias);
   a.status = status;
+  a.num_experts = num_experts;
+  a.dense_rows = dense_rows;
   const int tiles = mode == 1 ? (n_out + 63) / 64 : (n_out + BM - 1) / BM;
-  const dim3 grid(tiles, num_experts);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // few rows per expert: deep ring of small stages, two CTAs per SM; otherwise 256 rows per pass
-  if (num_rows <= 64LL * num_experts) return launch<64, 4>(a, tw, tx, grid, s);
+  const int64_t grouped = num_rows - dense_rows;
+  if (grouped <= 64LL * num_experts) {
+    const dim3 grid(tiles, num_experts + (dense_rows + 63) / 64);
+    return launch<64, 4>(a, tw, tx, grid, s);
+  }
+  const dim3 grid(tiles, num_experts + (dense_rows + 255) / 256);
   return launch<256, 4>(a, tw, tx, grid, s);
 }

@@ -39,6 +39,7 @@ struct RouteArgs {
   int32_t* offsets;         // [E]    end (exclusive) of each expert's rows
   int32_t* slot_to_row;     // [T, K] sorted-row index of token t's j-th expert in ascending expert order
   int32_t* cta_counts;      // [gridDim.x, E] workspace (unused with one CTA)
+  int identity_tail;        // also write sorted_token[T*K + t] = t (rows of a shared expert after the grouped ones)
 };
 
 // 32-bit expert masks up to 32 experts, 64-bit above: the selection loops are all shifts and tests
@@ -187,6 +188,7 @@ __global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
   }
   __syncthreads();
   if (t >= a.T) return;
+  if (a.identity_tail) a.sorted_token[a.T * K + t] = t;
   T* wout = static_cast<T*>(a.sorted_weight);
   for (int k = 0; k < K; ++k) {
     const int e = sel[k];
@@ -333,8 +335,8 @@ extern "C" size_t b200_moe_route_workspace_bytes(int32_t num_tokens, int32_t num
 extern "C" int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t num_tokens,
                               int32_t num_experts, int32_t top_k, int32_t* sorted_token,
                               int32_t* sorted_expert, void* sorted_weight, int32_t* expert_offsets,
-                              int32_t* slot_to_row, void* workspace, size_t workspace_bytes, int32_t dtype,
-                              void* stream) {
+                              int32_t* slot_to_row, int32_t identity_tail, void* workspace,
+                              size_t workspace_bytes, int32_t dtype, void* stream) {
   using namespace b200;
   if (num_tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts) return B200_ERR_ARG;
   if (dtype != B200_DTYPE_F32 && dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
@@ -358,6 +360,7 @@ extern "C" int b200_moe_route(const void* gate_logits, const float* expert_bias,
   a.offsets = expert_offsets;
   a.slot_to_row = slot_to_row;
   a.cta_counts = static_cast<int32_t*>(workspace);
+  a.identity_tail = identity_tail != 0;
   const int grid = num_tokens == 0 ? 1 : (num_tokens + kTok - 1) / kTok;   // 0 tokens: offsets = 0
 #define ROUTE_LAUNCH(T, EMAX)                                                       \
   do {                                                                              \

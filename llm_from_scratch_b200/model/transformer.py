@@ -133,6 +133,14 @@ class MoE(nn.Module):
             m.w13, m.b13, m.w2, m.b2 = self.w13[e], self.b13[e], self.w2[e], self.b2[e]
         self.d_ff = self.w2.shape[2]
         self.shared = MLP(p, prefix + ".shared_expert") if cfg.n_shared_experts > 0 else None
+        if self.shared is not None and p.dtype == torch.bfloat16:
+            # routed experts + the shared one as weight set E: one grouped launch covers both at decode sizes
+            self.w13_all = torch.cat([self.w13, self.shared.w13.unsqueeze(0)]).contiguous()
+            self.b13_all = torch.cat([self.b13, self.shared.b13.unsqueeze(0)]).contiguous()
+            self.w2_all = torch.cat([self.w2, self.shared.w2.unsqueeze(0)]).contiguous()
+            self.b2_all = torch.cat([self.b2, self.shared.b2.unsqueeze(0)]).contiguous()
+        else:
+            self.w13_all = None
 
     def route(self, x):
         logits = x @ self.gate_w.t()
@@ -183,9 +191,22 @@ class MoE(nn.Module):
         (decode) are bound by streaming the expert weights and use the tcgen05 grouped GEMM of this
         package (SwiGLU in its epilogue); large prefill batches are compute-bound and go to the
         library grouped GEMM."""
+        T = x.shape[0]
+        small = (T * self.K <= self.own_gemm_max_rows_per_expert * self.E and x.shape[1] % 8 == 0
+                 and self.d_ff % 8 == 0)
+        if small and self.w13_all is not None:
+            # decode sizes with a shared expert: its rows (every token) ride in the same two launches as
+            # the routed rows, as one more weight set; biases are added in the GEMM epilogues
+            tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K,
+                                                       identity_tail=True)
+            xs = x.index_select(0, tok)                              # [T*K routed rows | T shared rows]
+            act = ops.moe_grouped_gemm(xs, self.w13_all, offs, self.b13_all, swiglu=True, dense_rows=T)
+            y = ops.moe_grouped_gemm(act, self.w2_all, offs, self.b2_all, dense_rows=T)
+            R = T * self.K
+            return ops.moe_combine(y[:R], None, experts, w, inv, y[R:])
         tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K)
         xs = x.index_select(0, tok)
-        if xs.shape[0] <= self.own_gemm_max_rows_per_expert * self.E and xs.shape[1] % 8 == 0 and self.d_ff % 8 == 0:
+        if small:
             act = ops.moe_grouped_gemm(xs, self.w13, offs, self.b13, swiglu=True)
             y = ops.moe_grouped_gemm(act, self.w2, offs)
         else:

@@ -337,15 +337,16 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torc
 MOE_ROUTE_MAX_EXPERTS, MOE_ROUTE_MAX_TOPK, MOE_ROUTE_MAX_TOKENS = 64, 8, 65536
 
 
-def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int):
+def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int, identity_tail: bool = False):
     """Top-k routing + grouping by expert.  Returns (sorted_token, sorted_expert, sorted_weight,
-    expert_offsets, slot_to_row); see ``b200_moe_route`` in the header for the layout."""
+    expert_offsets, slot_to_row); see ``b200_moe_route`` in the header for the layout.  With
+    ``identity_tail`` sorted_token has T more entries 0..T-1 at its end (rows of a shared expert)."""
     _cuda(gate_logits, expert_bias)
     T, E = gate_logits.shape
     if not gate_logits.is_contiguous() or expert_bias.dtype != torch.float32 or expert_bias.numel() != E:
         raise ValueError("gate_logits must be contiguous [T, E] and expert_bias fp32 [E]")
     dev, n = gate_logits.device, T * top_k
-    tok = torch.empty(n, dtype=torch.int32, device=dev)
+    tok = torch.empty(n + (T if identity_tail else 0), dtype=torch.int32, device=dev)
     exp = torch.empty(n, dtype=torch.int32, device=dev)
     w = torch.empty(n, dtype=gate_logits.dtype, device=dev)
     offs = torch.empty(E, dtype=torch.int32, device=dev)
@@ -353,7 +354,7 @@ def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int):
     need = int(lib.b200_moe_route_workspace_bytes(T, E))
     ws = workspace(dev, need, "moe_route") if need else None
     check(lib.b200_moe_route(gate_logits.data_ptr(), expert_bias.data_ptr(), T, E, top_k, tok.data_ptr(),
-                             exp.data_ptr(), w.data_ptr(), offs.data_ptr(), inv.data_ptr(),
+                             exp.data_ptr(), w.data_ptr(), offs.data_ptr(), inv.data_ptr(), 1 if identity_tail else 0,
                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                              _dt(gate_logits), _stream()), "moe_route")
     return tok, exp, w, offs, inv
@@ -378,23 +379,31 @@ def swiglu(h: torch.Tensor, bias: torch.Tensor | None = None, row_expert: torch.
 
 
 def moe_grouped_gemm(x: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
-                     bias: torch.Tensor | None = None, swiglu: bool = False) -> torch.Tensor:
+                     bias: torch.Tensor | None = None, swiglu: bool = False, dense_rows: int = 0) -> torch.Tensor:
     """Rows of x [R, k] grouped by expert (expert_offsets int32 [E], exclusive ends) times the expert's
     weight: w [E, n, k] -> [R, n]; with ``swiglu`` w is [E, 2*d_ff, k] = [w1 | w3], bias [E, 2*d_ff],
-    and the result is silu(x w1^T + b1) * (x w3^T + b3) [R, d_ff].  bf16, tcgen05 tensor cores."""
+    and the result is silu(x w1^T + b1) * (x w3^T + b3) [R, d_ff].  bf16, tcgen05 tensor cores.
+    ``dense_rows`` > 0: the last rows of x are not grouped and all use one more weight set, w[E] (w and
+    bias then have E + 1 sets): a shared expert in the same launch."""
     _cuda(x, w, expert_offsets, bias)
     R, k = x.shape
     E, n, k2 = w.shape
+    if dense_rows:
+        E -= 1
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous():
         raise ValueError("x and w must be contiguous bfloat16")
     if k2 != k or expert_offsets.dtype != torch.int32 or expert_offsets.numel() != E or (swiglu and n % 2):
         raise ValueError("w must be [E, n, k] with k = x.shape[1]; expert_offsets int32 [E]")
     n_out = n // 2 if swiglu else n
-    if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous() or tuple(bias.shape) != (E, n)):
-        raise ValueError("bias must be contiguous bfloat16 [E, n]")
+    if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous()
+                             or tuple(bias.shape) != (w.shape[0], n)):
+        raise ValueError("bias must be contiguous bfloat16 [weight sets, n]")
+    if dense_rows < 0 or dense_rows > R or E < 1:
+        raise ValueError("dense_rows must be within the rows of x and leave at least one routed expert")
     out = torch.empty(R, n_out, dtype=torch.bfloat16, device=x.device)
     check(lib.b200_moe_grouped_gemm(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                    out.data_ptr(), expert_offsets.data_ptr(), R, E, n_out, k, 1 if swiglu else 0,
+                                    out.data_ptr(), expert_offsets.data_ptr(), R, E, int(dense_rows), n_out, k,
+                                    1 if swiglu else 0,
                                     _dt(x), status_word(x.device).data_ptr(), _stream()), "moe_grouped_gemm")
     return out
 

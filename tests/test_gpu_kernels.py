@@ -654,6 +654,31 @@ def test_moe_grouped_gemm_matches_per_expert_matmuls(counts, k, n, swiglu):
     assert torch.equal(again, ops.moe_grouped_gemm(x, w, offs, bias, swiglu=swiglu))
 
 
+@pytest.mark.parametrize("swiglu", [True, False])
+def test_moe_grouped_gemm_dense_tail_is_one_more_weight_set(swiglu):
+    """Rows after the grouped ones that all use weight set E (a shared expert in the same launch), in
+    chunks of 64; 150 tail rows = two full chunks and a ragged one."""
+    ops = _ops()
+    counts, tail, k, n = [12, 0, 31, 7, 16, 1, 60, 25], 150, 256, 192
+    E, R = len(counts), sum(counts)
+    offs = torch.tensor(np.cumsum(counts), dtype=torch.int32, device="cuda")
+    x = _randn((R + tail, k), 41, torch.bfloat16).cuda()
+    w = (_randn((E + 1, 2 * n if swiglu else n, k), 42, torch.float32) * k ** -0.5).bfloat16().cuda()
+    bias = _randn((E + 1, 2 * n if swiglu else n), 43, torch.bfloat16).cuda()
+    got = ops.moe_grouped_gemm(x, w, offs, bias, swiglu=swiglu, dense_rows=tail)
+    ops.check_status()
+    all_offs = torch.cat([offs, torch.tensor([R + tail], dtype=torch.int32, device="cuda")])
+    want = _grouped_reference(x, w, all_offs, bias, swiglu)
+    err = (got.float() - want.float()).abs()
+    assert (err <= 2e-2 * want.float().abs() + 2e-2).all(), err.max().item()
+    # routing with the identity tail: the gather index of the tail rows
+    logits = _randn((100, 8), 44, torch.bfloat16).cuda()
+    tok, experts, wts, o2, inv = ops.moe_route(logits, torch.zeros(8, device="cuda"), 2, identity_tail=True)
+    assert tok.numel() == 300 and torch.equal(tok[200:], torch.arange(100, device="cuda", dtype=torch.int32))
+    tok2 = ops.moe_route(logits, torch.zeros(8, device="cuda"), 2)[0]
+    assert torch.equal(tok[:200], tok2)
+
+
 # ----------------------------------------------------------------------------- empty inputs
 def test_empty_inputs_are_no_ops():
     """Zero tokens / zero sequences through every entry point: success, nothing launched or written."""
