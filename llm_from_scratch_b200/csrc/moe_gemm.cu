@@ -142,27 +142,45 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
   if (warp == 0) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      for (int pass = 0; pass < npass && ok; ++pass) {
-        const int n = min(NPASS, rows - pass * NPASS);
-        const int nb = (n + XBOX - 1) / XBOX;
+      const int total = npass * num_k;
+      auto weights = [&](int i) {           // stage i: arm the barrier for the whole stage, copy the weight tile
+        const int pass = i / num_k, ks = i - pass * num_k;
+        const int nb = (min(NPASS, rows - pass * NPASS) + XBOX - 1) / XBOX;
+        const int st = i % STAGES;
+        const uint32_t dst = sb + st * L::STAGE_BYTES;
+        umma::mbar_expect_tx(bar(FULL + st), A_BYTES + nb * (XBOX * 128));
+        tma_load_2d(dst, &tm_w, ks * BK, wrow_a, bar(FULL + st));
+        if (swiglu) tma_load_2d(dst + A_BYTES / 2, &tm_w, ks * BK, wrow_b, bar(FULL + st));
+      };
+      auto tokens = [&](int i) {            // stage i: the token rows
+        const int pass = i / num_k, ks = i - pass * num_k;
+        const int nb = (min(NPASS, rows - pass * NPASS) + XBOX - 1) / XBOX;
+        const int st = i % STAGES;
+        const uint32_t dst = sb + st * L::STAGE_BYTES + A_BYTES;
         const int xrow = row0 + pass * NPASS;
-        for (int ks = 0; ks < num_k; ++ks, ++it) {
-          const int st = it % STAGES;
-          if (it >= STAGES && !umma::mbar_wait(bar(EMPTY + st), ((it / STAGES) - 1) & 1, s_abort)) {
-            give_up();
-            ok = false;
-            break;
-          }
-          const uint32_t dst = sb + st * L::STAGE_BYTES;
-          umma::mbar_expect_tx(bar(FULL + st), A_BYTES + nb * (XBOX * 128));
-          tma_load_2d(dst, &tm_w, ks * BK, wrow_a, bar(FULL + st));
-          if (swiglu) tma_load_2d(dst + A_BYTES / 2, &tm_w, ks * BK, wrow_b, bar(FULL + st));
-          for (int j = 0; j < nb; ++j)
-            tma_load_2d(dst + A_BYTES + j * (XBOX * 128), &tm_x, ks * BK, xrow + j * XBOX, bar(FULL + st));
+        for (int j = 0; j < nb; ++j)
+          tma_load_2d(dst + j * (XBOX * 128), &tm_x, ks * BK, xrow + j * XBOX, bar(FULL + st));
+      };
+      // The weights do not depend on the kernel before this one in the stream, the token rows do: when
+      // this grid was launched early (programmatic dependent launch) the first ring of weight tiles is
+      // already streaming while the producer of the rows finishes; griddepcontrol.wait returns at once
+      // in an ordinary launch.
+      const int pre = min(STAGES, total);
+      for (int i = 0; i < pre; ++i) weights(i);
+      asm volatile("griddepcontrol.wait;\n" ::: "memory");
+      for (int i = 0; i < pre; ++i) tokens(i);
+      int it = pre;
+      for (; it < total; ++it) {
+        const int st = it % STAGES;
+        if (!umma::mbar_wait(bar(EMPTY + st), ((it / STAGES) - 1) & 1, s_abort)) {
+          give_up();
+          break;
         }
+        weights(it);
+        tokens(it);
       }
+      // let the next kernel in the stream start its own prologue while this one drains
+      asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
       if (*s_abort) {
         // copies still in flight must land before the CTA gives its shared memory back
         int never = 0;
@@ -350,7 +368,23 @@ int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3
       return B200_ERR_LAUNCH;
     configured[dev] = true;
   }
-  moe_gemm_kernel<NPASS, STAGES><<<grid, kThreads, L::SMEM, s>>>(a, tw, tx);
+  // mode 0 (the down-projection) follows mode 1 in the stream and only its token rows depend on it:
+  // launched as a programmatic dependent, its prologue and first weight tiles overlap the tail of the
+  // kernel before it (which may be any kernel: without an early trigger there this is an ordinary launch)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.mode == 0 ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, moe_gemm_kernel<NPASS, STAGES>, a, tw, tx) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
   return launch_result();
 }
 
