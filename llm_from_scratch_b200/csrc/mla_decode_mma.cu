@@ -17,6 +17,7 @@
 //   phase 2  warp h: sums the quarters of head h, scale, mask, online softmax (fp32, log2 domain), P -> smem
 //   phase 3  warp w: O[:, 32w..32w+31] += P . c
 #include "decode_common.cuh"
+#include "umma.cuh"
 
 namespace b200 {
 namespace {
@@ -28,11 +29,13 @@ constexpr int CPR = ROWB / 16;                    // 72 chunks per row
 constexpr int BLKB = kTok * ROWB;                 // 18432 bytes per block
 constexpr int GROUP = 4;                          // blocks per group (64 tokens)
 constexpr int GT = GROUP * kTok;                  // 64
-constexpr int kThreads = 512;                     // 16 warps: 4 token blocks x 4 k-quarters
+constexpr int kCompute = 512;                     // 16 compute warps: 4 token blocks x 4 k-quarters
+constexpr int kProducers = 128;                   // 4 warps that only fill the ring
+constexpr int kThreads = kCompute + kProducers;
 constexpr int KSTEPS = ROW / 16;                  // 36
 constexpr int QUART_K = KSTEPS / 4;               // 9 k-steps per warp in phase 1
 constexpr int SP_STRIDE = GT + 8;                 // padded row of the partial-S buffer (floats)
-constexpr int LOADS = (kTok * CPR + kThreads - 1) / kThreads;   // cp.async per thread per block
+constexpr int LOADS = (kTok * CPR + kProducers - 1) / kProducers;   // cp.async per producer thread per block (9)
 
 // shared memory map (bytes)
 constexpr int OFF_RING = 0;                                   // 2 groups x 4 blocks
@@ -41,7 +44,8 @@ constexpr int OFF_SPART = OFF_Q + 16 * ROWB;                  // [4][16][72] fp3
 constexpr int OFF_P = OFF_SPART + 4 * 16 * SP_STRIDE * 4;     // [16][64] bf16
 constexpr int OFF_STAT = OFF_P + 16 * GT * 2;                 // alpha[16], m[16], l[16] fp32
 constexpr int OFF_SCAN = OFF_STAT + 3 * 16 * 4;               // 34 ints
-constexpr int SMEM_BYTES = OFF_SCAN + 34 * 4 + 8;
+constexpr int OFF_BAR = (OFF_SCAN + 34 * 4 + 15) & ~15;        // full[2] mbarriers
+constexpr int SMEM_BYTES = OFF_BAR + 2 * 8 + 8;
 
 struct MlaArgs {
   const __nv_bfloat16* q_abs;   // [B, H, 512]
@@ -70,6 +74,16 @@ struct Group {
 
 __device__ __forceinline__ int swz72(int c, int row) { return c ^ (row & 7); }
 
+// Named barriers: 1 = the compute warps among themselves; 2 + half = "ring half filled" (producers arrive,
+// compute warps wait); 4 + half = "ring half free" (compute warps arrive, producers wait).
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCompute) : "memory"); }
+__device__ __forceinline__ void named_sync(int id) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(kThreads) : "memory");
+}
+__device__ __forceinline__ void named_arrive(int id) {
+  asm volatile("bar.arrive %0, %1;\n" ::"r"(id), "n"(kThreads) : "memory");
+}
+
 __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -84,6 +98,13 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
 
   const CtaRange rg = plan_cta_range(a.lens, B, a.bt_stride, kTok, s_scan);
   if (rg.cnt == 0) return;
+  auto full_bar = [&](int half) -> uint32_t { return sbase + OFF_BAR + half * 8; };
+  if (tid == 0) {
+    umma::mbar_init(full_bar(0), kProducers);   // one arrival per producer thread when its copies have landed
+    umma::mbar_init(full_bar(1), kProducers);
+    umma::mbar_init_fence();
+  }
+  __syncthreads();
 
   auto load_seq = [&](Cursor& c) {
     const int64_t len = a.lens[c.seq];
@@ -128,9 +149,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
   int ld_row[LOADS], ld_dst[LOADS], ld_src[LOADS];
 #pragma unroll
   for (int i = 0; i < LOADS; ++i) {
-    const int idx = tid + i * kThreads;
+    const int idx = (tid - kCompute) + i * kProducers;      // meaningful in the producer warps only
     const int r = idx / CPR, c = idx - r * CPR;
-    ld_row[i] = idx < kTok * CPR ? r : -1;
+    ld_row[i] = (idx >= 0 && idx < kTok * CPR) ? r : -1;
     ld_dst[i] = r * ROWB + swz72(c, r) * 16;
     ld_src[i] = idx * 16;
   }
@@ -158,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
       }
     }
   };
-  int groups_issued = 0, groups_total = 0;
+  int groups_total = 0;
   {
     // number of groups in the range (walk a copy of the cursor; a few iterations)
     Cursor t = L;
@@ -167,13 +188,21 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
       ++groups_total;
     }
   }
-  for (int s = 0; s < 2; ++s) {
-    if (groups_issued < groups_total) {
+  if (warp >= kCompute / 32) {
+    // =============================== producers ===============================
+    // Four warps do nothing but fill the ring: pushing the 4608 16-byte copies of a group through the
+    // load/store unit takes ~1200 clocks, which the compute warps used to spend between two groups.
+    for (int g = 0; g < groups_total; ++g) {
+      const int half = g & 1;
+      if (g >= 2) named_sync(4 + half);          // the compute warps are done with group g - 2
       const Group gr = next_group(L, true);
-      issue_group(gr, groups_issued & 1);
-      ++groups_issued;
+      issue_group(gr, half);
+      // arrives on the half's mbarrier when all copies this thread has issued so far have landed: the
+      // producer goes on to the next group at once, so two groups are in flight
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(full_bar(half)) : "memory");
     }
-    cp_async_commit();
+    cp_async_wait<0>();
+    return;
   }
 
   float o[4][4];
@@ -185,18 +214,12 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
   for (int gi = 0; gi < groups_total; ++gi) {
     const Group gr = next_group(C, false);
     const int half = gi & 1;
-    // form the group that will refill this ring half after phase 3 now, so that its block ids
-    // (and, on a sequence change, its context length) are in registers by then
-    Group nx;
-    nx.n = 0;
-    const bool have_next = groups_issued < groups_total;
-    if (have_next) nx = next_group(L, true);
     const uint32_t ring = sbase + OFF_RING + half * GROUP * BLKB;
     // ---- new segment: stage Q = [q_abs | q_rope] (rows >= H are zero), reset the running state
     if (fresh) {
       fresh = false;
       seg_first = gr.blk0;
-      for (int idx = tid; idx < 16 * CPR; idx += kThreads) {
+      for (int idx = tid; idx < 16 * CPR; idx += kCompute) {
         const int r = idx / CPR, c = idx - r * CPR;
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (r < H) {
@@ -214,8 +237,19 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         s_l[tid] = 0.f;
       }
     }
-    cp_async_wait<1>();
-    __syncthreads();
+    {
+      // the group has landed (one lane per warp polls, bounded); the barrier makes the verdict uniform and
+      // orders the Q staging above among the compute warps
+      int never = 0, ok = 1;
+      if (lane == 0) ok = umma::mbar_wait(full_bar(half), (gi >> 1) & 1, &never);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      int bad;
+      asm volatile("{\n.reg .pred p, q;\nsetp.eq.s32 p, %1, 0;\nbar.red.or.pred q, 1, %2, p;\nselp.s32 %0, 1, 0, q;\n}\n"
+                   : "=r"(bad) : "r"(ok), "n"(kCompute) : "memory");
+      // a timeout is reported and the group is computed on whatever is there: leaving the loop would
+      // strand the producer warps at their barrier
+      if (bad && tid == 0) report(a.status, B200_ERR_TIMEOUT);
+    }
 
     // ---- phase 1: partial S[head, token] over this warp's 16 tokens and a quarter of the 576 columns
     {
@@ -248,7 +282,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         *reinterpret_cast<float2*>(s_part + (kq * 16 + g + 8) * SP_STRIDE + token) = make_float2(sacc[n][2], sacc[n][3]);
       }
     }
-    __syncthreads();
+    compute_sync();
 
     // ---- phase 2: online softmax over the 64 tokens of the group; warp = head, lane = 2 tokens
     {
@@ -278,7 +312,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
       *reinterpret_cast<uint32_t*>(smem + OFF_P + h * 128 + (((lane >> 2) ^ (h & 7)) * 16) + (lane & 3) * 4) =
           pack_bf16x2(p0, p1);
     }
-    __syncthreads();
+    compute_sync();
 
     // ---- phase 3: O[:, 32*warp .. +31] = alpha * O + P . c
     {
@@ -307,13 +341,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         }
       }
     }
-    __syncthreads();   // this ring half, P and the partial-S buffer are free again
-
-    if (have_next) {
-      issue_group(nx, half);
-      ++groups_issued;
-    }
-    cp_async_commit();
+    compute_sync();   // P and the partial-S buffer are free again
+    if (gi + 2 < groups_total) named_arrive(4 + half);   // ... and so is this ring half: the producers refill it
 
     const bool seq_end = gr.blk0 + gr.n == gr.nblk;
     if (seq_end || gi == groups_total - 1) {
@@ -346,11 +375,10 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         a.seq_info[2 * gr.seq] = whole ? -1 : seq_start_flat / rg.per_cta;
         a.seq_info[2 * gr.seq + 1] = whole ? -1 : p;
       }
-      __syncthreads();   // the running state is re-initialised by the next segment
+      compute_sync();   // the running state is re-initialised by the next segment
     }
     flat += gr.n;
   }
-  cp_async_wait<0>();
 }
 
 bool mla_fast_shape(int H, int r, int dr, int bs) {
