@@ -9,13 +9,20 @@
 //
 // Work split: as in the GQA decode kernel the flat list of all KV blocks is cut into equal
 // contiguous ranges, one per persistent CTA (one CTA per SM); sequences cut across CTAs are merged
-// by the shared combine kernel.  A CTA (16 warps) consumes its range in groups of four blocks
-// (64 tokens) held in a two-group shared-memory ring filled by 16-byte cp.async copies, so one
-// group (72 KiB) is always in flight while the previous one is being used:
+// by the shared combine kernel.  A CTA consumes its range in groups of four blocks (64 tokens) held in
+// a two-group shared-memory ring (72 KiB per group), so one group is in flight while the previous one
+// is being used.  The ring is filled by a 17th warp with TMA: a block is ONE box of a rank-3 view of the
+// pool (64 columns x 16 tokens x 9 slabs, strides 2 B / 1152 B / 128 B), written slab by slab with the
+// 128-byte swizzle that ldmatrix wants and counted on an mbarrier per ring half; named barriers hand a
+// half back to the producer.  (With 16-byte cp.async copies issued by the compute warps themselves, 1200
+// of the 4300 clocks of a group went into pushing 4608 copies through the load/store unit.)
+// The 16 compute warps then run, per group:
 //   phase 1  warp w: tokens 16*(w&3)..+15, quarter (w>>2) of the 576-wide contraction -> partial S
 //            (its Q fragments stay in registers for the whole sequence segment)
 //   phase 2  warp h: sums the quarters of head h, scale, mask, online softmax (fp32, log2 domain), P -> smem
 //   phase 3  warp w: O[:, 32w..32w+31] += P . c
+#include <cuda.h>
+
 #include "decode_common.cuh"
 #include "umma.cuh"
 
@@ -30,12 +37,12 @@ constexpr int BLKB = kTok * ROWB;                 // 18432 bytes per block
 constexpr int GROUP = 4;                          // blocks per group (64 tokens)
 constexpr int GT = GROUP * kTok;                  // 64
 constexpr int kCompute = 512;                     // 16 compute warps: 4 token blocks x 4 k-quarters
-constexpr int kProducers = 128;                   // 4 warps that only fill the ring
+constexpr int kProducers = 32;                    // one warp that only fills the ring (TMA)
 constexpr int kThreads = kCompute + kProducers;
 constexpr int KSTEPS = ROW / 16;                  // 36
 constexpr int QUART_K = KSTEPS / 4;               // 9 k-steps per warp in phase 1
 constexpr int SP_STRIDE = GT + 8;                 // padded row of the partial-S buffer (floats)
-constexpr int LOADS = (kTok * CPR + kProducers - 1) / kProducers;   // cp.async per producer thread per block (9)
+constexpr int SLABS = ROW / 64;                   // 9 slabs of 64 columns (128 bytes) per block
 
 // shared memory map (bytes)
 constexpr int OFF_RING = 0;                                   // 2 groups x 4 blocks
@@ -45,7 +52,7 @@ constexpr int OFF_P = OFF_SPART + 4 * 16 * SP_STRIDE * 4;     // [16][64] bf16
 constexpr int OFF_STAT = OFF_P + 16 * GT * 2;                 // alpha[16], m[16], l[16] fp32
 constexpr int OFF_SCAN = OFF_STAT + 3 * 16 * 4;               // 34 ints
 constexpr int OFF_BAR = (OFF_SCAN + 34 * 4 + 15) & ~15;        // full[2] mbarriers
-constexpr int SMEM_BYTES = OFF_BAR + 2 * 8 + 8;
+constexpr int SMEM_BYTES = OFF_BAR + 2 * 8 + 8 + 1024;       // + slack to align the ring to 1024 bytes
 
 struct MlaArgs {
   const __nv_bfloat16* q_abs;   // [B, H, 512]
@@ -74,6 +81,12 @@ struct Group {
 
 __device__ __forceinline__ int swz72(int c, int row) { return c ^ (row & 7); }
 
+// byte offset of 16-byte chunk c (0..71) of token row r (0..15) inside a block of the ring: 9 slabs of
+// [16 rows x 128 B], chunks XOR-swizzled with the row as TMA's 128-byte swizzle writes them
+__device__ __forceinline__ int lat_off(int r, int c) {
+  return (c >> 3) * (kTok * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+
 // Named barriers: 1 = the compute warps among themselves; 2 + half = "ring half filled" (producers arrive,
 // compute warps wait); 4 + half = "ring half free" (compute warps arrive, producers wait).
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCompute) : "memory"); }
@@ -84,8 +97,10 @@ __device__ __forceinline__ void named_arrive(int id) {
   asm volatile("bar.arrive %0, %1;\n" ::"r"(id), "n"(kThreads) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaArgs a) {
-  extern __shared__ __align__(128) uint8_t smem[];
+__global__ void __launch_bounds__(kThreads, 1)
+mla_decode_mma_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_lat) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   float* s_part = reinterpret_cast<float*>(smem + OFF_SPART);
   float* s_alpha = reinterpret_cast<float*>(smem + OFF_STAT);
@@ -99,11 +114,17 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
   const CtaRange rg = plan_cta_range(a.lens, B, a.bt_stride, kTok, s_scan);
   if (rg.cnt == 0) return;
   auto full_bar = [&](int half) -> uint32_t { return sbase + OFF_BAR + half * 8; };
+  // Ring rows that no copy has written (blocks past the end of a group, at first) are read by phase 3
+  // with weight 0: they must hold finite numbers, so the ring starts as zeros.
+  for (int i = tid; i < 2 * GROUP * BLKB / 16; i += kThreads)
+    reinterpret_cast<uint4*>(smem + OFF_RING)[i] = make_uint4(0u, 0u, 0u, 0u);
   if (tid == 0) {
-    umma::mbar_init(full_bar(0), kProducers);   // one arrival per producer thread when its copies have landed
-    umma::mbar_init(full_bar(1), kProducers);
+    umma::mbar_init(full_bar(0), GROUP);        // one arrival (with its byte count) per block of the group
+    umma::mbar_init(full_bar(1), GROUP);
     umma::mbar_init_fence();
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tm_lat)) : "memory");
   }
+  umma::fence_async_proxy();
   __syncthreads();
 
   auto load_seq = [&](Cursor& c) {
@@ -145,37 +166,24 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
   load_seq(L);
   C = L;
 
-  // per-thread copy pattern of one block, fixed for the whole kernel
-  int ld_row[LOADS], ld_dst[LOADS], ld_src[LOADS];
-#pragma unroll
-  for (int i = 0; i < LOADS; ++i) {
-    const int idx = (tid - kCompute) + i * kProducers;      // meaningful in the producer warps only
-    const int r = idx / CPR, c = idx - r * CPR;
-    ld_row[i] = (idx >= 0 && idx < kTok * CPR) ? r : -1;
-    ld_dst[i] = r * ROWB + swz72(c, r) * 16;
-    ld_src[i] = idx * 16;
-  }
-  // fills ring half `half` with the four blocks of a group; missing rows / blocks are zero-filled
+  // fills ring half `half` with the blocks of a group: one rank-3 TMA box per block (64 columns x 16
+  // tokens x 9 slabs), each counted on the half's barrier; a missing or out-of-pool block only arrives
   auto issue_group = [&](const Group& gr, int half) {
+    const uint32_t bar = full_bar(half);
 #pragma unroll
     for (int b = 0; b < GROUP; ++b) {
-      const uint32_t dst = sbase + OFF_RING + (half * GROUP + b) * BLKB;
-      int valid = 0;
-      const uint8_t* src = a.lat;
+      bool load = false;
+      int id = 0;
       if (b < gr.n) {
-        const int id = gr.ids[b];
-        if (static_cast<uint64_t>(static_cast<int64_t>(id)) < static_cast<uint64_t>(a.num_blocks)) {
-          valid = min(kTok, gr.len - (gr.blk0 + b) * kTok);
-          src = a.lat + static_cast<int64_t>(id) * BLKB;
-        } else {
-          report(a.status, B200_ERR_BOUNDS);
-        }
+        id = gr.ids[b];
+        load = static_cast<uint64_t>(static_cast<int64_t>(id)) < static_cast<uint64_t>(a.num_blocks);
+        if (!load) report(a.status, B200_ERR_BOUNDS);
       }
-#pragma unroll
-      for (int i = 0; i < LOADS; ++i) {
-        if (ld_row[i] < 0) continue;
-        const bool ok = ld_row[i] < valid;
-        cp_async16(dst + ld_dst[i], ok ? src + ld_src[i] : a.lat, ok ? 16 : 0);
+      if (load) {
+        umma::mbar_expect_tx(bar, BLKB);
+        umma::tma_load_3d(sbase + OFF_RING + (half * GROUP + b) * BLKB, &tm_lat, 0, id * kTok, 0, bar);
+      } else {
+        umma::mbar_arrive(bar);
       }
     }
   };
@@ -189,19 +197,16 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
     }
   }
   if (warp >= kCompute / 32) {
-    // =============================== producers ===============================
-    // Four warps do nothing but fill the ring: pushing the 4608 16-byte copies of a group through the
-    // load/store unit takes ~1200 clocks, which the compute warps used to spend between two groups.
+    // =============================== producer ===============================
+    // One warp does nothing but fill the ring; the compute warps used to spend ~1200 clocks per group
+    // pushing 4608 16-byte cp.async copies through the load/store unit.
     for (int g = 0; g < groups_total; ++g) {
       const int half = g & 1;
       if (g >= 2) named_sync(4 + half);          // the compute warps are done with group g - 2
       const Group gr = next_group(L, true);
-      issue_group(gr, half);
-      // arrives on the half's mbarrier when all copies this thread has issued so far have landed: the
-      // producer goes on to the next group at once, so two groups are in flight
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(full_bar(half)) : "memory");
+      if (lane == 0) issue_group(gr, half);
+      __syncwarp();
     }
-    cp_async_wait<0>();
     return;
   }
 
@@ -243,6 +248,18 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
       int never = 0, ok = 1;
       if (lane == 0) ok = umma::mbar_wait(full_bar(half), (gi >> 1) & 1, &never);
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      {
+        // rows of the group's last block past the end of the context hold whatever the pool has there:
+        // zero them (their softmax weight is 0, but 0 * NaN is not)
+        const int valid = min(gr.len - gr.blk0 * kTok, gr.n * kTok);
+        const int extra = gr.n * kTok - valid;               // 0..15 rows, all in block gr.n - 1
+        for (int idx = tid; idx < extra * CPR; idx += kCompute) {
+          const int r = valid % kTok + idx / CPR, c = idx % CPR;
+          *reinterpret_cast<uint4*>(smem + OFF_RING + (half * GROUP + gr.n - 1) * BLKB + lat_off(r, c)) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (extra > 0) umma::fence_async_proxy();            // before the copy that refills this half
+      }
       int bad;
       asm volatile("{\n.reg .pred p, q;\nsetp.eq.s32 p, %1, 0;\nbar.red.or.pred q, 1, %2, p;\nselp.s32 %0, 1, 0, q;\n}\n"
                    : "=r"(bad) : "r"(ok), "n"(kCompute) : "memory");
@@ -270,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
 #pragma unroll
       for (int i = 0; i < QUART_K; ++i) {
         uint32_t bf[4];
-        ldmatrix_x4(bf, blk + rb * ROWB + swz72(2 * (kq * QUART_K + i) + chb, rb) * 16);
+        ldmatrix_x4(bf, blk + lat_off(rb, 2 * (kq * QUART_K + i) + chb));
         const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
         mma_bf16_16816(sacc[0], qf[i], b0);
         mma_bf16_16816(sacc[1], qf[i], b1);
@@ -334,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_mma_kernel(const MlaAr
         for (int pr2 = 0; pr2 < 2; ++pr2) {
           uint32_t bf[4];
           const int chunk = 4 * warp + 2 * pr2 + chp;
-          ldmatrix_x4_trans(bf, ring + kk * BLKB + rp * ROWB + swz72(chunk, rp) * 16);
+          ldmatrix_x4_trans(bf, ring + kk * BLKB + lat_off(rp, chunk));
           const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
           mma_bf16_16816(o[2 * pr2], pf, b0);
           mma_bf16_16816(o[2 * pr2 + 1], pf, b1);
@@ -385,6 +402,26 @@ bool mla_fast_shape(int H, int r, int dr, int bs) {
   return r == R && dr == DR && bs == kTok && H >= 1 && H <= 16;
 }
 
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn tensor_map_encoder() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
 }  // namespace
 
 size_t mla_decode_mma_workspace(int batch, int H, int r, int dr) {
@@ -402,12 +439,29 @@ int mla_decode_mma_launch(const void* q_abs, const void* q_rope, const void* lat
   if (!mla_fast_shape(H, r, dr, bs)) return B200_ERR_UNSUPPORTED;
   if (!aligned16(q_abs) || !aligned16(q_rope) || !aligned16(lat) || !aligned16(out))
     return B200_ERR_UNSUPPORTED;
+  if (num_blocks <= 0 || num_blocks * kTok > 2147483647LL) return B200_ERR_UNSUPPORTED;
+  EncodeFn enc = tensor_map_encoder();
+  if (enc == nullptr) return B200_ERR_UNSUPPORTED;
   const int sms = sm_count_cached();
   if (sms <= 0) return B200_ERR_NO_DEVICE;
   const size_t grid = static_cast<size_t>(sms);
   const size_t need = decode_workspace_bytes(grid, batch, H, R);
   if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
+  // The pool seen as (column within a slab: 64, token row: num_blocks * 16, slab: 9) with strides
+  // (2 B, 1152 B, 128 B): one box = one KV block, written slab by slab — [9][16 tokens][128 B] — which is
+  // the layout lat_off() addresses, so a block is a single copy instruction.
+  CUtensorMap tm;
+  {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(num_blocks) * kTok, static_cast<cuuint64_t>(SLABS)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ROWB), 128};
+    const cuuint32_t box[3] = {64, kTok, static_cast<cuuint32_t>(SLABS)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(lat), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return B200_ERR_UNSUPPORTED;
+  }
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -436,7 +490,7 @@ int mla_decode_mma_launch(const void* q_abs, const void* q_rope, const void* lat
   a.part_ml = reinterpret_cast<float*>(w);
   w += align256(grid * 2 * H * 2 * sizeof(float));
   a.seq_info = reinterpret_cast<int32_t*>(w);
-  mla_decode_mma_kernel<<<static_cast<int>(grid), kThreads, SMEM_BYTES, s>>>(a);
+  mla_decode_mma_kernel<<<static_cast<int>(grid), kThreads, SMEM_BYTES, s>>>(a, tm);
   const int rc = launch_result();
   if (rc != B200_OK) return rc;
   CombineArgs c{};
