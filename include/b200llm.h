@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 5
+#define B200_ABI_VERSION 6
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -170,6 +170,24 @@ int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                         int64_t num_blocks, const int32_t* plan, int32_t plan_tile_rows,
                         int32_t plan_capacity, int32_t dtype, int32_t* status, void* stream);
 
+/* The same attention for keys stored in two parts, as the expanded form of multi-head latent attention
+ * has them (model/attention/MLA.py:93-95,131: k = [k_nope of the head | k_rope shared by all heads]):
+ *   k_head [total_k, H, head_dim_qk - tail_dim]  per-head columns, token stride k_head_token_stride
+ *   k_tail [total_k, tail_dim]                   last tail_dim columns of every head's key
+ *   q      [total_q, H, head_dim_qk], v [total_k, H, head_dim_v], out [total_q, H, head_dim_v]
+ * so the rotary part is never copied into every head.  Keys/values are packed (no paged prefix).
+ * bf16, (head_dim_qk, head_dim_v) = (192, 128) or equal dims of 32/64/128, all parts 16-byte aligned
+ * with tail_dim a multiple of 8; anything else returns B200_ERR_UNSUPPORTED.  plan: as above, for the
+ * tile_rows of b200_prefill_tile_rows(head_dim_qk, head_dim_v, H, H, dtype). */
+int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const void* k_tail, const void* v,
+                                    void* out, int64_t q_token_stride, int64_t k_head_token_stride,
+                                    int64_t k_tail_token_stride, int64_t v_token_stride,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                    int32_t num_seqs, int32_t max_seqlen_q, int32_t num_heads,
+                                    int32_t head_dim_qk, int32_t tail_dim, int32_t head_dim_v, float scale,
+                                    const int32_t* plan, int32_t plan_tile_rows, int32_t plan_capacity,
+                                    int32_t dtype, int32_t* status, void* stream);
+
 /* Tile list for b200_prefill_varlen, computed on the device from cu_seqlens_q (one small launch per
  * step; all layers of the step reuse it).
  *   b200_prefill_tile_rows: query rows per tile of the kernel that serves this shape (128 tcgen05,
@@ -229,6 +247,27 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride, const flo
                             int64_t num_slots, int64_t num_tokens, int32_t num_q_heads,
                             int32_t num_kv_heads, int32_t head_dim, float eps, int32_t dtype,
                             int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Everything MultiHeadLatentAttention.forward does between its projections and the attention
+ * (model/attention/MLA.py:114-131 and the cache write of :137-138), one pass per token:
+ *   q_up    [num_tokens, >= H*head_dim + H*rope_dim] (row stride in elements): the fused q up-projection,
+ *           q_nope of all heads followed by q_rope of all heads;
+ *   kv_down [num_tokens, >= kv_lora_rank + rope_dim]: the kv down-projection followed by k_rope.
+ *   q_out    [num_tokens, H, head_dim + rope_dim] = [ q_nope | RoPE(q_rope) ]
+ *   rows_out [num_tokens, kv_lora_rank + rope_dim] = [ RMSNorm(c) * kv_norm_weight | RoPE(k_rope) ]
+ *            (may be NULL); the same row is written to latent_cache[slot_mapping[t]] when
+ *            latent_cache != NULL (slot < 0 skipped).
+ * RoPE is half-split, fp32, and reads cos from rope_table[pos, 0 : rope_dim/2] and "sin" from
+ * rope_table[pos, rope_dim/2 : rope_dim]: the reference slices a table built for head_dim to its first
+ * rope_dim columns (model/attention/utils.py:38), which this reproduces.  bf16 only.
+ * ------------------------------------------------------------------------------------------- */
+int b200_mla_prologue(const void* q_up, int64_t q_up_stride, const void* kv_down, int64_t kv_down_stride,
+                      const float* kv_norm_weight, const float* rope_table, int64_t rope_width,
+                      int64_t rope_positions, const int64_t* positions, void* q_out, void* rows_out,
+                      void* latent_cache, const int64_t* slot_mapping, int64_t num_slots,
+                      int64_t num_tokens, int32_t num_heads, int32_t head_dim, int32_t rope_dim,
+                      int32_t kv_lora_rank, float eps, int32_t dtype, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * MoE routing for inference (Gate.forward, model/architecture/moe.py:45-90, and the grouping by

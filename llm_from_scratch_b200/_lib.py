@@ -32,6 +32,8 @@ SIGNATURES = {
                                      _i32, _i64, _f32, _vp, _sz, _i32, _vp, _vp]),
     "b200_paged_decode_gqa_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32,
                                             _i32, _i32, _i64, _f32, _i32, _vp, _vp]),
+    "b200_prefill_varlen_shared_tail": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
+                                               _i32, _i32, _i32, _i32, _f32, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b200_prefill_varlen": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
                                    _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _i64, _i32,
                                    _i64, _vp, _i32, _i32, _i32, _vp, _vp]),
@@ -39,6 +41,8 @@ SIGNATURES = {
     "b200_prefill_plan_bytes": (_sz, [_i64, _i32, _i32]),
     "b200_prefill_plan": (_i32, [_vp, _i32, _i32, _i32, _vp, _sz, _vp, _vp]),
     "b200_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _i32, _i32, _vp]),
+    "b200_mla_prologue": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                 _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp]),
     "b200_qk_norm_rope_store": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                        _i32, _i32, _i32, _f32, _i32, _vp, _vp]),
     "b200_moe_route_workspace_bytes": (_sz, [_i32, _i32]),

@@ -373,3 +373,177 @@ extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride
     qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
   return launch_result();
 }
+
+// ---------------------------------------------------------------------------------------------
+// MLA pre-attention stage (MultiHeadLatentAttention.forward between the projections and the attention,
+// model/attention/MLA.py:114-131,137-138), one warp per token:
+//   q_out[t, h]   = [ q_nope[t, h] (copied) | rope(q_rope[t, h]) ]           from the q up-projection row
+//   rows_out[t]   = [ kv_norm(c[t]) | rope(k_rope[t]) ]                       from the kv down-projection row
+//   latent_cache[slot_mapping[t]] = rows_out[t]                               (slot < 0 skipped)
+// kv_norm is RMSNorm over the kv_lora_rank columns in fp32, rounded to the dtype.  RoPE is the
+// reference's half-split rotation in fp32 with the table sliced to the first rope_dim columns of a row:
+// cos = row[0 : rope_dim/2], sin = row[rope_dim/2 : rope_dim] — for a table wider than rope_dim that
+// "sin" is not a sine (model/attention/utils.py:38); the slice is reproduced as it is.
+namespace b200 {
+namespace {
+
+struct MlaProArgs {
+  const __nv_bfloat16* qf;      // [T, >= H*hd + H*dr]: q_nope of all heads, then q_rope of all heads
+  int64_t qf_stride;
+  const __nv_bfloat16* kvp;     // [T, >= r + dr]: latent c, then k_rope
+  int64_t kvp_stride;
+  const float* kv_norm_w;       // [r]
+  const float* rope;            // [max_pos, rope_width]
+  int64_t rope_width, max_pos;
+  const int64_t* positions;
+  __nv_bfloat16* q_out;         // [T, H, hd + dr]
+  __nv_bfloat16* rows_out;      // [T, r + dr] or null
+  __nv_bfloat16* cache;         // [num_slots, r + dr] or null
+  const int64_t* slots;
+  int64_t num_slots;
+  int H, hd, dr, r;
+  float eps;
+  int32_t* status;
+};
+
+// rotate 8 consecutive elements of a half-split pair: x = own chunk, the partner chunk (half a vector
+// away) comes from the lane `partner_lanes` away; j0 = index of the chunk's first element within its half
+__device__ __forceinline__ uint4 rope8(uint4 raw, bool first_half, const float* cs, int j0, int half, int partner_lanes) {
+  Bf16x8 u, o;
+  u.u = raw;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float xv = __bfloat162float(u.b[i]);
+    const float pv = __shfl_xor_sync(0xffffffffu, xv, partner_lanes);
+    const float c = cs[j0 + i], s = cs[half + j0 + i];
+    o.b[i] = __float2bfloat16(first_half ? xv * c - pv * s : xv * c + pv * s);
+  }
+  return o.u;
+}
+
+__global__ void __launch_bounds__(kWarpRows * 32) mla_prologue_kernel(const MlaProArgs a, int64_t num_tokens) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarpRows + (threadIdx.x >> 5);
+  if (t >= num_tokens) return;
+  const int H = a.H, hd = a.hd, dr = a.dr, r = a.r, half = dr / 2, W = hd + dr;
+  int64_t pos = a.positions[t];
+  if (pos < 0 || pos >= a.max_pos) {
+    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
+    pos = pos < 0 ? 0 : a.max_pos - 1;
+  }
+  const float* cs = a.rope + pos * a.rope_width;
+  const __nv_bfloat16* qrow = a.qf + t * a.qf_stride;
+  __nv_bfloat16* qo = a.q_out + t * H * W;
+  // ---- q_nope: straight copy, 16 bytes per lane and trip
+  const int nope_chunks = H * hd / 8, cph = hd / 8;
+  for (int c = lane; c < nope_chunks; c += 32) {
+    const int h = c / cph, j = c - h * cph;
+    *reinterpret_cast<uint4*>(qo + h * W + j * 8) = *reinterpret_cast<const uint4*>(qrow + c * 8);
+  }
+  // ---- q_rope: dr/8 chunks per head, partner chunk half a head away = (dr/16) lanes away
+  const int rpc = dr / 8, partner = rpc / 2;
+  const __nv_bfloat16* qr = qrow + H * hd;
+  for (int c0 = 0; c0 < H * rpc; c0 += 32) {      // H * rpc is a multiple of 32 or the tail lanes idle in pairs
+    const int c = c0 + lane;
+    const bool live = c < H * rpc;
+    const int h = live ? c / rpc : 0, j = live ? c - h * rpc : 0;
+    const uint4 raw = live ? *reinterpret_cast<const uint4*>(qr + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+    const bool first = j < partner;
+    const uint4 rot = rope8(raw, first, cs, (first ? j : j - partner) * 8, half, partner);
+    if (live) *reinterpret_cast<uint4*>(qo + h * W + hd + j * 8) = rot;
+  }
+  // ---- latent row: RMSNorm of c, RoPE of k_rope
+  const __nv_bfloat16* krow = a.kvp + t * a.kvp_stride;
+  float ss = 0.f;
+  for (int c = lane; c < r / 8; c += 32) {
+    Bf16x8 u;
+    u.u = *reinterpret_cast<const uint4*>(krow + c * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = __bfloat162float(u.b[i]);
+      ss += f * f;
+    }
+  }
+  const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(r) + a.eps);
+  int64_t slot = a.cache ? a.slots[t] : -1;
+  if (slot >= a.num_slots) {
+    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
+    slot = -1;
+  }
+  __nv_bfloat16* ro = a.rows_out ? a.rows_out + t * (r + dr) : nullptr;
+  __nv_bfloat16* co = slot >= 0 ? a.cache + slot * (r + dr) : nullptr;
+  for (int c = lane; c < r / 8; c += 32) {
+    Bf16x8 u, o;
+    u.u = *reinterpret_cast<const uint4*>(krow + c * 8);
+    const float4 w0 = *reinterpret_cast<const float4*>(a.kv_norm_w + c * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(a.kv_norm_w + c * 8 + 4);
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.b[i] = __float2bfloat16(__bfloat162float(u.b[i]) * inv * ww[i]);
+    if (ro) *reinterpret_cast<uint4*>(ro + c * 8) = o.u;
+    if (co) *reinterpret_cast<uint4*>(co + c * 8) = o.u;
+  }
+  {
+    const bool live = lane < rpc;
+    const uint4 raw = live ? *reinterpret_cast<const uint4*>(krow + r + lane * 8) : make_uint4(0u, 0u, 0u, 0u);
+    const bool first = lane < partner;
+    const uint4 rot = rope8(raw, first, cs, (first ? lane : lane - partner) * 8, half, partner);
+    if (live) {
+      if (ro) *reinterpret_cast<uint4*>(ro + r + lane * 8) = rot;
+      if (co) *reinterpret_cast<uint4*>(co + r + lane * 8) = rot;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_mla_prologue(const void* q_up, int64_t q_up_stride, const void* kv_down, int64_t kv_down_stride,
+                                 const float* kv_norm_weight, const float* rope_table, int64_t rope_width,
+                                 int64_t rope_positions, const int64_t* positions, void* q_out, void* rows_out,
+                                 void* latent_cache, const int64_t* slot_mapping, int64_t num_slots,
+                                 int64_t num_tokens, int32_t num_heads, int32_t head_dim, int32_t rope_dim,
+                                 int32_t kv_lora_rank, float eps, int32_t dtype, int32_t* status, void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || num_heads <= 0 || head_dim <= 0 || rope_dim <= 0 || kv_lora_rank <= 0 || rope_positions <= 0)
+    return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  // 16-byte chunks everywhere, and a rotation partner that is a whole number of lanes away
+  const int rpc = rope_dim / 8;
+  if (head_dim % 8 || rope_dim % 16 || kv_lora_rank % 8 || (rpc & (rpc - 1)) || rpc > 32 || rope_width < rope_dim)
+    return B200_ERR_UNSUPPORTED;
+  if (num_tokens == 0) return B200_OK;
+  if (!q_up || !kv_down || !kv_norm_weight || !rope_table || !positions || !q_out) return B200_ERR_ARG;
+  if (latent_cache && !slot_mapping) return B200_ERR_ARG;
+  const int64_t q_w = static_cast<int64_t>(num_heads) * (head_dim + rope_dim);
+  if (q_up_stride < q_w || kv_down_stride < kv_lora_rank + rope_dim || q_up_stride % 8 || kv_down_stride % 8)
+    return B200_ERR_ARG;
+  if (!aligned16(q_up) || !aligned16(kv_down) || !aligned16(kv_norm_weight) || !aligned16(q_out) ||
+      (rows_out && !aligned16(rows_out)) || (latent_cache && !aligned16(latent_cache)))
+    return B200_ERR_ALIGN;
+  if (num_tokens > 2147483647LL * kWarpRows) return B200_ERR_TOO_LARGE;
+  MlaProArgs a{};
+  a.qf = static_cast<const __nv_bfloat16*>(q_up);
+  a.qf_stride = q_up_stride;
+  a.kvp = static_cast<const __nv_bfloat16*>(kv_down);
+  a.kvp_stride = kv_down_stride;
+  a.kv_norm_w = kv_norm_weight;
+  a.rope = rope_table;
+  a.rope_width = rope_width;
+  a.max_pos = rope_positions;
+  a.positions = positions;
+  a.q_out = static_cast<__nv_bfloat16*>(q_out);
+  a.rows_out = static_cast<__nv_bfloat16*>(rows_out);
+  a.cache = static_cast<__nv_bfloat16*>(latent_cache);
+  a.slots = slot_mapping;
+  a.num_slots = num_slots;
+  a.H = num_heads;
+  a.hd = head_dim;
+  a.dr = rope_dim;
+  a.r = kv_lora_rank;
+  a.eps = eps;
+  a.status = status;
+  const int grid = static_cast<int>((num_tokens + kWarpRows - 1) / kWarpRows);
+  mla_prologue_kernel<<<grid, kWarpRows * 32, 0, static_cast<cudaStream_t>(stream)>>>(a, num_tokens);
+  return launch_result();
+}

@@ -26,6 +26,11 @@ struct MmaArgs {
   const __nv_bfloat16* v;
   __nv_bfloat16* out;
   int64_t q_stride, k_stride, v_stride;  // elements between tokens
+  // keys in two parts (packed K only): columns [0, DQK - tail) per kv head from `k`, the last `tail`
+  // columns from `k_tail`, one row per token shared by every head (MLA's rotary key part)
+  const __nv_bfloat16* k_tail;
+  int64_t k_tail_stride;
+  int tail;
   const int32_t* cu_q;
   const int32_t* cu_k;
   int Hq, Hkv, ntiles_max;
@@ -89,8 +94,9 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
       }
       return a.kc + ((static_cast<int64_t>(id) * a.bs + n % a.bs) * a.Hkv + kvh) * DQK;
     }
-    return a.k + static_cast<int64_t>(k0 + n) * a.k_stride + static_cast<int64_t>(kvh) * DQK;
+    return a.k + static_cast<int64_t>(k0 + n) * a.k_stride + static_cast<int64_t>(kvh) * (DQK - a.tail);
   };
+  const int head_chunks = (DQK - a.tail) / 8;   // 16-byte chunks of a key row that come from `k`
   auto v_row = [&](int n) -> const __nv_bfloat16* {
     if (PAGED) {
       const int id = __ldg(a.bt + static_cast<int64_t>(seq) * a.bt_stride + n / a.bs);
@@ -111,6 +117,8 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
       const int idx = threadIdx.x + i * kThreads;
       const int r = idx / CPRK, c = idx % CPRK;
       const __nv_bfloat16* src = r < valid ? k_row(n0 + r) : nullptr;
+      if (!PAGED && src && c >= head_chunks)
+        src = a.k_tail + static_cast<int64_t>(k0 + n0 + r) * a.k_tail_stride - head_chunks * 8;
       cp_async16(sK + stage * KB + r * (DQK * 2) + swz<DQK>(c, r) * 16,
                  src ? src + c * 8 : dummy, src ? 16 : 0);
     }
@@ -308,8 +316,9 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        int Dqk, int Dv, float scale, const void* kc, const void* vc,
                        const int32_t* bt, int64_t bt_stride, int bs, int64_t num_blocks,
                        const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
-                       cudaStream_t s) {
+                       cudaStream_t s, const void* k_tail, int64_t k_tail_stride, int tail) {
   const bool paged = bt != nullptr;
+  if (tail < 0 || tail % 8 || tail >= Dqk || (tail > 0 && (paged || !k_tail))) return B200_ERR_ARG;
   const bool shape_ok = (Dqk == Dv && (Dqk == 32 || Dqk == 64 || Dqk == 128)) ||
                         (Dqk == 192 && Dv == 128);
   if (!shape_ok) return B200_ERR_UNSUPPORTED;
@@ -322,6 +331,7 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
   if (!al(q, q_stride) || !aligned16(out)) return B200_ERR_UNSUPPORTED;
   if (paged ? !(aligned16(kc) && aligned16(vc)) : !(al(k, k_stride) && al(v, v_stride)))
     return B200_ERR_UNSUPPORTED;
+  if (tail > 0 && !al(k_tail, k_tail_stride)) return B200_ERR_UNSUPPORTED;
   MmaArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.k = static_cast<const __nv_bfloat16*>(k);
@@ -330,6 +340,9 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
   a.q_stride = q_stride;
   a.k_stride = k_stride;
   a.v_stride = v_stride;
+  a.k_tail = static_cast<const __nv_bfloat16*>(k_tail);
+  a.k_tail_stride = k_tail_stride;
+  a.tail = tail;
   a.cu_q = cu_q;
   a.cu_k = cu_k;
   a.Hq = Hq;

@@ -110,7 +110,7 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        int Dqk, int Dv, float scale, const void* kc, const void* vc,
                        const int32_t* bt, int64_t bt_stride, int bs, int64_t num_blocks,
                        const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
-                       cudaStream_t s);
+                       cudaStream_t s, const void* k_tail = nullptr, int64_t k_tail_stride = 0, int tail = 0);
 
 // tcgen05 path (prefill_umma.cu): head_dim 128, even group size
 int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
@@ -319,4 +319,26 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
   else
     prefill_simple_kernel<__nv_bfloat16><<<grid, kWarps * 32, 0, s>>>(a);
   return launch_result();
+}
+
+extern "C" int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const void* k_tail, const void* v,
+                                               void* out, int64_t q_token_stride, int64_t k_head_token_stride,
+                                               int64_t k_tail_token_stride, int64_t v_token_stride,
+                                               const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                               int32_t num_seqs, int32_t max_seqlen_q, int32_t num_heads,
+                                               int32_t head_dim_qk, int32_t tail_dim, int32_t head_dim_v,
+                                               float scale, const int32_t* plan, int32_t plan_tile_rows,
+                                               int32_t plan_capacity, int32_t dtype, int32_t* status,
+                                               void* stream) {
+  using namespace b200;
+  if (num_seqs < 0 || max_seqlen_q < 0 || num_heads <= 0 || head_dim_qk <= 0 || head_dim_v <= 0 ||
+      tail_dim <= 0 || tail_dim >= head_dim_qk)
+    return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (num_seqs == 0 || max_seqlen_q == 0) return B200_OK;
+  if (!q || !k_head || !k_tail || !v || !out || !cu_seqlens_q || !cu_seqlens_k) return B200_ERR_ARG;
+  return prefill_mma_launch(q, k_head, v, out, q_token_stride, k_head_token_stride, v_token_stride, cu_seqlens_q,
+                            cu_seqlens_k, num_seqs, max_seqlen_q, num_heads, num_heads, head_dim_qk, head_dim_v,
+                            scale, nullptr, nullptr, nullptr, 0, 0, 0, plan, plan_tile_rows, plan_capacity, status,
+                            static_cast<cudaStream_t>(stream), k_tail, k_tail_token_stride, tail_dim);
 }

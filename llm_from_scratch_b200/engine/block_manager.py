@@ -116,16 +116,13 @@ class BlockManager:
     def allocate(self, seq: Sequence) -> None:
         """Give ``seq`` a block per ``block_size`` tokens, reusing blocks whose chained hash and
         token ids match (block_manager.py:85-114)."""
+        if not self.reference_exact:
+            return self._allocate_fast(seq)
         h = -1
         bs = self.block_size
-        # default mode: all full-block hashes of the prompt in one native call (same chain of values)
-        chain = None if self.reference_exact else ops.block_hash_chain(seq.token_ids, bs)
         for i in range(seq.num_blocks):
             token_ids = seq.block(i)
-            if chain is not None:
-                h = chain[i] if len(token_ids) == bs else -1
-            else:
-                h = self.compute_hash(token_ids, h) if len(token_ids) == bs else -1
+            h = self.compute_hash(token_ids, h) if len(token_ids) == bs else -1
             block_id = self.hash_to_block_id.get(h, -1)
             hit = block_id != -1 and self.blocks[block_id].token_ids == token_ids
             if hit:
@@ -141,6 +138,45 @@ class BlockManager:
                 if h != -1:
                     self.hash_to_block_id[h] = block.block_id
             seq.block_table.append(block.block_id)
+
+    def _allocate_fast(self, seq: Sequence) -> None:
+        """``allocate`` of the default mode with the per-block calls folded into one loop: all full-block
+        hashes of the prompt come from one native call (the same chain of values), and a miss takes the
+        oldest free block, drops the stale hash entry that still points at it and fills it in place."""
+        bs = self.block_size
+        ids = seq.token_ids
+        chain = ops.block_hash_chain(ids, bs)
+        blocks, free, used, h2b = self.blocks, self._free, self.used_block_ids, self.hash_to_block_id
+        table = seq.block_table
+        cached = 0
+        for i in range(seq.num_blocks):
+            token_ids = ids[i * bs:(i + 1) * bs]
+            h = chain[i] if len(token_ids) == bs else -1
+            block_id = h2b.get(h, -1)
+            if block_id != -1 and blocks[block_id].token_ids == token_ids:
+                cached += bs
+                block = blocks[block_id]
+                if block_id in used:
+                    block.ref_count += 1
+                else:                       # a free block whose contents are still what this prompt needs
+                    block.ref_count = 1
+                    del free[block_id]
+                    used.add(block_id)
+            else:
+                try:
+                    block_id = free.popitem(last=False)[0]
+                except KeyError:
+                    raise IndexError("KV block pool exhausted") from None
+                block = blocks[block_id]
+                old = block.hash
+                if old != -1 and h2b.get(old) == block_id:
+                    del h2b[old]
+                block.hash, block.token_ids, block.ref_count = h, token_ids, 1
+                used.add(block_id)
+                if h != -1:
+                    h2b[h] = block_id
+            table.append(block_id)
+        seq.num_cached_tokens += cached
 
     def deallocate(self, seq: Sequence) -> None:
         order = seq.block_table if self.reference_exact else reversed(seq.block_table)

@@ -69,6 +69,7 @@ def prepare_prefill(seqs: list[Sequence], block_size: int) -> StepMetadata:
     """
     ids, slots, pos = [], [], []
     q_lens, k_lens = [], []
+    in_block = np.arange(block_size, dtype=np.int64)
     for s in seqs:
         cached = s.num_cached_tokens
         ids.append(np.asarray(s.token_ids[cached:], dtype=np.int64))
@@ -77,11 +78,14 @@ def prepare_prefill(seqs: list[Sequence], block_size: int) -> StepMetadata:
         pos.append(np.arange(cached, s.num_tokens, dtype=np.int64))
         if not s.block_table:
             continue
+        # slots of blocks [num_cached_blocks, end of the table): whole blocks, the sequence's last one ragged
         first, last = s.num_cached_blocks, s.num_blocks - 1
-        for j in range(first, len(s.block_table)):
-            n = block_size if j != last else s.last_block_num_tokens
-            base = s.block_table[j] * block_size
-            slots.append(np.arange(base, base + n, dtype=np.int64))
+        bt = np.asarray(s.block_table[first:], dtype=np.int64)
+        if bt.size:
+            n = bt.size * block_size
+            if first + bt.size - 1 == last:
+                n -= block_size - s.last_block_num_tokens
+            slots.append((bt[:, None] * block_size + in_block).reshape(-1)[:n])
     cu_q = np.zeros(len(seqs) + 1, dtype=np.int32)
     cu_k = np.zeros(len(seqs) + 1, dtype=np.int32)
     np.cumsum(q_lens, out=cu_q[1:])

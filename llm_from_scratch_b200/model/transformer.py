@@ -311,31 +311,40 @@ class MLAAttention(nn.Module):
         self.rope = rope
         self.scale = (self.hd + self.dr) ** -0.5
         self.dtype = p.dtype
+        self.w_ukv = up.contiguous()         # [2*H*hd, r]: W_UK of all heads, then W_UV, for the prefill expansion
+        self.fused = True                    # False: the pre-attention stage as separate tensor ops
         self.latent_cache = torch.empty(0)   # [num_blocks, block_size, r + dr]; set by the runner
 
     def forward(self, x, ctx, positions, out=None):
         T, H, hd, r, dr = x.shape[0], self.H, self.hd, self.r, self.dr
         x = x.to(self.dtype)
-        qc = _vector_norm(F.linear(x, self.w_qd, self.b_qd), self.q_norm)
+        fused = self.fused and self.dtype == torch.bfloat16
+        qd = F.linear(x, self.w_qd, self.b_qd)
+        qc = ops.add_rmsnorm(qd, self.q_norm, torch.finfo(self.dtype).eps) if fused else _vector_norm(qd, self.q_norm)
         qf = F.linear(qc, self.w_qu, self.b_qu)
-        q_nope = qf[:, :self.d].view(T, H, hd)
-        q_rope = apply_rope(qf[:, self.d:].view(T, H, dr), positions, self.rope).to(self.dtype)
         kvp = F.linear(x, self.w_kv, self.b_kv)
-        c = _vector_norm(kvp[:, :r], self.kv_norm)
-        pe = apply_rope(kvp[:, r:].unsqueeze(1), positions, self.rope).squeeze(1).to(self.dtype)
-        rows = torch.cat([c, pe], dim=-1)                                   # [T, r + dr]
-        if self.latent_cache.numel():
-            ops.store_rows(rows, self.latent_cache, ctx.slot_mapping)
-        if ctx.is_prefill:
-            o = self._prefill(q_nope, q_rope, rows, ctx, out)
+        if fused:
+            # q assembly + RoPE, latent RMSNorm + RoPE and the cache write in one kernel
+            q, rows = ops.mla_prologue(qf, kvp, self.kv_norm, self.rope, positions, H, hd, dr, r,
+                                       self.latent_cache, ctx.slot_mapping)
         else:
-            q_abs = torch.einsum("thd,hdk->thk", q_nope, self.w_uk)          # absorb W_UK (MLA.py:153)
-            lat = ops.mla_decode(q_abs.contiguous(), q_rope.contiguous(), self.latent_cache, ctx.block_tables,
+            q_rope = apply_rope(qf[:, self.d:].view(T, H, dr), positions, self.rope).to(self.dtype)
+            q = torch.cat([qf[:, :self.d].view(T, H, hd), q_rope], dim=-1)
+            c = _vector_norm(kvp[:, :r], self.kv_norm)
+            pe = apply_rope(kvp[:, r:].unsqueeze(1), positions, self.rope).squeeze(1).to(self.dtype)
+            rows = torch.cat([c, pe], dim=-1)                               # [T, r + dr]
+            if self.latent_cache.numel():
+                ops.store_rows(rows, self.latent_cache, ctx.slot_mapping)
+        if ctx.is_prefill:
+            o = self._prefill(q, rows, ctx, out)
+        else:
+            q_abs = torch.einsum("thd,hdk->thk", q[..., :hd], self.w_uk)     # absorb W_UK (MLA.py:153)
+            lat = ops.mla_decode(q_abs.contiguous(), q[..., hd:].contiguous(), self.latent_cache, ctx.block_tables,
                                  ctx.context_lens, self.scale)
             o = torch.einsum("thk,hdk->thd", lat, self.w_uv)                 # absorb W_UV (MLA.py:178)
         return F.linear(o.reshape(T, H * hd), self.w_o, self.b_o)
 
-    def _prefill(self, q_nope, q_rope, rows, ctx, out=None):
+    def _prefill(self, q, rows, ctx, out=None):
         """Causal attention of the packed new tokens over their contexts.
 
         Prefill expands the latent rows once per step instead of absorbing the up-projections into
@@ -344,13 +353,19 @@ class MLAAttention(nn.Module):
         constant over keys and cancels in the softmax; b_v is absent from the reference's cache
         branch), at 320 instead of 1088 multiply-adds per (query, key, head).
         """
-        r, H, dr = self.r, self.H, self.dr
+        r, H, hd, dr = self.r, self.H, self.hd, self.dr
         if ctx.block_tables is not None:
             rows = self._gather_context_rows(ctx)
         c, pe = rows[:, :r], rows[:, r:]
-        k = torch.cat([torch.einsum("tk,hdk->thd", c, self.w_uk), pe.unsqueeze(1).expand(-1, H, dr)], dim=-1)
-        v = torch.einsum("tk,hdk->thd", c, self.w_uv).contiguous()
-        q = torch.cat([q_nope, q_rope], dim=-1)
+        Tk = rows.shape[0]
+        # one GEMM for both expansions: [Tk, r] x [r, 2*H*hd] -> K_nope of all heads, then V of all heads
+        kv = F.linear(c, self.w_ukv)
+        k_nope, v = kv[:, :H * hd].view(Tk, H, hd), kv[:, H * hd:].view(Tk, H, hd)
+        if rows.dtype == torch.bfloat16:
+            # the kernel reads the rotary part once per token instead of a copy per head
+            return ops.prefill_varlen_shared_tail(q, k_nope, pe, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
+                                                  ctx.max_seqlen_q, self.scale, out=out, plan=ctx.prefill_plan)
+        k = torch.cat([k_nope, pe.unsqueeze(1).expand(-1, H, dr)], dim=-1)
         return ops.prefill_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
                                   ctx.max_seqlen_k, self.scale, out=out, plan=ctx.prefill_plan)
 

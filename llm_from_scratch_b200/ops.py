@@ -211,6 +211,43 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
     return out
 
 
+def prefill_varlen_shared_tail(q: torch.Tensor, k_head: torch.Tensor, k_tail: torch.Tensor, v: torch.Tensor,
+                               cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int,
+                               scale: float, out: torch.Tensor | None = None,
+                               plan: "PrefillPlan | None" = None) -> torch.Tensor:
+    """``prefill_varlen`` over packed keys given in two parts: k_head [Tk, H, Dqk - tail] per head and
+    k_tail [Tk, tail], the last columns of every head's key (MLA's shared rotary part).  bf16.
+
+    q: [Tq, H, Dqk], v: [Tk, H, Dv]; token strides are free, heads contiguous.  Returns out [Tq, H, Dv].
+    """
+    dev = _cuda(q, k_head, k_tail, v, cu_seqlens_q, cu_seqlens_k, out)
+    Tq, H, Dqk = q.shape
+    Tk, tail = k_tail.shape
+    Dv = v.shape[2]
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32 \
+            or cu_seqlens_q.numel() != cu_seqlens_k.numel():
+        raise ValueError("cu_seqlens must be int32 tensors of the same length")
+    if k_head.shape != (Tk, H, Dqk - tail) or v.shape[:2] != (Tk, H):
+        raise ValueError("k_head must be [Tk, H, Dqk - tail] and v [Tk, H, Dv]")
+    if any(t.dtype != torch.bfloat16 for t in (q, k_head, k_tail, v)):
+        raise ValueError("prefill_varlen_shared_tail takes bf16 tensors")
+    if q.stride(2) != 1 or q.stride(1) != Dqk or k_head.stride(2) != 1 or k_head.stride(1) != Dqk - tail \
+            or v.stride(2) != 1 or v.stride(1) != Dv or k_tail.stride(1) != 1:
+        raise ValueError("heads must be contiguous")
+    if out is None:
+        out = torch.empty((Tq, H, Dv), dtype=q.dtype, device=q.device)
+    elif out.shape != (Tq, H, Dv) or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [Tq, H, Dv] tensor")
+    check(lib.b200_prefill_varlen_shared_tail(
+        q.data_ptr(), k_head.data_ptr(), k_tail.data_ptr(), v.data_ptr(), out.data_ptr(), q.stride(0),
+        k_head.stride(0), k_tail.stride(0), v.stride(0), cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(),
+        cu_seqlens_q.numel() - 1, int(max_seqlen_q), H, Dqk, tail, Dv, float(scale),
+        plan.buffer.data_ptr() if plan is not None else None, plan.tile_rows if plan is not None else 0,
+        plan.capacity if plan is not None else 0, _dt(q), status_word(dev).data_ptr(), _stream()),
+        "prefill_varlen_shared_tail")
+    return out
+
+
 class PrefillPlan:
     """Device-side tile list shared by all prefill attention calls of one step (``prefill_plan``)."""
 
@@ -332,6 +369,49 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torc
         "qk_norm_rope_store")
     v = qkv[:, wq + wk:].view(T, num_kv_heads, head_dim)
     return q, k, v
+
+
+def mla_prologue(q_up: torch.Tensor, kv_down: torch.Tensor, kv_norm_w: torch.Tensor, rope_table: torch.Tensor,
+                 positions: torch.Tensor, num_heads: int, head_dim: int, rope_dim: int, kv_lora_rank: int,
+                 latent_cache: torch.Tensor | None = None, slot_mapping: torch.Tensor | None = None):
+    """MLA stage between the projections and the attention: q = [q_nope | RoPE(q_rope)] per head and the
+    latent row [kv_norm(c) | RoPE(k_rope)], also scattered into the paged latent cache.
+
+    q_up: [T, H*head_dim + H*rope_dim]; kv_down: [T, kv_lora_rank + rope_dim]; bf16.
+    Returns (q [T, H, head_dim + rope_dim], rows [T, kv_lora_rank + rope_dim]).
+    """
+    dev = _cuda(q_up, kv_down, kv_norm_w, rope_table, positions, latent_cache, slot_mapping)
+    T = q_up.shape[0]
+    if q_up.dtype != torch.bfloat16 or kv_down.dtype != torch.bfloat16:
+        raise ValueError("mla_prologue takes bf16 projections")
+    if q_up.shape[1] != num_heads * (head_dim + rope_dim) or q_up.stride(1) != 1:
+        raise ValueError("q_up must be [T, H*(head_dim + rope_dim)] with contiguous rows")
+    if kv_down.shape != (T, kv_lora_rank + rope_dim) or kv_down.stride(1) != 1:
+        raise ValueError("kv_down must be [T, kv_lora_rank + rope_dim] with contiguous rows")
+    if positions.dtype != torch.int64 or positions.numel() != T or not positions.is_contiguous():
+        raise ValueError("positions must be a contiguous int64 [T] tensor")
+    if rope_table.dtype != torch.float32 or not rope_table.is_contiguous() or rope_table.dim() != 2:
+        raise ValueError("rope_table must be a contiguous fp32 [positions, width] tensor")
+    if kv_norm_w.dtype != torch.float32 or kv_norm_w.numel() != kv_lora_rank:
+        raise ValueError("kv_norm_w must be fp32 [kv_lora_rank]")
+    use_cache = latent_cache is not None and latent_cache.numel() > 0
+    if use_cache:
+        if latent_cache.dtype != torch.bfloat16 or latent_cache.shape[-1] != kv_lora_rank + rope_dim \
+                or not latent_cache.is_contiguous():
+            raise ValueError("latent_cache must be contiguous bf16 [..., kv_lora_rank + rope_dim]")
+        if slot_mapping is None or slot_mapping.dtype != torch.int64 or slot_mapping.numel() != T:
+            raise ValueError("slot_mapping must be int64 [T]")
+    q = torch.empty(T, num_heads, head_dim + rope_dim, dtype=q_up.dtype, device=q_up.device)
+    rows = torch.empty(T, kv_lora_rank + rope_dim, dtype=q_up.dtype, device=q_up.device)
+    check(lib.b200_mla_prologue(
+        q_up.data_ptr(), q_up.stride(0), kv_down.data_ptr(), kv_down.stride(0), kv_norm_w.data_ptr(),
+        rope_table.data_ptr(), rope_table.shape[1], rope_table.shape[0], positions.data_ptr(), q.data_ptr(),
+        rows.data_ptr(), latent_cache.data_ptr() if use_cache else None,
+        slot_mapping.data_ptr() if use_cache else None,
+        (latent_cache.numel() // (kv_lora_rank + rope_dim)) if use_cache else 0, T, num_heads, head_dim, rope_dim,
+        kv_lora_rank, float(torch.finfo(q_up.dtype).eps), _dt(q_up), status_word(dev).data_ptr(), _stream()),
+        "mla_prologue")
+    return q, rows
 
 
 MOE_ROUTE_MAX_EXPERTS, MOE_ROUTE_MAX_TOPK, MOE_ROUTE_MAX_TOKENS = 64, 8, 65536

@@ -532,6 +532,99 @@ def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype, Hq, Hkv, D):
     assert (kc.view(-1, Hkv, D).float().abs().sum(dim=(1, 2)) > 0).sum().item() == T - 1
 
 
+@pytest.mark.parametrize("H,hd,dr,r,width", [(16, 128, 64, 512, 128), (4, 64, 32, 128, 64), (3, 64, 64, 72, 64),
+                                             (16, 128, 64, 512, 64)])
+def test_mla_prologue_matches_oracle(H, hd, dr, r, width):
+    """q = [q_nope | RoPE(q_rope)] and the latent row [kv_norm(c) | RoPE(k_rope)] against the oracle's
+    RMSNorm and RoPE (model/attention/MLA.py:114-131), with the rope table sliced to rope_dim columns as
+    the reference slices it (a table wider than rope_dim yields cosines in the "sin" half), and the
+    scatter into the latent cache including a padded (-1) slot."""
+    ops, orc = _ops(), _oracle()
+    dtype = torch.bfloat16
+    T, bs, nb = 37, 16, 4
+    qf = _randn((T, H * (hd + dr)), 11, dtype)
+    kvp = _randn((T, r + dr), 12, dtype)
+    w = _randn((r,), 13, torch.float32)
+    table = orc.rope_table(10000.0, width, 96)
+    pos = torch.from_numpy(np.random.default_rng(2).integers(0, 96, size=T).astype(np.int64))
+    slots = torch.from_numpy(np.random.default_rng(3).permutation(nb * bs)[:T].astype(np.int64))
+    slots[5] = -1
+    eps = torch.finfo(dtype).eps
+    q_nope = qf[:, :H * hd].view(T, H, hd)
+    q_rope = orc.apply_rope(qf[:, H * hd:].view(T, H, dr).transpose(0, 1).float(), pos, table).transpose(0, 1)
+    want_q = torch.cat([q_nope, q_rope.to(dtype)], dim=-1)
+    cf = kvp[:, :r].float()
+    c = (cf * torch.rsqrt(cf.pow(2).mean(-1, keepdim=True) + eps) * w).to(dtype)
+    pe = orc.apply_rope(kvp[:, r:].float().unsqueeze(0), pos, table).squeeze(0).to(dtype)
+    want_rows = torch.cat([c, pe], dim=-1)
+
+    cache = torch.zeros(nb, bs, r + dr, dtype=dtype).cuda()
+    gq, grows = ops.mla_prologue(qf.cuda(), kvp.cuda(), w.cuda(), table.cuda(), pos.cuda(), H, hd, dr, r,
+                                 cache, slots.cuda())
+    ops.check_status()
+    assert torch.equal(gq[..., :hd].cpu(), q_nope)
+    tol = 4e-2                                            # one bf16 rounding step of values up to ~4
+    assert (gq.float().cpu() - want_q.float()).abs().max().item() <= tol
+    assert (grows.float().cpu() - want_rows.float()).abs().max().item() <= tol
+    # nearly every element rounds the same way as the tensor-op form
+    assert (gq.cpu() == want_q).float().mean().item() > 0.99
+    assert (grows.cpu() == want_rows).float().mean().item() > 0.99
+    flat = cache.view(-1, r + dr)
+    assert torch.equal(flat[slots[slots >= 0].cuda()].cpu(), grows.cpu()[slots >= 0])
+    assert (flat.float().abs().sum(dim=1) > 0).sum().item() == T - 1
+    # without a cache nothing is scattered and the rows are the same
+    gq2, grows2 = ops.mla_prologue(qf.cuda(), kvp.cuda(), w.cuda(), table.cuda(), pos.cuda(), H, hd, dr, r)
+    assert torch.equal(gq2, gq) and torch.equal(grows2, grows)
+
+
+def test_mla_prologue_rejects_bad_arguments():
+    ops = _ops()
+    dtype = torch.bfloat16
+    qf, kvp = torch.zeros(4, 4 * 96, dtype=dtype).cuda(), torch.zeros(4, 160, dtype=dtype).cuda()
+    w, table = torch.ones(128).cuda(), torch.zeros(8, 64).cuda()
+    pos = torch.zeros(4, dtype=torch.int64).cuda()
+    with pytest.raises(ValueError):
+        ops.mla_prologue(qf.float(), kvp.float(), w, table, pos, 4, 64, 32, 128)
+    with pytest.raises(ValueError):
+        ops.mla_prologue(qf, kvp[:, :100], w, table, pos, 4, 64, 32, 128)
+    with pytest.raises(RuntimeError):                      # rope_dim 24: 3 chunks, not a power of two
+        ops.mla_prologue(torch.zeros(4, 4 * 88, dtype=dtype).cuda(), torch.zeros(4, 152, dtype=dtype).cuda(), w,
+                         table, pos, 4, 64, 24, 128)
+    # a position outside the table is clamped and reported
+    pos[2] = 99
+    ops.mla_prologue(qf, kvp, w, table, pos, 4, 64, 32, 128)
+    with pytest.raises(RuntimeError):
+        ops.check_status()
+
+
+@pytest.mark.parametrize("with_plan", [False, True])
+def test_prefill_shared_tail_equals_expanded_keys(with_plan):
+    """Keys in two parts (per-head columns + a rotary tail shared by all heads, MLA.py:131) give the
+    same output, bit for bit, as the same kernel run on keys with the tail copied into every head;
+    the parts are strided views of wider buffers, as the model passes them."""
+    ops = _ops()
+    H, hd, dr = 4, 128, 64
+    lens_q, lens_k = [70, 1, 200, 33], [70, 1, 260, 33]
+    cu_q = torch.tensor(np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)).cuda()
+    cu_k = torch.tensor(np.concatenate([[0], np.cumsum(lens_k)]).astype(np.int32)).cuda()
+    Tq, Tk = sum(lens_q), sum(lens_k)
+    q = _randn((Tq, H, hd + dr), 21, torch.bfloat16).cuda()
+    kv = _randn((Tk, 2 * H * hd), 22, torch.bfloat16).cuda()
+    rows = _randn((Tk, 512 + dr), 23, torch.bfloat16).cuda()
+    k_head, v = kv[:, :H * hd].view(Tk, H, hd), kv[:, H * hd:].view(Tk, H, hd)
+    tail = rows[:, 512:]
+    k_full = torch.cat([k_head, tail.unsqueeze(1).expand(-1, H, dr)], dim=-1)
+    plan = None
+    if with_plan:
+        rows_per_tile = ops.prefill_tile_rows(H, H, hd + dr, hd, torch.bfloat16)
+        plan = ops.prefill_plan(cu_q, Tq, max(lens_q), rows_per_tile)
+    want = ops.prefill_varlen(q, k_full, v.contiguous(), cu_q, cu_k, max(lens_q), max(lens_k), 192 ** -0.5, plan=plan)
+    got = ops.prefill_varlen_shared_tail(q, k_head, tail, v, cu_q, cu_k, max(lens_q), 192 ** -0.5, plan=plan)
+    ops.check_status()
+    assert torch.equal(got, want)
+    assert got.float().abs().sum().item() > 0
+
+
 def _moe_rows(T, K, E, seed):
     """A consistent grouping: every token picks K distinct experts; rows sorted by (expert, token)."""
     rng = np.random.default_rng(seed)
