@@ -176,8 +176,8 @@ int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
  *   k_tail [total_k, tail_dim]                   last tail_dim columns of every head's key
  *   q      [total_q, H, head_dim_qk], v [total_k, H, head_dim_v], out [total_q, H, head_dim_v]
  * so the rotary part is never copied into every head.  Keys/values are packed (no paged prefix).
- * bf16, (head_dim_qk, head_dim_v) = (192, 128) or equal dims of 32/64/128, all parts 16-byte aligned
- * with tail_dim a multiple of 8; anything else returns B200_ERR_UNSUPPORTED.  plan: as above, for the
+ * bf16, (head_dim_qk, tail_dim, head_dim_v) = (192, 64, 128), all parts 16-byte aligned; anything else
+ * returns B200_ERR_UNSUPPORTED (the caller then expands the keys and uses b200_prefill_varlen).  plan: as above, for the
  * tile_rows of b200_prefill_tile_rows(head_dim_qk, head_dim_v, H, H, dtype). */
 int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const void* k_tail, const void* v,
                                     void* out, int64_t q_token_stride, int64_t k_head_token_stride,

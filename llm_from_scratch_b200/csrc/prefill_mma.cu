@@ -30,7 +30,6 @@ struct MmaArgs {
   // columns from `k_tail`, one row per token shared by every head (MLA's rotary key part)
   const __nv_bfloat16* k_tail;
   int64_t k_tail_stride;
-  int tail;
   const int32_t* cu_q;
   const int32_t* cu_k;
   int Hq, Hkv, ntiles_max;
@@ -52,7 +51,7 @@ __device__ __forceinline__ int swz(int c, int row) {
   return c ^ ((row >> 1) & (CPR - 1));
 }
 
-template <int DQK, int DV, bool PAGED>
+template <int DQK, int DV, bool PAGED, int TAIL = 0>
 __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int KQ = DQK / 16;   // k-steps of S
@@ -94,9 +93,8 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
       }
       return a.kc + ((static_cast<int64_t>(id) * a.bs + n % a.bs) * a.Hkv + kvh) * DQK;
     }
-    return a.k + static_cast<int64_t>(k0 + n) * a.k_stride + static_cast<int64_t>(kvh) * (DQK - a.tail);
+    return a.k + static_cast<int64_t>(k0 + n) * a.k_stride + static_cast<int64_t>(kvh) * (DQK - TAIL);
   };
-  const int head_chunks = (DQK - a.tail) / 8;   // 16-byte chunks of a key row that come from `k`
   auto v_row = [&](int n) -> const __nv_bfloat16* {
     if (PAGED) {
       const int id = __ldg(a.bt + static_cast<int64_t>(seq) * a.bt_stride + n / a.bs);
@@ -112,15 +110,34 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
     const int n0 = j * BN;
     const int valid = min(BN, kmax - n0);
     constexpr int CPRK = DQK / 8, CPRV = DV / 8;
+    if constexpr (TAIL == 0) {
 #pragma unroll
-    for (int i = 0; i < BN * CPRK / kThreads; ++i) {
-      const int idx = threadIdx.x + i * kThreads;
-      const int r = idx / CPRK, c = idx % CPRK;
-      const __nv_bfloat16* src = r < valid ? k_row(n0 + r) : nullptr;
-      if (!PAGED && src && c >= head_chunks)
-        src = a.k_tail + static_cast<int64_t>(k0 + n0 + r) * a.k_tail_stride - head_chunks * 8;
-      cp_async16(sK + stage * KB + r * (DQK * 2) + swz<DQK>(c, r) * 16,
-                 src ? src + c * 8 : dummy, src ? 16 : 0);
+      for (int i = 0; i < BN * CPRK / kThreads; ++i) {
+        const int idx = threadIdx.x + i * kThreads;
+        const int r = idx / CPRK, c = idx % CPRK;
+        const __nv_bfloat16* src = r < valid ? k_row(n0 + r) : nullptr;
+        cp_async16(sK + stage * KB + r * (DQK * 2) + swz<DQK>(c, r) * 16,
+                   src ? src + c * 8 : dummy, src ? 16 : 0);
+      }
+    } else {
+      // per-head columns, then the tail columns every head shares: two loops with power-of-two row widths
+      constexpr int CH = (DQK - TAIL) / 8, CT = TAIL / 8;
+#pragma unroll
+      for (int i = 0; i < BN * CH / kThreads; ++i) {
+        const int idx = threadIdx.x + i * kThreads;
+        const int r = idx / CH, c = idx % CH;
+        const __nv_bfloat16* src = r < valid ? k_row(n0 + r) : nullptr;
+        cp_async16(sK + stage * KB + r * (DQK * 2) + swz<DQK>(c, r) * 16,
+                   src ? src + c * 8 : dummy, src ? 16 : 0);
+      }
+#pragma unroll
+      for (int i = 0; i < BN * CT / kThreads; ++i) {
+        const int idx = threadIdx.x + i * kThreads;
+        const int r = idx / CT, c = idx % CT;
+        const bool ok = r < valid;
+        cp_async16(sK + stage * KB + r * (DQK * 2) + swz<DQK>(CH + c, r) * 16,
+                   ok ? a.k_tail + static_cast<int64_t>(k0 + n0 + r) * a.k_tail_stride + c * 8 : dummy, ok ? 16 : 0);
+      }
     }
 #pragma unroll
     for (int i = 0; i < BN * CPRV / kThreads; ++i) {
@@ -289,13 +306,13 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_mma_kernel(const MmaArgs 
   }
 }
 
-template <int DQK, int DV>
+template <int DQK, int DV, int TAIL = 0>
 int launch(const MmaArgs& a, int num_seqs, int plan_capacity, bool paged, cudaStream_t s) {
   constexpr size_t smem = size_t(BM) * DQK * 2 + 2 * size_t(BN) * DQK * 2 + 2 * size_t(BN) * DV * 2;
   static bool configured[64][2] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = paged ? prefill_mma_kernel<DQK, DV, true> : prefill_mma_kernel<DQK, DV, false>;
+  auto kern = paged ? prefill_mma_kernel<DQK, DV, true, 0> : prefill_mma_kernel<DQK, DV, false, TAIL>;
   if (dev >= 0 && dev < 64 && !configured[dev][paged]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
@@ -342,7 +359,6 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
   a.v_stride = v_stride;
   a.k_tail = static_cast<const __nv_bfloat16*>(k_tail);
   a.k_tail_stride = k_tail_stride;
-  a.tail = tail;
   a.cu_q = cu_q;
   a.cu_k = cu_k;
   a.Hq = Hq;
@@ -357,6 +373,10 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
   a.bs = bs;
   a.num_blocks = num_blocks;
   a.status = status;
+  if (tail > 0) {   // compiled for MLA's split: 128 per-head columns + 64 shared
+    if (Dqk != 192 || tail != 64) return B200_ERR_UNSUPPORTED;
+    return launch<192, 128, 64>(a, num_seqs, plan_capacity, false, s);
+  }
   if (Dqk == 192) return launch<192, 128>(a, num_seqs, plan_capacity, paged, s);
   if (Dqk == 128) return launch<128, 128>(a, num_seqs, plan_capacity, paged, s);
   if (Dqk == 64) return launch<64, 64>(a, num_seqs, plan_capacity, paged, s);

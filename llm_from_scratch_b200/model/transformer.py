@@ -361,7 +361,7 @@ class MLAAttention(nn.Module):
         # one GEMM for both expansions: [Tk, r] x [r, 2*H*hd] -> K_nope of all heads, then V of all heads
         kv = F.linear(c, self.w_ukv)
         k_nope, v = kv[:, :H * hd].view(Tk, H, hd), kv[:, H * hd:].view(Tk, H, hd)
-        if rows.dtype == torch.bfloat16:
+        if rows.dtype == torch.bfloat16 and (hd, dr) == (128, 64):
             # the kernel reads the rotary part once per token instead of a copy per head
             return ops.prefill_varlen_shared_tail(q, k_nope, pe, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                                   ctx.max_seqlen_q, self.scale, out=out, plan=ctx.prefill_plan)
