@@ -324,9 +324,14 @@ int b200_moe_combine(const void* expert_out, const void* bias, const int32_t* ro
  * dense_rows > 0: the last dense_rows of the num_rows rows are not grouped: they all use weight set
  *   number num_experts (w and bias then hold num_experts + 1 sets) — a shared expert applied to every token
  *   (moe.py:272-273) computed by the same launch, in chunks that cost a CTA what an expert's rows cost.
+ * mode | B200_MOE_GEMM_EARLY_LAUNCH: the launch is a programmatic dependent of the kernel before it in
+ *   the stream: the prologue and the first ring of weight tiles overlap that kernel's tail, and only the
+ *   reads of x wait for it.  The caller asserts that w, bias and expert_offsets were complete before
+ *   that kernel started (they come from two or more launches back, as in route -> gather -> up -> down).
  * Requires k_dim % 8 == 0 and 16-byte aligned x, w (B200_ERR_ALIGN).  A wait that runs out inside
  * the kernel sets *status to B200_ERR_TIMEOUT.
  * ------------------------------------------------------------------------------------------- */
+#define B200_MOE_GEMM_EARLY_LAUNCH 0x100
 int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* out,
                           const int32_t* expert_offsets, int64_t num_rows, int32_t num_experts,
                           int32_t dense_rows, int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype,

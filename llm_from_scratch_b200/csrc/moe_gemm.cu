@@ -356,7 +356,7 @@ bool make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int box
 }
 
 template <int NPASS, int STAGES>
-int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3 grid, cudaStream_t s) {
+int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3 grid, bool early, cudaStream_t s) {
   using L = Layout<NPASS, STAGES>;
   static bool configured[64] = {};
   int dev = 0;
@@ -368,9 +368,9 @@ int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3
       return B200_ERR_LAUNCH;
     configured[dev] = true;
   }
-  // mode 0 (the down-projection) follows mode 1 in the stream and only its token rows depend on it:
-  // launched as a programmatic dependent, its prologue and first weight tiles overlap the tail of the
-  // kernel before it (which may be any kernel: without an early trigger there this is an ordinary launch)
+  // Only the token rows depend on the kernel before this one in the stream when the caller says so
+  // (`early`): launched as a programmatic dependent, the prologue and first weight tiles overlap the tail of
+  // that kernel (which may be any kernel: one that never triggers releases its dependents as its CTAs exit)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
@@ -380,7 +380,7 @@ int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = a.mode == 0 ? 1 : 0;
+  cfg.numAttrs = early ? 1 : 0;
   if (cudaLaunchKernelEx(&cfg, moe_gemm_kernel<NPASS, STAGES>, a, tw, tx) != cudaSuccess) {
     cudaGetLastError();
     return B200_ERR_LAUNCH;
@@ -396,6 +396,8 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* b
                                      int32_t dense_rows, int32_t n_out, int32_t k_dim, int32_t mode,
                                      int32_t dtype, int32_t* status, void* stream) {
   using namespace b200;
+  const bool early = (mode & B200_MOE_GEMM_EARLY_LAUNCH) != 0;
+  mode &= ~B200_MOE_GEMM_EARLY_LAUNCH;
   if (num_rows < 0 || num_experts <= 0 || n_out <= 0 || k_dim <= 0 || (mode != 0 && mode != 1) ||
       dense_rows < 0 || dense_rows > num_rows)
     return B200_ERR_ARG;
@@ -426,8 +428,8 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* b
   const int64_t grouped = num_rows - dense_rows;
   if (grouped <= 64LL * num_experts) {
     const dim3 grid(tiles, num_experts + (dense_rows + 63) / 64);
-    return launch<64, 4>(a, tw, tx, grid, s);
+    return launch<64, 4>(a, tw, tx, grid, early, s);
   }
   const dim3 grid(tiles, num_experts + (dense_rows + 255) / 256);
-  return launch<256, 4>(a, tw, tx, grid, s);
+  return launch<256, 4>(a, tw, tx, grid, early, s);
 }

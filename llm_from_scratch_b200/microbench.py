@@ -120,7 +120,8 @@ def moe_experts(steps: int = 20, warmup: int = 3, tokens: int = 256, layers: int
 
     def all_layers():
         for i in range(layers):
-            ops.moe_grouped_gemm(ops.moe_grouped_gemm(xs, w13[i], offs, b13, swiglu=True), w2[i], offs)
+            ops.moe_grouped_gemm(ops.moe_grouped_gemm(xs, w13[i], offs, b13, swiglu=True, early_launch=True), w2[i], offs,
+                                 early_launch=True)
 
     all_layers()
     torch.cuda.synchronize()

@@ -200,15 +200,16 @@ class MoE(nn.Module):
             tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K,
                                                        identity_tail=True)
             xs = x.index_select(0, tok)                              # [T*K routed rows | T shared rows]
-            act = ops.moe_grouped_gemm(xs, self.w13_all, offs, self.b13_all, swiglu=True, dense_rows=T)
-            y = ops.moe_grouped_gemm(act, self.w2_all, offs, self.b2_all, dense_rows=T)
+            # early_launch: offs and the weights are older than the gather / the up-projection before each GEMM
+            act = ops.moe_grouped_gemm(xs, self.w13_all, offs, self.b13_all, swiglu=True, dense_rows=T, early_launch=True)
+            y = ops.moe_grouped_gemm(act, self.w2_all, offs, self.b2_all, dense_rows=T, early_launch=True)
             R = T * self.K
             return ops.moe_combine(y[:R], None, experts, w, inv, y[R:])
         tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K)
         xs = x.index_select(0, tok)
         if small:
-            act = ops.moe_grouped_gemm(xs, self.w13, offs, self.b13, swiglu=True)
-            y = ops.moe_grouped_gemm(act, self.w2, offs)
+            act = ops.moe_grouped_gemm(xs, self.w13, offs, self.b13, swiglu=True, early_launch=True)
+            y = ops.moe_grouped_gemm(act, self.w2, offs, early_launch=True)
         else:
             act = ops.swiglu(torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs), self.b13, experts)
             y = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs)

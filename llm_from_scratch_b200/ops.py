@@ -415,6 +415,7 @@ def mla_prologue(q_up: torch.Tensor, kv_down: torch.Tensor, kv_norm_w: torch.Ten
 
 
 MOE_ROUTE_MAX_EXPERTS, MOE_ROUTE_MAX_TOPK, MOE_ROUTE_MAX_TOKENS = 64, 8, 65536
+MOE_GEMM_EARLY_LAUNCH = 0x100   # B200_MOE_GEMM_EARLY_LAUNCH
 
 
 def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int, identity_tail: bool = False):
@@ -459,7 +460,8 @@ def swiglu(h: torch.Tensor, bias: torch.Tensor | None = None, row_expert: torch.
 
 
 def moe_grouped_gemm(x: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
-                     bias: torch.Tensor | None = None, swiglu: bool = False, dense_rows: int = 0) -> torch.Tensor:
+                     bias: torch.Tensor | None = None, swiglu: bool = False, dense_rows: int = 0,
+                     early_launch: bool = False) -> torch.Tensor:
     """Rows of x [R, k] grouped by expert (expert_offsets int32 [E], exclusive ends) times the expert's
     weight: w [E, n, k] -> [R, n]; with ``swiglu`` w is [E, 2*d_ff, k] = [w1 | w3], bias [E, 2*d_ff],
     and the result is silu(x w1^T + b1) * (x w3^T + b3) [R, d_ff].  bf16, tcgen05 tensor cores.
@@ -483,7 +485,7 @@ def moe_grouped_gemm(x: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Ten
     out = torch.empty(R, n_out, dtype=torch.bfloat16, device=x.device)
     check(lib.b200_moe_grouped_gemm(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
                                     out.data_ptr(), expert_offsets.data_ptr(), R, E, int(dense_rows), n_out, k,
-                                    1 if swiglu else 0,
+                                    (1 if swiglu else 0) | (MOE_GEMM_EARLY_LAUNCH if early_launch else 0),
                                     _dt(x), status_word(x.device).data_ptr(), _stream()), "moe_grouped_gemm")
     return out
 
