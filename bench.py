@@ -147,6 +147,8 @@ def main():
                     help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
                          "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
     ap.add_argument("--rate", type=float, default=0.0, help="engine workload: Poisson arrival rate (req/s); 0 = offline")
+    ap.add_argument("--decode-window", type=int, default=1,
+                    help="engine workload: decode steps per scheduling decision (1 = the reference's loop)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="sequences per GPU; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()
@@ -160,6 +162,8 @@ def main():
         kw = dict(steps=args.steps, warmup=args.warmup)
         if args.workload == "engine" and args.rate > 0:
             kw["rate"] = args.rate
+        if args.workload == "engine" and args.decode_window > 1:
+            kw["decode_window"] = args.decode_window
         if args.batch != BATCH:   # profiling cases: fewer sequences / tokens
             key = {"mla_decode": "batch", "engine": "batch", "prefill": "total", "store": "tokens",
                    "moe_experts": "tokens", "engine_mla": "batch"}[args.workload]

@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 6
+#define B200_ABI_VERSION 7
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -336,6 +336,21 @@ int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* 
                           const int32_t* expert_offsets, int64_t num_rows, int32_t num_experts,
                           int32_t dense_rows, int32_t n_out, int32_t k_dim, int32_t mode, int32_t dtype,
                           int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode metadata of the next step, computed on the device from the step that just ran, so that several
+ * decode steps can be launched back to back (host counterpart: ModelRunner.prepare_decode,
+ * engine/model_runner.py:253-278).  For every row i < num_seqs:
+ *   input_ids[i] = sampled[i];  context_lens[i] += 1;
+ *   slot_mapping[i] = block_tables[i, (len-1)/block_size] * block_size + (len-1) % block_size  (len = new length)
+ *   history[i] = sampled[i] when history != NULL (the host reads all steps' tokens at the end).
+ * block_tables int32 [num_seqs, bt_stride] must already list the block the new token falls into; a table
+ * that does not sets the slot to -1 and reports B200_ERR_BOUNDS in *status.
+ * ------------------------------------------------------------------------------------------- */
+int b200_decode_advance(const int64_t* sampled, int64_t* input_ids, int64_t* context_lens,
+                        int64_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride,
+                        int32_t block_size, int64_t num_blocks, int32_t num_seqs, int64_t* history,
+                        int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Token sampling (Sampler.forward, utils/sampler.py:35-52; greedy argmax of generate.py:62), one launch.

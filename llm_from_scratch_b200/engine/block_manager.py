@@ -210,3 +210,22 @@ class BlockManager:
             table.append(self._allocate_block(self._oldest_free()).block_id)
         else:
             assert last.block_id in self.used_block_ids and last.hash == -1
+
+    # ------------------------------------------------------------------ several decode steps per schedule
+    def open_block(self, seq: Sequence) -> None:
+        """Opens the next block of ``seq`` ahead of time: what ``append`` does at ``len % block_size == 1``,
+        for a length the sequence reaches inside a window of decode steps (its tokens are not known yet,
+        so the block before it is sealed afterwards, by ``seal_block``)."""
+        seq.block_table.append(self._allocate_block(self._oldest_free()).block_id)
+
+    def seal_block(self, seq: Sequence, index: int) -> None:
+        """Gives block ``index`` of ``seq``, now full, its chained hash: what ``append`` does at
+        ``len % block_size == 0``, for a length passed inside a window of decode steps."""
+        table, bs = seq.block_table, self.block_size
+        block = self.blocks[table[index]]
+        prefix = -1 if index == 0 else self.blocks[table[index - 1]].hash
+        token_ids = seq.token_ids[index * bs:(index + 1) * bs]
+        h = self.compute_hash(token_ids, prefix)
+        block.update(h, token_ids)
+        self.hash_to_block_id[h] = block.block_id
+

@@ -31,6 +31,10 @@ class LLMEngine:
             block_size=block_size,
             eos=_cfg(config, "eos", default=50256),
         )
+        # decode steps the engine may run per scheduling decision (1 = the reference's step-by-step loop);
+        # larger values keep the GPU busy while the host schedules, at the price of admitting waiting
+        # requests and retiring finished ones up to decode_window - 1 steps later
+        self.decode_window = int(_cfg(config, "decode_window", default=1))
         self.tokenizer = tokenizer
         self.verbose = verbose
         self.stats = dict(prefill_tokens=0, decode_tokens=0, prefill_time=0.0, decode_time=0.0, steps=0)
@@ -63,15 +67,30 @@ class LLMEngine:
         self.timing["schedule_s"] += t1 - t0
         if not seqs:
             return [], 0, is_prefill
-        token_ids = self.model_runner.run(seqs, is_prefill)
-        t2 = time.perf_counter()
-        kind = "prefill" if is_prefill else "decode"
-        self.timing[f"run_{kind}_s"] += t2 - t1
-        self.timing[f"{kind}_steps"] += 1
-        self.scheduler.postprocess(seqs, token_ids)
+        runner = self.model_runner
+        window = 1
+        if not is_prefill and self.decode_window > 1 and getattr(runner, "can_run_window", None) \
+                and runner.can_run_window(seqs):
+            window = self.scheduler.plan_decode_window(seqs, self.decode_window, runner.max_model_length)
+            t1 = time.perf_counter()
+            self.timing["schedule_s"] += t1 - t0
+        if window > 1:
+            # several decode steps back to back: each step's sampled tokens feed the next on the device
+            steps = runner.run_window(seqs, window)
+            t2 = time.perf_counter()
+            self.timing["run_decode_s"] += t2 - t1
+            self.timing["decode_steps"] += window
+            processed = self.scheduler.postprocess_window(seqs, steps)
+        else:
+            token_ids = runner.run(seqs, is_prefill)
+            t2 = time.perf_counter()
+            kind = "prefill" if is_prefill else "decode"
+            self.timing[f"run_{kind}_s"] += t2 - t1
+            self.timing[f"{kind}_steps"] += 1
+            self.scheduler.postprocess(seqs, token_ids)
+            processed = sum(len(s) for s in seqs) if is_prefill else len(seqs)
         self.timing["postprocess_s"] += time.perf_counter() - t2
         outputs = [(s.seq_id, s.completion_token_ids) for s in seqs if s.is_finished]
-        processed = sum(len(s) for s in seqs) if is_prefill else len(seqs)
         return outputs, processed, is_prefill
 
     def is_finished(self) -> bool:

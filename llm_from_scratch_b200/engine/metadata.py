@@ -188,4 +188,5 @@ class DecodeBatchBuilder:
         out_tables[:n, :width] = self.tables[rows, :width]
         out_ids[:n] = [s.last_token for s in seqs]
         out_lens[:n] = lens
-        out_slots[:n] = self.tables[rows, nblk - 1].astype(np.int64) * bs + (lens - 1) % bs
+        # the block the new token falls into: the last one, unless blocks were opened ahead for later steps
+        out_slots[:n] = self.tables[rows, (lens - 1) // bs].astype(np.int64) * bs + (lens - 1) % bs

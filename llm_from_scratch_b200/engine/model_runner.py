@@ -224,7 +224,7 @@ class ModelRunner:
         return token_ids
 
     @torch.inference_mode()
-    def _replay_decode(self, seqs: list[Sequence]) -> torch.Tensor:
+    def _replay_decode(self, seqs: list[Sequence], replay: bool = True) -> torch.Tensor:
         """Decode step from a captured graph.  The graph's inputs live in one device buffer mirrored by
         one pinned host buffer: the step's metadata is written straight into the host mirror (padding
         rows: slot -1, context 0) and shipped with a single copy; nothing else runs before the replay."""
@@ -238,8 +238,36 @@ class ModelRunner:
         self.graph_dev[:nbytes].copy_(self.graph_host[:nbytes], non_blocking=True)
         set_context(False, slot_mapping=v["slot_mapping"][:n], context_lens=v["context_lens"][:n],
                     block_tables=v["block_tables"][:n])
-        self.graphs[bucket].replay()
+        if replay:
+            self.graphs[bucket].replay()
         return v["logits"][:n]
+
+    def can_run_window(self, seqs: list[Sequence]) -> bool:
+        """Whether ``run_window`` can serve this decode batch: captured graphs, all rows greedy."""
+        return bool(self.graphs) and not self.enforce_eager and len(seqs) <= max(self.graphs) \
+            and not any(s.temperature for s in seqs)
+
+    @torch.inference_mode()
+    def run_window(self, seqs: list[Sequence], steps: int) -> list[list[int]]:
+        """``steps`` greedy decode steps back to back from the captured graph.  Between two replays a
+        small kernel turns the sampled tokens into the next step's inputs (input id, context length, slot
+        from the block table, which already lists the blocks opened for the window) and records them; the
+        host reads all tokens once at the end.  Returns tokens[step][sequence]."""
+        n = len(seqs)
+        v = self.graph_vars
+        self._replay_decode(seqs, replay=False)
+        bucket = next(b for b in sorted(self.graphs) if b >= n)
+        graph, hist = self.graphs[bucket], v["history"]
+        for j in range(steps):
+            graph.replay()
+            if j + 1 < steps:
+                ops.decode_advance(v["greedy"][:n], v["input_ids"], v["context_lens"], v["slot_mapping"],
+                                   v["block_tables"], self.block_size, self.num_kv_blocks, hist[j])
+            else:
+                hist[j, :n].copy_(v["greedy"][:n])
+        tokens = hist[:steps, :n].tolist()
+        reset_context()
+        return tokens
 
     @torch.inference_mode()
     def run_logits(self, seqs: list[Sequence], is_prefill: bool) -> torch.Tensor:
@@ -366,6 +394,7 @@ class ModelRunner:
         # the graph also holds the lm_head GEMM and the greedy argmax, so a greedy step launches nothing else
         v["logits"] = torch.zeros(max_bs, self.model_config.vocab_size, dtype=self.dtype, device=dev)
         v["greedy"] = torch.zeros(max_bs, dtype=torch.int64, device=dev)
+        v["history"] = torch.zeros(self.block_size, max_bs, dtype=torch.int64, device=dev)   # run_window: tokens per step
         buckets = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
         if max_bs not in buckets:
             buckets.append(max_bs)

@@ -119,6 +119,65 @@ class Scheduler:
             self.running.extendleft(reversed(batch))
         return batch
 
+    # ------------------------------------------------------------------ several decode steps per schedule
+    def plan_decode_window(self, seqs: list[Sequence], max_steps: int, max_positions: int) -> int:
+        """How many decode steps the batch ``schedule()`` just returned may run back to back without the
+        host (the sampled token of one step is the input of the next on the device), at most
+        ``max_steps``; opens the blocks those steps write into.  The window ends where the longest-lived
+        sequence stops, never passes ``max_positions`` tokens, and is 1 when the pool cannot cover the
+        blocks to open.  Sequences that stop inside the window still occupy their row to its end (their
+        extra tokens are dropped by ``postprocess_window``), and waiting requests are admitted after it."""
+        bm = self.block_manager
+        bs = bm.block_size
+        if max_steps <= 1 or self.reference_exact:
+            return 1
+        k, longest = min(max_steps, bs), 0
+        for s in seqs:
+            n = s.num_tokens
+            left = s.max_tokens - 1 - (n - s.num_prompt_tokens)        # appends until the stop rule fires
+            if s.max_model_length is not None and s.max_model_length - n < left:
+                left = s.max_model_length - n
+            if left > longest:
+                longest = left
+            if max_positions - n + 1 < k:
+                k = max_positions - n + 1
+        k = min(k, longest)
+        if k <= 1:
+            return 1
+        # lengths n+1 .. n+k-1 that start a block (n itself was handled by schedule())
+        opening = [s for s in seqs if 1 <= (1 - s.num_tokens) % bs <= k - 1]
+        if len(opening) > bm.num_free_blocks:
+            return 1
+        for s in opening:
+            bm.open_block(s)
+        return k
+
+    def postprocess_window(self, seqs: list[Sequence], steps: list[list[int]]) -> int:
+        """``postprocess`` for a window of decode steps: ``steps[j][i]`` is the token step j sampled for
+        ``seqs[i]``.  Tokens after a sequence's stop are dropped; blocks that filled inside the window
+        get their hash now.  Returns the number of tokens kept."""
+        eos, bm = self.eos, self.block_manager
+        bs, last = bm.block_size, len(steps) - 1
+        kept = 0
+        for i, seq in enumerate(seqs):
+            for j, row in enumerate(steps):
+                token_id = row[i]
+                seq.token_ids.append(token_id)
+                seq.last_token = token_id
+                n = seq.num_tokens = seq.num_tokens + 1
+                kept += 1
+                hit_eos = token_id == eos and not seq.ignore_eos
+                hit_max_tokens = 1 + n - seq.num_prompt_tokens >= seq.max_tokens
+                hit_max_length = seq.max_model_length is not None and n >= seq.max_model_length
+                if hit_eos or hit_max_tokens or hit_max_length:
+                    seq.status = SequenceStatus.FINISHED
+                    bm.deallocate(seq)
+                    self.running.remove(seq)
+                    break
+                if j < last and n % bs == 0:
+                    bm.seal_block(seq, n // bs - 1)
+        return kept
+
     def preempt(self, seq: Sequence) -> None:
         self.block_manager.deallocate(seq)
         seq.status = SequenceStatus.WAITING

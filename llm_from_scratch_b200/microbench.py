@@ -142,7 +142,7 @@ C3_MODEL = dict(vocab_size=32000, context_length=2048, d_model=1024, num_layers=
 
 
 def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None = None,
-           pool_blocks: int = 110000) -> dict:
+           pool_blocks: int = 110000, decode_window: int = 1) -> dict:
     """End-to-end continuous batching, GQA+MoE decoder (d_model 1024, 16 layers, 16/4 heads, head_dim 64,
     16 experts top-2 + shared, d_ff 704, vocab 32000), bf16, random init (seed 0): ``batch`` requests,
     prompts uniform [64,1024], outputs geometric(mean 256) capped at 1024, max 256 sequences and 8192
@@ -151,7 +151,8 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
     2048 requests, so no request is preempted and re-prefilled; the scheduler admits waiting requests
     before it decodes, whatever the number already running, and fills any smaller pool).
     Under torchrun every rank is an independent replica serving requests rank, rank + N, ...; the
-    aggregate is tokens of all replicas / the slowest replica's wall time.  ``steps``/``warmup`` unused."""
+    aggregate is tokens of all replicas / the slowest replica's wall time.  ``steps``/``warmup`` unused.
+    ``decode_window`` > 1: that many decode steps per scheduling decision (the engine's ``decode_window``)."""
     import itertools
     import os
     import time
@@ -174,7 +175,7 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
         Sequence.counter = itertools.count()
         cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
                    max_num_batched_tokens=8192, max_cached_blocks=pool_blocks, eos=-1, device=f"cuda:{local_rank}",
-                   max_model_length=2048, seed=0)
+                   max_model_length=2048, seed=0, decode_window=decode_window)
         t0 = time.perf_counter()
         built["engine"] = LLMEngine(cfg)
         built["build_s"] = time.perf_counter() - t0
@@ -206,7 +207,8 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
                 replicas=world, requests=batch, generated_tokens=gen, prompt_tokens=prompt_tokens, wall_s=wall,
                 replica_wall_s=[r.wall_s for r in reports], steps=[r.steps for r in reports],
                 output_tokens_per_s=gen / wall, total_tokens_per_s=(gen + prompt_tokens) / wall,
-                engine_build_s=built["build_s"], cuda_graphs=graphs, kv_pool_blocks=pool_blocks, rank0_timing=timing)
+                engine_build_s=built["build_s"], cuda_graphs=graphs, kv_pool_blocks=pool_blocks,
+                decode_window=decode_window, rank0_timing=timing)
 
 
 C4_MODEL = dict(vocab_size=32000, context_length=16640, d_model=2048, num_layers=12, num_heads=16, d_ff=1024,

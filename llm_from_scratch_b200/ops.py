@@ -522,6 +522,27 @@ def block_hash(token_ids, prefix: int = -1) -> int:
     return int(lib.b200_block_hash(addr, n, 0 if prefix == -1 else prefix, 0 if prefix == -1 else 1))
 
 
+def decode_advance(sampled: torch.Tensor, input_ids: torch.Tensor, context_lens: torch.Tensor,
+                   slot_mapping: torch.Tensor, block_tables: torch.Tensor, block_size: int, num_blocks: int,
+                   history: torch.Tensor | None = None) -> None:
+    """Turns the decode inputs of the step that just sampled ``sampled`` into those of the next step, in
+    place and on the device: input id = sampled token, context length + 1, slot of the new position from
+    the block table (which must already list that block).  ``history`` [n] also receives the tokens."""
+    dev = _cuda(sampled, input_ids, context_lens, slot_mapping, block_tables, history)
+    n = sampled.numel()
+    for t in (sampled, input_ids, context_lens, slot_mapping) + ((history,) if history is not None else ()):
+        if t.dtype != torch.int64 or t.numel() < n or not t.is_contiguous():
+            raise ValueError("sampled, input_ids, context_lens, slot_mapping, history must be contiguous int64 [n]")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or block_tables.shape[0] < n \
+            or block_tables.stride(1) != 1:
+        raise ValueError("block_tables must be int32 [n, max_blocks]")
+    check(lib.b200_decode_advance(sampled.data_ptr(), input_ids.data_ptr(), context_lens.data_ptr(),
+                                  slot_mapping.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+                                  int(block_size), int(num_blocks), n,
+                                  history.data_ptr() if history is not None else None,
+                                  status_word(dev).data_ptr(), _stream()), "decode_advance")
+
+
 def block_hash_chain(token_ids, block_size: int) -> list[int]:
     """Chained XXH64 hashes of every full block of ``token_ids`` in one native call: element i is what
     ``block_hash(block i, prefix = element i-1)`` returns."""

@@ -230,3 +230,33 @@ def test_bf16_moe_engine_prefill_and_decode_graphs_match_eager():
         eng.exit()
     same = sum(a == b for a, b in zip(streams[True], streams[False]))
     assert same == len(prompts), (streams[True], streams[False])
+
+
+@pytest.mark.parametrize("kind", ["dense_fp32", "moe_bf16"])
+def test_decode_windows_give_the_step_by_step_streams(kind):
+    """decode_window = 4: four graph replays per scheduling decision with the device-side metadata step
+    (b200_decode_advance) in between give the streams of the one-step-at-a-time loop; requests have
+    different output lengths, so rows stop inside windows, and sequences cross block boundaries inside them."""
+    from llm_from_scratch_b200.engine import SamplingParams
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    if kind == "dense_fp32":
+        cfg, dtype = dict(C1, num_layers=2), torch.float32
+    else:
+        cfg, dtype = dict(vocab_size=500, context_length=256, d_model=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                          d_ff=192, attention_type="GQA", use_moe=True, n_routed_experts=8, num_experts_per_tok=2,
+                          n_shared_experts=1), torch.bfloat16
+    weights = init_reference_order(ModelConfig.from_dict(cfg), 3)
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, cfg["vocab_size"], (int(n),), generator=g).tolist() for n in (5, 64, 17, 130, 33, 1, 96, 15)]
+    sps = [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=True) for m in (40, 7, 23, 2, 31, 40, 12, 35)]
+    streams, steps = {}, {}
+    for window in (1, 4):
+        eng = make_engine(cfg, weights, dtype=dtype, eager=False, max_num_batched_tokens=512, decode_window=window)
+        streams[window] = eng.generate(prompts, sps)["token_ids"]
+        steps[window] = eng.stats["steps"]
+        eng.exit()
+    from llm_from_scratch_b200 import ops
+    ops.check_status()                      # no slot looked up outside a block table
+    assert streams[4] == streams[1]
+    assert [len(s) for s in streams[1]] == [m - 1 for m in (40, 7, 23, 2, 31, 40, 12, 35)]
+    assert steps[4] < steps[1] / 2          # far fewer scheduling decisions

@@ -109,3 +109,71 @@ def test_block_hash_chain_equals_block_by_block_hashing():
             h = ops.block_hash(ids[i * 16:(i + 1) * 16], h)
             want.append(h)
         assert ops.block_hash_chain(ids, 16) == want
+
+
+class _WindowRunner:
+    """Greedy stand-in whose token depends only on the request's own tokens.  ``run_window`` plays the
+    device's part of a window: it carries each row's tokens forward itself and checks that the block the
+    new position falls into was opened before the window started."""
+
+    def __init__(self, blocks, block_size, max_len=512):
+        self.num_kv_blocks, self.block_size, self.max_model_length = blocks, block_size, max_len
+        self.windows = []
+
+    @staticmethod
+    def _token(tokens):
+        return (sum(tokens[-3:]) * 31 + len(tokens) * 7) % 50
+
+    def run(self, seqs, is_prefill):
+        return [self._token(s.token_ids) for s in seqs]
+
+    def can_run_window(self, seqs):
+        return True
+
+    def run_window(self, seqs, steps):
+        self.windows.append(steps)
+        rows = [list(s.token_ids) for s in seqs]
+        tables = [list(s.block_table) for s in seqs]
+        out = []
+        for _ in range(steps):
+            for r, t in zip(rows, tables):
+                assert (len(r) - 1) // self.block_size < len(t), "position without a block"
+            toks = [self._token(r) for r in rows]
+            for r, tok in zip(rows, toks):
+                r.append(tok)
+            out.append(toks)
+        return out
+
+    def exit(self):
+        pass
+
+
+def _serve_windowed(window, blocks, eos, seed=5, n_req=30):
+    Sequence.counter = itertools.count()
+    rng = random.Random(seed)
+    runner = _WindowRunner(blocks, 4)
+    eng = LLMEngine(dict(block_size=4, max_num_sequences=5, max_num_batched_tokens=64, eos=eos,
+                         decode_window=window), runner=runner)
+    for _ in range(n_req):
+        eng.add_request([rng.randrange(50) for _ in range(rng.randrange(1, 30))],
+                        SamplingParams(temperature=0.0, max_tokens=rng.randrange(2, 40), ignore_eos=eos < 0))
+    outs = {}
+    while not eng.is_finished():
+        done, _n, _p = eng.step()
+        outs.update(done)
+    bm = eng.scheduler.block_manager
+    assert bm.num_free_blocks == blocks and not bm.used_block_ids
+    return outs, set(bm.hash_to_block_id), runner.windows
+
+
+@pytest.mark.parametrize("eos", [-1, 7])                # stops by max_tokens only, and by a sampled end token too
+@pytest.mark.parametrize("blocks", [400, 40])
+def test_decode_windows_give_the_step_by_step_tokens(blocks, eos):
+    """Several decode steps per scheduling decision: the same tokens per request as one step at a time
+    (a request's tokens depend on nothing but its own), every block sealed with the same hash, the pool
+    whole again at the end; sequences that stop inside a window lose their surplus tokens."""
+    want, want_hashes, _ = _serve_windowed(1, blocks, eos)
+    got, got_hashes, windows = _serve_windowed(4, blocks, eos)
+    assert got == want
+    assert got_hashes == want_hashes
+    assert windows and max(windows) == 4
