@@ -84,6 +84,9 @@ paged_decode_bf16_kernel(const DecodeArgs a) {
     local += num_kv_blocks(a.lens[i], a.bt_stride, kTok);
   int T;
   block_inclusive_scan(local, s_scan, &T);
+  // the combine kernel is launched as a programmatic dependent: let its CTAs be placed while this grid
+  // runs (they wait for this grid's completion before they read anything)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int Q = (T + P - 1) / P;
   const int start = p * Q;
   if (Q == 0 || start >= T) return;
@@ -363,6 +366,8 @@ constexpr int kCombineMaxParts = 8;  // parts whose weights are kept in shared m
 __global__ void __launch_bounds__(kCombineThreads)
 paged_decode_combine_kernel(const DecodeArgs a) {
   extern __shared__ float s_w[];  // [kCombineMaxParts][Hq]
+  // launched early (programmatic dependent of the attention kernel): everything below reads its results
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   const int i = blockIdx.x;
   const int n = a.Hq * a.D;
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + static_cast<int64_t>(i) * n;
@@ -438,6 +443,26 @@ paged_decode_combine_kernel(const DecodeArgs a) {
   }
 }
 
+// The combine follows the attention kernel in the stream and reads only what that kernel wrote: as a
+// programmatic dependent its launch and CTA placement overlap the attention kernel's tail.
+int launch_combine(const DecodeArgs& a, int batch, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(batch);
+  cfg.blockDim = dim3(kCombineThreads);
+  cfg.dynamicSmemBytes = (kCombineMaxParts + 2) * a.Hq * sizeof(float);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, paged_decode_combine_kernel, a) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
+  return launch_result();
+}
+
 }  // namespace
 
 int decode_combine_launch(const CombineArgs& c, cudaStream_t s) {
@@ -450,9 +475,7 @@ int decode_combine_launch(const CombineArgs& c, cudaStream_t s) {
   a.batch = c.batch;
   a.Hq = c.H;
   a.D = c.D;
-  paged_decode_combine_kernel<<<c.batch, kCombineThreads,
-                                (kCombineMaxParts + 2) * c.H * sizeof(float), s>>>(a);
-  return launch_result();
+  return launch_combine(a, c.batch, s);
 }
 
 namespace {
@@ -666,9 +689,7 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
     else
       rc = pl.nt == 1 ? launch_fast<32, 1>(a, pl, gi, s) : launch_fast<32, 2>(a, pl, gi, s);
     if (rc != B200_OK) return rc;
-    paged_decode_combine_kernel<<<batch, kCombineThreads,
-                                  (kCombineMaxParts + 2) * num_q_heads * sizeof(float), s>>>(a);
-    return launch_result();
+    return launch_combine(a, batch, s);
   }
 
   if (head_dim > kSimpleMaxPerLane * 32) return B200_ERR_UNSUPPORTED;
