@@ -110,6 +110,8 @@ mla_decode_mma_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_la
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int B = a.batch, H = a.H, p = blockIdx.x;
+  // the combine kernel is a programmatic dependent: its CTAs may be placed while this grid runs
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
   const CtaRange rg = plan_cta_range(a.lens, B, a.bt_stride, kTok, s_scan);
   if (rg.cnt == 0) return;
