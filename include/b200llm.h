@@ -175,13 +175,15 @@ int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
  *   k_head [total_k, H, head_dim_qk - tail_dim]  per-head columns, token stride k_head_token_stride
  *   k_tail [total_k, tail_dim]                   last tail_dim columns of every head's key
  *   q      [total_q, H, head_dim_qk], v [total_k, H, head_dim_v], out [total_q, H, head_dim_v]
- * so the rotary part is never copied into every head.  Keys/values are packed (no paged prefix).
+ * so the rotary part is never copied into every head.  Keys/values are packed (no paged prefix);
+ * total_q_tokens / total_k_tokens are the row counts of q and of k_head / k_tail / v, as above.
  * bf16, (head_dim_qk, tail_dim, head_dim_v) = (192, 64, 128), all parts 16-byte aligned; anything else
  * returns B200_ERR_UNSUPPORTED (the caller then expands the keys and uses b200_prefill_varlen).  plan: as above, for the
  * tile_rows of b200_prefill_tile_rows(head_dim_qk, head_dim_v, H, H, dtype). */
 int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const void* k_tail, const void* v,
                                     void* out, int64_t q_token_stride, int64_t k_head_token_stride,
                                     int64_t k_tail_token_stride, int64_t v_token_stride,
+                                    int64_t total_q_tokens, int64_t total_k_tokens,
                                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                                     int32_t num_seqs, int32_t max_seqlen_q, int32_t num_heads,
                                     int32_t head_dim_qk, int32_t tail_dim, int32_t head_dim_v, float scale,
@@ -190,8 +192,8 @@ int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const voi
 
 /* Tile list for b200_prefill_varlen, computed on the device from cu_seqlens_q (one small launch per
  * step; all layers of the step reuse it).
- *   b200_prefill_tile_rows: query rows per tile of the kernel that serves this shape (128 tcgen05,
- *     64 mma.sync), or 0 when only the general kernel applies (no plan then).
+ *   b200_prefill_tile_rows: query rows per tile of the kernel that serves this shape with packed keys
+ *     (128 or 256 tcgen05, 64 mma.sync), or 0 when only the general kernel applies (no plan then).
  *   b200_prefill_plan_bytes: size of `plan` for up to total_q_tokens rows in up to num_seqs sequences;
  *     its capacity in tiles is bytes / 4 - 4.
  *   b200_prefill_plan: max_seqlen_q is a host-side upper bound of the longest sequence

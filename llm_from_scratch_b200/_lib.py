@@ -32,7 +32,7 @@ SIGNATURES = {
                                      _i32, _i64, _f32, _vp, _sz, _i32, _vp, _vp]),
     "b200_paged_decode_gqa_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32,
                                             _i32, _i32, _i64, _f32, _i32, _vp, _vp]),
-    "b200_prefill_varlen_shared_tail": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
+    "b200_prefill_varlen_shared_tail": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
                                                _i32, _i32, _i32, _i32, _f32, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b200_prefill_varlen": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
                                    _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _i64, _i32,

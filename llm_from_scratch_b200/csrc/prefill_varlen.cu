@@ -112,6 +112,14 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
                        cudaStream_t s, const void* k_tail = nullptr, int64_t k_tail_stride = 0, int tail = 0);
 
+// tcgen05 path for the other head shapes (prefill_umma2.cu): packed keys/values, 256 query rows of one head per CTA
+int prefill_umma2_tile_rows(int Hq, int Hkv, int Dqk, int Dv);
+int prefill_umma2_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride, int64_t k_stride,
+                         int64_t v_stride, int64_t total_q, int64_t total_k, const int32_t* cu_q,
+                         const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv,
+                         float scale, const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
+                         cudaStream_t s, const void* k_tail, int64_t k_tail_stride, int tail);
+
 // tcgen05 path (prefill_umma.cu): head_dim 128, even group size
 int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
                         int64_t k_stride, int64_t v_stride, int64_t total_q, int64_t total_k,
@@ -218,6 +226,7 @@ extern "C" int32_t b200_prefill_tile_rows(int32_t num_q_heads, int32_t num_kv_he
                                           int32_t head_dim_v, int32_t dtype) {
   if (dtype != B200_DTYPE_BF16 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return 0;
   if (head_dim_qk == 128 && head_dim_v == 128 && ((num_q_heads / num_kv_heads) & 1) == 0) return 128;
+  if (const int r = b200::prefill_umma2_tile_rows(num_q_heads, num_kv_heads, head_dim_qk, head_dim_v)) return r;
   const bool mma = (head_dim_qk == head_dim_v && (head_dim_qk == 32 || head_dim_qk == 64 || head_dim_qk == 128)) ||
                    (head_dim_qk == 192 && head_dim_v == 128);
   return mma ? 64 : 0;
@@ -280,6 +289,13 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
                                         block_tables, bt_stride, block_size, num_blocks, plan, plan_tile_rows,
                                         plan_capacity, status, s);
     if (rcu != B200_ERR_UNSUPPORTED) return rcu;
+    if (block_tables == nullptr) {
+      const int rc2 = prefill_umma2_launch(q, k, v, out, q_token_stride, k_token_stride, v_token_stride,
+                                           total_q_tokens, total_k_tokens, cu_seqlens_q, cu_seqlens_k, num_seqs,
+                                           max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk, head_dim_v, scale,
+                                           plan, plan_tile_rows, plan_capacity, status, s, nullptr, 0, 0);
+      if (rc2 != B200_ERR_UNSUPPORTED) return rc2;
+    }
     const int rc = prefill_mma_launch(q, k, v, out, q_token_stride, k_token_stride,
                                       v_token_stride, cu_seqlens_q, cu_seqlens_k, num_seqs,
                                       max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk,
@@ -324,6 +340,7 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
 extern "C" int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const void* k_tail, const void* v,
                                                void* out, int64_t q_token_stride, int64_t k_head_token_stride,
                                                int64_t k_tail_token_stride, int64_t v_token_stride,
+                                               int64_t total_q_tokens, int64_t total_k_tokens,
                                                const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                                                int32_t num_seqs, int32_t max_seqlen_q, int32_t num_heads,
                                                int32_t head_dim_qk, int32_t tail_dim, int32_t head_dim_v,
@@ -337,6 +354,13 @@ extern "C" int b200_prefill_varlen_shared_tail(const void* q, const void* k_head
   if (dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
   if (num_seqs == 0 || max_seqlen_q == 0) return B200_OK;
   if (!q || !k_head || !k_tail || !v || !out || !cu_seqlens_q || !cu_seqlens_k) return B200_ERR_ARG;
+  if (total_q_tokens <= 0 || total_k_tokens <= 0) return B200_ERR_ARG;
+  const int rc2 = prefill_umma2_launch(q, k_head, v, out, q_token_stride, k_head_token_stride, v_token_stride,
+                                       total_q_tokens, total_k_tokens, cu_seqlens_q, cu_seqlens_k, num_seqs,
+                                       max_seqlen_q, num_heads, num_heads, head_dim_qk, head_dim_v, scale, plan,
+                                       plan_tile_rows, plan_capacity, status, static_cast<cudaStream_t>(stream),
+                                       k_tail, k_tail_token_stride, tail_dim);
+  if (rc2 != B200_ERR_UNSUPPORTED) return rc2;
   return prefill_mma_launch(q, k_head, v, out, q_token_stride, k_head_token_stride, v_token_stride, cu_seqlens_q,
                             cu_seqlens_k, num_seqs, max_seqlen_q, num_heads, num_heads, head_dim_qk, head_dim_v,
                             scale, nullptr, nullptr, nullptr, 0, 0, 0, plan, plan_tile_rows, plan_capacity, status,

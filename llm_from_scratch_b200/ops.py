@@ -240,7 +240,7 @@ def prefill_varlen_shared_tail(q: torch.Tensor, k_head: torch.Tensor, k_tail: to
         raise ValueError("out must be a contiguous [Tq, H, Dv] tensor")
     check(lib.b200_prefill_varlen_shared_tail(
         q.data_ptr(), k_head.data_ptr(), k_tail.data_ptr(), v.data_ptr(), out.data_ptr(), q.stride(0),
-        k_head.stride(0), k_tail.stride(0), v.stride(0), cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(),
+        k_head.stride(0), k_tail.stride(0), v.stride(0), Tq, Tk, cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(),
         cu_seqlens_q.numel() - 1, int(max_seqlen_q), H, Dqk, tail, Dv, float(scale),
         plan.buffer.data_ptr() if plan is not None else None, plan.tile_rows if plan is not None else 0,
         plan.capacity if plan is not None else 0, _dt(q), status_word(dev).data_ptr(), _stream()),

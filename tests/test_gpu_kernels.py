@@ -263,7 +263,7 @@ def test_prefill_plan_lists_every_tile_once_and_gives_identical_output(Hq, Hkv, 
     q, k, v, cu = q.cuda(), k.cuda(), v.cuda(), cu.cuda()
     scale = D ** -0.5
     rows = ops.prefill_tile_rows(Hq, Hkv, D, D, torch.bfloat16)
-    assert rows == (128 if D == 128 else 64)
+    assert rows == {128: 128, 64: 256, 32: 64}[D]       # two-head tcgen05, row-pair tcgen05, mma.sync
     plan = ops.prefill_plan(cu, sum(lens), max(lens), rows)
     ops.check_status()
     buf = plan.buffer.cpu().numpy()
@@ -348,6 +348,29 @@ def test_prefill_varlen_mla_head_dims_192_128():
     want = _oracle().prefill_varlen(q, k, v, cu, cu, scale)
     got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), scale)
     assert_close(got, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dqk,Dv", [(4, 4, 192, 128), (6, 2, 128, 128), (3, 1, 128, 128), (8, 2, 64, 64)])
+def test_prefill_row_pair_kernel_long_ragged_batch(Hq, Hkv, Dqk, Dv):
+    """Head shapes served by the tcgen05 kernel that gives a CTA 256 query rows of one head (MLA's
+    192/128, head_dim 128 with an odd group size, head_dim 64): lengths around the 128- and 256-row
+    boundaries, sequences that end inside the first half of a CTA, many key tiles; with and without
+    the tile list."""
+    ops = _ops()
+    lens = [1, 127, 128, 129, 255, 256, 257, 700, 1500, 2, 64, 385]
+    q, k, v, cu = _prefill_inputs(lens, Hq, Hkv, Dqk, Dv, torch.bfloat16, seed=Dqk + Hq)
+    scale = Dqk ** -0.5
+    want = _oracle().prefill_varlen(q, k, v, cu, cu, scale)
+    q, k, v, cu = q.cuda(), k.cuda(), v.cuda(), cu.cuda()
+    got = ops.prefill_varlen(q, k, v, cu, cu, max(lens), max(lens), scale)
+    ops.check_status()
+    assert_close(got, want, torch.bfloat16)
+    rows = ops.prefill_tile_rows(Hq, Hkv, Dqk, Dv, torch.bfloat16)
+    assert rows == 256
+    plan = ops.prefill_plan(cu, sum(lens), max(lens), rows)
+    planned = ops.prefill_varlen(q, k, v, cu, cu, max(lens), max(lens), scale, plan=plan)
+    ops.check_status()
+    assert torch.equal(planned, got)
 
 
 # ----------------------------------------------------------------------------- MLA decode
