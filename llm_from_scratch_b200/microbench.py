@@ -86,6 +86,36 @@ def prefill(steps: int = 5, warmup: int = 2, total: int = 262144) -> dict:
                 scatter_bytes=T * (2 * Hkv * D * 2 * 2 + 8), launches_per_call=3)
 
 
+def mla_prefill(steps: int = 10, warmup: int = 3, seqs: int = 16) -> dict:
+    """Prefill attention of the MLA+MoE decoder's benchmark step: ``seqs`` prompts with lengths uniform
+    [256,4096] (seed 4), 16 heads, keys = 128 per-head columns (a strided view of the fused up-projection
+    output, like the values) + 64 rotary columns shared by all heads (a view of the latent rows), values
+    128 wide; one call = the step's tile list + the attention of one layer."""
+    rng = np.random.default_rng(4)
+    lens = rng.integers(256, 4097, size=seqs)
+    T, H, hd, dr, r = int(lens.sum()), 16, 128, 64, 512
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn(T, H, hd + dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    kv = torch.randn(T, 2 * H * hd, generator=g, device="cuda", dtype=torch.bfloat16)
+    rows = torch.randn(T, r + dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    k_head, v, tail = kv[:, :H * hd].view(T, H, hd), kv[:, H * hd:].view(T, H, hd), rows[:, r:]
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).cuda()
+    out = torch.empty(T, H, hd, device="cuda", dtype=torch.bfloat16)
+    mx = int(lens.max())
+    tile_rows = ops.prefill_tile_rows(H, H, hd + dr, hd, torch.bfloat16)
+
+    def call():
+        plan = ops.prefill_plan(cu, T, mx, tile_rows)
+        ops.prefill_varlen_shared_tail(q, k_head, tail, v, cu, cu, mx, (hd + dr) ** -0.5, out=out, plan=plan)
+
+    ms = _time(call, steps, warmup)
+    ops.check_status()
+    flops = prefill_flops(lens, H, hd + dr, hd)
+    return dict(workload=f"MLA prefill attention: {seqs} seqs U[256,4096], {T} tokens, 16 heads, 192/128 head dims "
+                         "(128 + shared 64-wide rotary tail), bf16", ms=ms, tokens=T, flops=flops,
+                tflops=flops / ms / 1e9, tile_rows=tile_rows, launches_per_call=2)
+
+
 def store(steps: int = 50, warmup: int = 5, tokens: int = 262144) -> dict:
     """store_kvcache of the prefill stress batch: shuffled slot mapping (seed 2), 8 x 128 bf16 rows."""
     Hkv, D, bs = 8, 128, 16
