@@ -858,3 +858,31 @@ def test_sample_with_temperature_follows_the_softmax_distribution():
     mixed[::2] = 0.0                                                          # greedy and sampled rows together
     out = ops.sample(logits, mixed, seed=5, offset=1)
     assert (out[::2] == 6).all() and (out[1::2] != 6).any()
+
+
+def test_decode_advance_steps_the_decode_metadata():
+    """input id = sampled token, context length + 1 and the slot of the new position from the block table,
+    exactly what prepare_decode computes on the host for the next step (model_runner.py:253-278); a table
+    that does not list the needed block gives slot -1 and a reported bounds error; rows past n untouched."""
+    ops = _ops()
+    bs, nb, n = 16, 64, 5
+    lens = torch.tensor([1, 15, 16, 17, 47, 99, 99], dtype=torch.int64)
+    tables = torch.from_numpy(np.random.default_rng(5).permutation(nb)[:7 * 4].reshape(7, 4).astype(np.int32))
+    sampled = torch.tensor([11, 12, 13, 14, 15, 16, 17], dtype=torch.int64)
+    ids, slots = torch.full((7,), -5, dtype=torch.int64), torch.full((7,), -5, dtype=torch.int64)
+    hist = torch.full((7,), -5, dtype=torch.int64)
+    d = [t.cuda() for t in (sampled, ids, lens.clone(), slots, tables, hist)]
+    ops.decode_advance(d[0][:n], d[1], d[2], d[3], d[4], bs, nb, d[5])
+    ops.check_status()
+    new_len = lens[:n] + 1
+    want_slots = tables[torch.arange(n), (new_len - 1) // bs].long() * bs + (new_len - 1) % bs
+    assert d[1].cpu().tolist() == [11, 12, 13, 14, 15, -5, -5]
+    assert d[2].cpu().tolist() == new_len.tolist() + [99, 99]
+    assert d[3].cpu().tolist() == want_slots.tolist() + [-5, -5]
+    assert d[5].cpu().tolist() == [11, 12, 13, 14, 15, -5, -5]
+    # length 64 -> 65 needs block 4 of a 4-entry table: slot -1, error reported (and cleared by the read)
+    lens2 = torch.tensor([64], dtype=torch.int64).cuda()
+    ops.decode_advance(d[0][:1], d[1], lens2, d[3], d[4], bs, nb)
+    assert d[3][0].item() == -1
+    with pytest.raises(RuntimeError):
+        ops.check_status()
