@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 7
+#define B200_ABI_VERSION 8
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -353,6 +353,13 @@ int b200_decode_advance(const int64_t* sampled, int64_t* input_ids, int64_t* con
                         int64_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride,
                         int32_t block_size, int64_t num_blocks, int32_t num_seqs, int64_t* history,
                         int32_t* status, void* stream);
+
+/* Device-resident block tables: writes `count` (row, column, block id) int32 triples into
+ * block_tables [rows, bt_stride], so that a decode step uploads only the table entries that changed since
+ * the previous step (the reference rebuilds and ships the whole table, engine/model_runner.py:263-268).
+ * A triple outside the table is skipped and reported as B200_ERR_BOUNDS in *status. */
+int b200_block_table_patch(const int32_t* patches, int32_t count, int32_t* block_tables, int64_t bt_stride,
+                           int32_t rows, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Token sampling (Sampler.forward, utils/sampler.py:35-52; greedy argmax of generate.py:62), one launch.

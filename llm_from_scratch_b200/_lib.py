@@ -50,6 +50,7 @@ SIGNATURES = {
     "b200_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     "b200_moe_grouped_gemm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "b200_decode_advance": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "b200_block_table_patch": (_i32, [_vp, _i32, _vp, _i64, _i32, _vp, _vp]),
     "b200_sample": (_i32, [_vp, _i64, _vp, _i64, _i32, _u64, _u64, _vp, _i32, _vp]),
     "b200_moe_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "b200_mla_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),

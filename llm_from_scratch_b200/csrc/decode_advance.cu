@@ -53,3 +53,38 @@ extern "C" int b200_decode_advance(const int64_t* sampled, int64_t* input_ids, i
       history, status);
   return launch_result();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Device-resident block tables: instead of uploading the whole [batch, max_blocks] table every decode
+// step (ModelRunner.prepare_decode rebuilds and ships it, engine/model_runner.py:263-268), the host sends
+// only the entries that changed since the previous step — normally one new block per sequence every
+// block_size steps — as (row, column, block id) triples that this kernel writes into the table.
+namespace b200 {
+namespace {
+
+__global__ void block_table_patch_kernel(const int32_t* __restrict__ patches, int count,
+                                         int32_t* __restrict__ tables, int64_t bt_stride, int rows,
+                                         int32_t* status) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= count) return;
+  const int row = patches[3 * p], col = patches[3 * p + 1], val = patches[3 * p + 2];
+  if (row < 0 || row >= rows || col < 0 || col >= bt_stride) {
+    report(status, B200_ERR_BOUNDS);
+    return;
+  }
+  tables[static_cast<int64_t>(row) * bt_stride + col] = val;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_block_table_patch(const int32_t* patches, int32_t count, int32_t* block_tables,
+                                      int64_t bt_stride, int32_t rows, int32_t* status, void* stream) {
+  using namespace b200;
+  if (count < 0 || bt_stride <= 0 || rows < 0) return B200_ERR_ARG;
+  if (count == 0) return B200_OK;
+  if (!patches || !block_tables) return B200_ERR_ARG;
+  block_table_patch_kernel<<<(count + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      patches, count, block_tables, bt_stride, rows, status);
+  return launch_result();
+}

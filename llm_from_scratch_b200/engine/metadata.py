@@ -125,20 +125,31 @@ class DecodeBatchBuilder:
     (input_ids, slot_mapping, context_lens, block_tables) into caller-owned arrays.
 
     The owner must call ``invalidate`` for every sequence that goes through a prefill (its block table
-    may have been replaced by one of the same length after a preemption)."""
+    may have been replaced by one of the same length after a preemption).
 
-    def __init__(self, block_size: int, max_blocks: int, rows: int = 1024):
+    With ``device_rows`` > 0 the builder also mirrors what the device-resident table holds at every batch
+    position (which sequence row, at which epoch, how many entries), and ``build(..., patches=)`` emits only
+    the (position, column, block id) triples the device lacks: block tables are append-only between two
+    prefills of a sequence, so a steady batch costs one triple per sequence every ``block_size`` steps
+    instead of a ``batch x max_blocks`` upload (the reference re-uploads the table, model_runner.py:263-268)."""
+
+    def __init__(self, block_size: int, max_blocks: int, rows: int = 1024, device_rows: int = 0):
         self.block_size = block_size
         self.tables = np.zeros((rows, max_blocks), dtype=np.int32)
         self.row_blocks = np.full(rows, -1, dtype=np.int64)     # valid entries per row, -1 = rebuild
         self.row_seq: list = [None] * rows
         self.row_owner = np.zeros(rows, dtype=np.int64)         # id() of the owning sequence, 0 = none
+        self.row_epoch = np.zeros(rows, dtype=np.int64)         # bumped whenever the row's table may have been replaced
         self.free = list(range(rows - 1, -1, -1))
+        self.dev_row = np.full(device_rows, -1, dtype=np.int64)      # builder row mirrored at each batch position
+        self.dev_epoch = np.zeros(device_rows, dtype=np.int64)
+        self.dev_blocks = np.zeros(device_rows, dtype=np.int64)      # entries of that row present on the device
 
     def invalidate(self, seqs) -> None:
         for s in seqs:
             if s._row is not None and self.row_seq[s._row] is s:
                 self.row_blocks[s._row] = -1
+                self.row_epoch[s._row] += 1
 
     def _assign(self, s) -> int:
         if not self.free:
@@ -153,17 +164,23 @@ class DecodeBatchBuilder:
                 self.tables = np.concatenate([self.tables, np.zeros_like(self.tables)])
                 self.row_blocks = np.concatenate([self.row_blocks, np.full(old, -1, dtype=np.int64)])
                 self.row_owner = np.concatenate([self.row_owner, np.zeros(old, dtype=np.int64)])
+                self.row_epoch = np.concatenate([self.row_epoch, np.zeros(old, dtype=np.int64)])
                 self.row_seq.extend([None] * old)
                 self.free = list(range(2 * old - 1, old - 1, -1))
         r = self.free.pop()
         self.row_seq[r] = s
         self.row_owner[r] = id(s)
         self.row_blocks[r] = -1
+        self.row_epoch[r] += 1
         s._row = r
         return r
 
     def build(self, seqs, out_ids: np.ndarray, out_slots: np.ndarray, out_lens: np.ndarray,
-              out_tables: np.ndarray) -> None:
+              out_tables: np.ndarray, patches: np.ndarray | None = None) -> int:
+        """Writes the step's metadata.  Without ``patches`` the block tables go to ``out_tables`` and the
+        result is -1.  With ``patches`` (int32 [capacity, 3]) the entries the device table lacks are written
+        there as (position, column, block id) and their number is returned; when they exceed the capacity
+        (a new batch composition) the whole tables go to ``out_tables`` instead and the result is -1."""
         n, bs = len(seqs), self.block_size
         rows_l = [s._row for s in seqs]
         ids = np.array([id(s) for s in seqs], dtype=np.int64)
@@ -184,9 +201,28 @@ class DecodeBatchBuilder:
                 k = 0
             self.tables[r, k:len(bt)] = bt[k:]
             self.row_blocks[r] = len(bt)
-        width = int(nblk.max())
-        out_tables[:n, :width] = self.tables[rows, :width]
+        count = -1
+        if patches is not None:
+            same = (self.dev_row[:n] == rows) & (self.dev_epoch[:n] == self.row_epoch[rows])
+            start = np.where(same, np.minimum(self.dev_blocks[:n], nblk), 0)
+            cnt = nblk - start
+            total = int(cnt.sum())
+            if total <= patches.shape[0]:
+                count = total
+                if total:
+                    pos = np.repeat(np.arange(n, dtype=np.int64), cnt)
+                    col = np.arange(total, dtype=np.int64) - np.repeat(np.cumsum(cnt) - cnt, cnt) + np.repeat(start, cnt)
+                    patches[:total, 0] = pos
+                    patches[:total, 1] = col
+                    patches[:total, 2] = self.tables[rows[pos], col]
+            self.dev_row[:n] = rows
+            self.dev_epoch[:n] = self.row_epoch[rows]
+            self.dev_blocks[:n] = nblk
+        if count < 0:
+            width = int(nblk.max())
+            out_tables[:n, :width] = self.tables[rows, :width]
         out_ids[:n] = [s.last_token for s in seqs]
         out_lens[:n] = lens
         # the block the new token falls into: the last one, unless blocks were opened ahead for later steps
         out_slots[:n] = self.tables[rows, (lens - 1) // bs].astype(np.int64) * bs + (lens - 1) % bs
+        return count

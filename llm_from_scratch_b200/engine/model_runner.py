@@ -231,11 +231,19 @@ class ModelRunner:
         n = len(seqs)
         bucket = next(b for b in sorted(self.graphs) if b >= n)
         h, v = self.graph_host_np, self.graph_vars
-        self.decode_builder.build(seqs, h["input_ids"], h["slot_mapping"], h["context_lens"], h["block_tables"])
+        # block tables live on the device: a step ships the entries that changed (one new block per sequence
+        # every block_size steps) as patches behind the small arrays, or the whole table for a new batch
+        patched = self.decode_builder.build(seqs, h["input_ids"], h["slot_mapping"], h["context_lens"],
+                                            h["block_tables"], patches=h["patches"])
         h["slot_mapping"][n:bucket] = -1
         h["context_lens"][n:bucket] = 0
-        nbytes = self.graph_tables_offset + bucket * h["block_tables"].shape[1] * 4
+        if patched >= 0:
+            nbytes = self.graph_patches_offset + patched * 12
+        else:
+            nbytes = self.graph_tables_offset + bucket * h["block_tables"].shape[1] * 4
         self.graph_dev[:nbytes].copy_(self.graph_host[:nbytes], non_blocking=True)
+        if patched > 0:
+            ops.block_table_patch(v["patches"], patched, v["block_tables"])
         set_context(False, slot_mapping=v["slot_mapping"][:n], context_lens=v["context_lens"][:n],
                     block_tables=v["block_tables"][:n])
         if replay:
@@ -373,6 +381,7 @@ class ModelRunner:
         # step copies only the prefix its batch bucket uses)
         fields = (("input_ids", np.int64, torch.int64, (max_bs,)), ("slot_mapping", np.int64, torch.int64, (max_bs,)),
                   ("context_lens", np.int64, torch.int64, (max_bs,)),
+                  ("patches", np.int32, torch.int32, (8 * max_bs, 3)),
                   ("block_tables", np.int32, torch.int32, (max_bs, max_blocks)))
         offsets, total = {}, 0
         for name, npdt, _, shape in fields:
@@ -381,6 +390,7 @@ class ModelRunner:
         self.graph_dev = torch.zeros(total, dtype=torch.uint8, device=dev)
         self.graph_host = torch.zeros(total, dtype=torch.uint8).pin_memory()
         self.graph_tables_offset = offsets["block_tables"]
+        self.graph_patches_offset = offsets["patches"]
         host_bytes = self.graph_host.numpy()
         v, self.graph_host_np = {}, {}
         for name, npdt, tdt, shape in fields:
@@ -389,7 +399,7 @@ class ModelRunner:
             self.graph_host_np[name] = host_bytes[offsets[name]:offsets[name] + nbytes].view(npdt).reshape(shape)
         v["slot_mapping"].fill_(-1)
         self.graph_host_np["slot_mapping"][:] = -1
-        self.decode_builder = md.DecodeBatchBuilder(self.block_size, max_blocks, rows=4 * max_bs)
+        self.decode_builder = md.DecodeBatchBuilder(self.block_size, max_blocks, rows=4 * max_bs, device_rows=max_bs)
         v["outputs"] = torch.zeros(max_bs, self.model_config.d_model, dtype=self.dtype, device=dev)
         # the graph also holds the lm_head GEMM and the greedy argmax, so a greedy step launches nothing else
         v["logits"] = torch.zeros(max_bs, self.model_config.vocab_size, dtype=self.dtype, device=dev)

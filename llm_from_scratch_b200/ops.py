@@ -543,6 +543,21 @@ def decode_advance(sampled: torch.Tensor, input_ids: torch.Tensor, context_lens:
                                   status_word(dev).data_ptr(), _stream()), "decode_advance")
 
 
+def block_table_patch(patches: torch.Tensor, count: int, block_tables: torch.Tensor) -> None:
+    """Writes the first ``count`` (row, column, block id) int32 triples of ``patches`` into ``block_tables``
+    [rows, max_blocks] on the device (incremental update of a device-resident table)."""
+    if count <= 0:
+        return
+    dev = _cuda(patches, block_tables)
+    if patches.dtype != torch.int32 or not patches.is_contiguous() or patches.numel() < 3 * count:
+        raise ValueError("patches must be a contiguous int32 tensor of at least 3 * count elements")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or block_tables.stride(1) != 1:
+        raise ValueError("block_tables must be int32 [rows, max_blocks]")
+    check(lib.b200_block_table_patch(patches.data_ptr(), int(count), block_tables.data_ptr(), block_tables.stride(0),
+                                     block_tables.shape[0], status_word(dev).data_ptr(), _stream()),
+          "block_table_patch")
+
+
 def block_hash_chain(token_ids, block_size: int) -> list[int]:
     """Chained XXH64 hashes of every full block of ``token_ids`` in one native call: element i is what
     ``block_hash(block i, prefix = element i-1)`` returns."""

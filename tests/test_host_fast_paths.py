@@ -19,12 +19,17 @@ class _Runner:
         self.rng = random.Random(7)
         self.log = []
         self.builder = md.DecodeBatchBuilder(block_size, 64, rows=8) if check_builder else None
+        # a second builder drives a stand-in for the device-resident table through patches only
+        self.patcher = md.DecodeBatchBuilder(block_size, 64, rows=8, device_rows=16) if check_builder else None
+        self.dev_tables = np.full((16, 64), -9, dtype=np.int32)
+        self.patch_counts = []
 
     def run(self, seqs, is_prefill):
         self.log.append((is_prefill, [s.seq_id for s in seqs], [list(s.block_table) for s in seqs]))
         if self.builder is not None:
             if is_prefill:
                 self.builder.invalidate(seqs)
+                self.patcher.invalidate(seqs)
             else:
                 want = md.prepare_decode(seqs, self.block_size)
                 n = len(seqs)
@@ -37,6 +42,23 @@ class _Runner:
                     k = len(s.block_table)
                     assert np.array_equal(tables[i, :k], want.block_tables[i, :k])
                 assert (ids[n:] == -7).all() and (tables[n:] == -7).all()
+                # incremental form: apply the patches (or the full upload when they do not fit) to the
+                # persistent table; every sequence's entries must then be what the full rebuild gives
+                patches = np.zeros((6, 3), dtype=np.int32)
+                full = np.full((n, 64), -7, dtype=np.int32)
+                ids2, slots2, lens2 = (np.zeros(n, dtype=np.int64) for _ in range(3))
+                cnt = self.patcher.build(seqs, ids2, slots2, lens2, full, patches=patches)
+                self.patch_counts.append(cnt)
+                if cnt >= 0:
+                    for r, c, v in patches[:cnt].tolist():
+                        self.dev_tables[r, c] = v
+                else:
+                    for i, s in enumerate(seqs):
+                        self.dev_tables[i, :len(s.block_table)] = full[i, :len(s.block_table)]
+                assert np.array_equal(ids2, want.input_ids) and np.array_equal(slots2, want.slot_mapping)
+                for i, s in enumerate(seqs):
+                    k = len(s.block_table)
+                    assert np.array_equal(self.dev_tables[i, :k], want.block_tables[i, :k]), (i, cnt)
         return [self.rng.randrange(50) for _ in seqs]
 
     def exit(self):
@@ -61,6 +83,7 @@ def _serve(blocks, general_only=False, check_builder=False, n_req=40, seed=3):
                                                               ignore_eos=True))
         done, _n, _p = eng.step()
         outs.update(done)
+    _serve.last_runner = runner
     return runner.log, outs
 
 
@@ -78,6 +101,9 @@ def test_decode_batch_builder_equals_prepare_decode(blocks):
     small pool sequences are preempted and prefilled again into different blocks."""
     log, _ = _serve(blocks, check_builder=True)
     assert sum(1 for p, _, _ in log if not p) > 20
+    counts = _serve.last_runner.patch_counts
+    # steady batches ship nothing or a block or two; a new composition falls back to the full table
+    assert counts.count(0) > 5 and any(0 < c <= 6 for c in counts) and -1 in counts
 
 
 def test_decode_batch_builder_rejects_rows_of_another_builder():
