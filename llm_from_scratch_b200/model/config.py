@@ -1,7 +1,7 @@
 """Architecture fields of the reference's ``Config`` (model/config.py:97-252) that the decoder reads."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass, asdict
 from typing import Optional
 
 
