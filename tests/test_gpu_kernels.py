@@ -886,3 +886,58 @@ def test_decode_advance_steps_the_decode_metadata():
     assert d[3][0].item() == -1
     with pytest.raises(RuntimeError):
         ops.check_status()
+
+
+def test_mla_decode_benchmark_shape_sampled_rows():
+    """The MLA benchmark's decode batch at full size (240 sequences, contexts uniform [512,16384], latent
+    512 + 64, 2.07 M context tokens): a sample of rows against the oracle, and a second call gives the
+    same bits (fixed cut, no atomics)."""
+    from llm_from_scratch_b200.workloads import c4_decode_case
+    ops = _ops()
+    case = c4_decode_case()
+    H, r, dr, bs = 16, 512, 64, 16
+    g = torch.Generator(device="cuda").manual_seed(4)
+    lat = (torch.randn(case.num_blocks, bs, r + dr, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    qa = (torch.randn(case.batch, H, r, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    qr = torch.randn(case.batch, H, dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    bt, cl = torch.from_numpy(case.block_tables).cuda(), torch.from_numpy(case.context_lens).cuda()
+    scale = 192 ** -0.5
+    out = ops.mla_decode(qa, qr, lat, bt, cl, scale)
+    ops.check_status()
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, ops.mla_decode(qa, qr, lat, bt, cl, scale))
+    for b in [0, 7, 123, 239, int(np.argmax(case.context_lens)), int(np.argmin(case.context_lens))]:
+        L = int(case.context_lens[b])
+        nblk = (L + bs - 1) // bs
+        ids = torch.from_numpy(case.block_tables[b, :nblk].astype(np.int64)).cuda()
+        want = _oracle().mla_decode(qa[b:b + 1].cpu(), qr[b:b + 1].cpu(), lat[ids].cpu(), [list(range(nblk))], [L], scale)
+        assert_close(out[b:b + 1], want, torch.bfloat16)
+
+
+def test_mla_prefill_benchmark_step_sampled_sequences():
+    """The MLA benchmark's prefill batch at full size (16 prompts, lengths uniform [256,4096], 16 heads,
+    192/128 head dims, keys = per-head columns + the rotary tail shared by all heads, both strided views):
+    the shortest, the longest and one more sequence against the oracle on expanded keys."""
+    ops = _ops()
+    rng = np.random.default_rng(4)
+    lens = rng.integers(256, 4097, size=16)
+    T, H, hd, dr, r = int(lens.sum()), 16, 128, 64, 512
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(T, H, hd + dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    kv = torch.randn(T, 2 * H * hd, generator=g, device="cuda", dtype=torch.bfloat16)
+    rows = torch.randn(T, r + dr, generator=g, device="cuda", dtype=torch.bfloat16)
+    k_head, v, tail = kv[:, :H * hd].view(T, H, hd), kv[:, H * hd:].view(T, H, hd), rows[:, r:]
+    cu_np = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cu = torch.from_numpy(cu_np).cuda()
+    mx = int(lens.max())
+    plan = ops.prefill_plan(cu, T, mx, ops.prefill_tile_rows(H, H, hd + dr, hd, torch.bfloat16))
+    scale = (hd + dr) ** -0.5
+    out = ops.prefill_varlen_shared_tail(q, k_head, tail, v, cu, cu, mx, scale, plan=plan)
+    ops.check_status()
+    assert torch.isfinite(out.float()).all()
+    for s in sorted({int(np.argmin(lens)), int(np.argmax(lens)), 5}):
+        a, b = int(cu_np[s]), int(cu_np[s + 1])
+        k_full = torch.cat([k_head[a:b], tail[a:b].unsqueeze(1).expand(-1, H, dr)], dim=-1).cpu()
+        one = torch.tensor([0, b - a], dtype=torch.int32)
+        want = _oracle().prefill_varlen(q[a:b].cpu(), k_full, v[a:b].cpu(), one, one, scale)
+        assert_close(out[a:b], want, torch.bfloat16)
