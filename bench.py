@@ -143,7 +143,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "mla_prefill", "store", "moe_experts", "engine", "engine_mla"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "mla_prefill", "store", "moe_experts", "engine", "engine_mla", "engine_step"],
                     help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
                          "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
     ap.add_argument("--rate", type=float, default=0.0, help="engine workload: Poisson arrival rate (req/s); 0 = offline")
@@ -166,7 +166,7 @@ def main():
             kw["decode_window"] = args.decode_window
         if args.batch != BATCH:   # profiling cases: fewer sequences / tokens
             key = {"mla_decode": "batch", "engine": "batch", "prefill": "total", "store": "tokens",
-                   "moe_experts": "tokens", "engine_mla": "batch", "mla_prefill": "seqs"}[args.workload]
+                   "moe_experts": "tokens", "engine_mla": "batch", "mla_prefill": "seqs", "engine_step": "batch"}[args.workload]
             kw[key] = args.batch
         res = fn(**kw)
         if not res:       # a non-zero rank of a multi-replica engine run

@@ -241,6 +241,53 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
                 decode_window=decode_window, rank0_timing=timing)
 
 
+def engine_step(steps: int = 0, warmup: int = 0, batch: int = 1024) -> dict:
+    """Kernel shares of one decode step and one prefill step of the GQA+MoE engine at steady state
+    (``batch`` requests of the continuous-batching workload, all at t = 0): the engine runs normally and
+    the first decode step after engine step 300 and the first prefill step after engine step 40 are
+    recorded with the CUPTI activity profiler.  Durations under the profiler are for shares, not rates."""
+    import itertools
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from .engine import SamplingParams, Sequence
+    from .engine.llm_engine import LLMEngine
+    from .workloads import c3_requests
+    prompts, outs, _ = c3_requests(batch, rate=None)
+    Sequence.counter = itertools.count()
+    eng = LLMEngine(dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
+                         max_num_batched_tokens=8192, max_cached_blocks=110000, eos=-1, device="cuda:0",
+                         max_model_length=2048, seed=0))
+    for p, n in zip(prompts, outs):
+        eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=int(n) + 1, ignore_eos=True))
+    want = {"prefill": 40, "decode": 300}
+    got, step = {}, 0
+    while not eng.is_finished():
+        due = [k for k, first in want.items() if k not in got and step >= first]
+        if not due:
+            eng.step()
+            step += 1
+            continue
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            _out, n, is_prefill = eng.step()
+            torch.cuda.synchronize()
+        step += 1
+        kind = "prefill" if is_prefill else "decode"
+        if kind in due:
+            rows = [(e.key, e.self_device_time_total, e.count) for e in prof.key_averages()
+                    if e.self_device_time_total > 0 and not e.key.startswith(("aten::", "cuda", "Memcpy", "Memset",
+                                                                              "Activity", "Lazy"))]
+            total = sum(r[1] for r in rows)
+            rows.sort(key=lambda r: -r[1])
+            got[kind] = dict(engine_step=step, tokens=n, kernel_us=total, kernels=[
+                dict(name=k[:100], us=round(us, 1), share=round(us / total, 4), launches=c) for k, us, c in rows[:14]])
+    ops.check_status()
+    eng.exit()
+    return dict(workload=f"GQA+MoE engine, {batch} requests at t=0: kernel shares of one decode and one prefill step "
+                         "(CUPTI activity records)", **got)
+
+
 C4_MODEL = dict(vocab_size=32000, context_length=16640, d_model=2048, num_layers=12, num_heads=16, d_ff=1024,
                 attention_type="MLA", kv_lora_rank=512, q_lora_rank=1024, rope_dim=64, use_moe=True,
                 n_routed_experts=32, num_experts_per_tok=4, n_shared_experts=1)
