@@ -203,3 +203,34 @@ def test_decode_windows_give_the_step_by_step_tokens(blocks, eos):
     assert got == want
     assert got_hashes == want_hashes
     assert windows and max(windows) == 4
+
+
+def test_decode_window_planning_respects_length_and_pool_limits():
+    """The window never runs past the block table's capacity, ends where the longest-lived sequence stops,
+    opens exactly the blocks the extra steps write into, and collapses to 1 when the pool cannot cover them."""
+    Sequence.counter = itertools.count()
+    Sequence.block_size = 4
+    sched = Scheduler(max_num_sequences=4, max_num_batched_tokens=64, max_cached_blocks=8, block_size=4, eos=-1)
+    a = Sequence(list(range(6)), SamplingParams(temperature=0.0, max_tokens=50, ignore_eos=True))
+    b = Sequence(list(range(3)), SamplingParams(temperature=0.0, max_tokens=50, ignore_eos=True))
+    for s in (a, b):
+        sched.add_sequence(s)
+    seqs, is_prefill = sched.schedule()
+    assert is_prefill and seqs == [a, b]
+    sched.postprocess(seqs, [1, 2])                      # lengths 7 and 4
+    seqs, is_prefill = sched.schedule()                  # decode round: b (4 = full block) is sealed
+    assert not is_prefill
+    tables = [list(s.block_table) for s in seqs]
+    # 30 positions at most: a (7 tokens) could run 24 steps, the table bound cuts the window at 30 - 7 + 1
+    assert sched.plan_decode_window(seqs, 4, 30) == 4
+    # steps 2-4 write positions 7,8,9 of a (block 1, then block 2 opened ahead) and 4,5,6 of b (block 1 opened ahead)
+    assert len(a.block_table) == len(tables[0]) + 1 and len(b.block_table) == len(tables[1]) + 1
+    assert sched.plan_decode_window(seqs, 4, 8) == 2     # a has room for one more step only (8 - 7 + 1)
+    a.max_tokens = b.max_tokens = 3                      # both stop after their next token
+    assert sched.plan_decode_window(seqs, 4, 30) == 1
+    a.max_tokens = b.max_tokens = 50
+    free = sched.block_manager.num_free_blocks
+    for _ in range(free):                                # drain the pool: nothing can be opened ahead
+        sched.block_manager.open_block(a)
+    a.num_tokens = 8                                     # next lengths 9.. would start a block
+    assert sched.plan_decode_window(seqs, 4, 300) == 1
