@@ -39,11 +39,13 @@ struct Lay {
   static constexpr int NST = DQK >= 192 ? 3 : 4;
   static constexpr int OFF_QA = 0, OFF_QB = Q_BYTES, OFF_KV = 2 * Q_BYTES;
   static constexpr int OFF_BAR = OFF_KV + NST * STAGE;
-  // barriers: Q_FULL, then per stage K_FULL, V_FULL, K_EMPTY, V_EMPTY, then S_FULL[2], P_READY[2], O_FINAL[2]
-  static constexpr int Q_FULL = 0, K_FULL = 1, V_FULL = 1 + NST, K_EMPTY = 1 + 2 * NST, V_EMPTY = 1 + 3 * NST;
-  static constexpr int S_FULL = 1 + 4 * NST, P_READY = S_FULL + 2, O_FINAL = S_FULL + 4, NUM_BARS = S_FULL + 6;
+  // barriers: Q_FULL, then per stage K_FULL, V_FULL, K_EMPTY[problem], V_EMPTY[problem], then
+  // S_FULL[problem][score buffer], P_READY[problem], PV_DONE[problem], O_FINAL[problem]
+  static constexpr int Q_FULL = 0, K_FULL = 1, V_FULL = 1 + NST, K_EMPTY = 1 + 2 * NST, V_EMPTY = 1 + 4 * NST;
+  static constexpr int S_FULL = 1 + 6 * NST, P_READY = S_FULL + 4, PV_DONE = S_FULL + 6, O_FINAL = S_FULL + 8,
+                       NUM_BARS = S_FULL + 10;
   static constexpr int SMEM = OFF_BAR + NUM_BARS * 8 + 32 + 1024;   // + slack to align the base to 1024 bytes
-  static constexpr int TCOLS_USED = 2 * (64 + DV);
+  static constexpr int TCOLS_USED = 2 * (128 + DV);   // per problem: two score buffers of 64 columns + O
   static constexpr int TCOLS = TCOLS_USED > 256 ? 512 : 256;
 };
 
@@ -107,11 +109,15 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
     for (int s = 0; s < NST; ++s) {
       umma::mbar_init(bar(L::K_FULL + s), 1);
       umma::mbar_init(bar(L::V_FULL + s), 1);
-      umma::mbar_init(bar(L::K_EMPTY + s), 1);
-      umma::mbar_init(bar(L::V_EMPTY + s), 1);
+      for (int x = 0; x < 2; ++x) {
+        umma::mbar_init(bar(L::K_EMPTY + 2 * s + x), 1);
+        umma::mbar_init(bar(L::V_EMPTY + 2 * s + x), 1);
+      }
     }
     for (int x = 0; x < 2; ++x) {
-      umma::mbar_init(bar(L::S_FULL + x), 1);
+      umma::mbar_init(bar(L::S_FULL + 2 * x), 1);
+      umma::mbar_init(bar(L::S_FULL + 2 * x + 1), 1);
+      umma::mbar_init(bar(L::PV_DONE + x), 1);
       umma::mbar_init(bar(L::P_READY + x), 128);
       umma::mbar_init(bar(L::O_FINAL + x), 1);
     }
@@ -123,7 +129,8 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tS[2] = {tmem, tmem + 64 + DV}, tO[2] = {tmem + 64, tmem + 128 + DV};
+  // problem x: score buffers at x * (128 + DV) + {0, 64}, output accumulator behind them
+  const uint32_t tS[2] = {tmem, tmem + 128 + DV}, tO[2] = {tmem + 128, tmem + 256 + DV};
 
   auto give_up = [&]() {
     *s_abort = 1;
@@ -149,7 +156,10 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
       const int full0 = is_k ? L::K_FULL : L::V_FULL, empty0 = is_k ? L::K_EMPTY : L::V_EMPTY;
       for (int j = 0; j < n; ++j) {
         const int st = j % NST;
-        if (j >= NST) WAIT_OR_ABORT(empty0 + st, ((j / NST) - 1) & 1)
+        if (j >= NST) {   // both problems must have released the tile that occupied this stage
+          if (j - NST < nt[0]) WAIT_OR_ABORT(empty0 + 2 * st, ((j / NST) - 1) & 1)
+          if (j - NST < nt[1]) WAIT_OR_ABORT(empty0 + 2 * st + 1, ((j / NST) - 1) & 1)
+        }
         const uint32_t dst = sb + L::OFF_KV + st * L::STAGE + (is_k ? 0 : L::K_BYTES);
         if (is_k) {
           umma::mbar_expect_tx(bar(full0 + st), L::K_BYTES);
@@ -166,68 +176,53 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
         }
       }
     }
-  } else if (warp == 2) {
-    // =============================== MMA issuer ===============================
-    if (lane == 0) {
+  } else if (warp < 4) {
+    // =============================== MMA issuers ===============================
+    // One issuing thread per problem (warp 2: A, warp 3: B) and two score buffers per problem: the scores of
+    // tile j + 1 are issued before the thread waits for the probabilities of tile j, so a softmax warp finds
+    // its next tile ready, and neither problem's waits hold up the other's instructions.
+    const int x = warp - 2;
+    if (lane == 0 && nt[x] > 0) {
       const uint32_t idesc_qk = umma::instr_desc_bf16(BM, BN, false, false);
       const uint32_t idesc_pv = umma::instr_desc_bf16(BM, DV, false, true);
-      auto qk = [&](int x, int st) {     // S_x = Q_x . K^T : contraction over d in steps of 16
-        const uint32_t qbase = sb + (x ? L::OFF_QB : L::OFF_QA), kbase = sb + L::OFF_KV + st * L::STAGE;
+      const uint32_t qbase = sb + (x ? L::OFF_QB : L::OFF_QA);
+      const int nx = nt[x];
+      auto qk = [&](int j) {       // S[j & 1] = Q . K_j^T : contraction over d in steps of 16
+        const int st = j % NST;
+        const uint32_t kbase = sb + L::OFF_KV + st * L::STAGE;
 #pragma unroll
         for (int ks = 0; ks < DQK / 16; ++ks) {
-          const uint32_t oq = (ks >> 2) * Q_SLAB + (ks & 3) * 32, ok = (ks >> 2) * K_SLAB + (ks & 3) * 32;
-          umma::mma_ss(tS[x], umma::smem_desc(qbase + oq, 0, 1024), umma::smem_desc(kbase + ok, 0, 1024),
-                       idesc_qk, ks > 0);
+          const uint32_t oq = (ks >> 2) * Q_SLAB + (ks & 3) * 32, ok2 = (ks >> 2) * K_SLAB + (ks & 3) * 32;
+          umma::mma_ss(tS[x] + (j & 1) * 64, umma::smem_desc(qbase + oq, 0, 1024),
+                       umma::smem_desc(kbase + ok2, 0, 1024), idesc_qk, ks > 0);
         }
+        umma::commit(bar(L::S_FULL + 2 * x + (j & 1)));
+        umma::commit(bar(L::K_EMPTY + 2 * st + x));
       };
-      auto pv = [&](int x, int st, bool first) {   // O_x += P_x . V : contraction over the 64 keys
+      bool ok = umma::mbar_wait(bar(L::Q_FULL), 0, s_abort) && umma::mbar_wait(bar(L::K_FULL + 0), 0, s_abort);
+      if (!ok) give_up();
+      if (ok) {
+        umma::fence_after_sync();
+        qk(0);
+      }
+      for (int j = 0; ok && j < nx; ++j) {
+        const int st = j % NST, ph = (j / NST) & 1;
+        if (j + 1 < nx) {
+          WAIT_OR_ABORT(L::K_FULL + (j + 1) % NST, ((j + 1) / NST) & 1)
+          umma::fence_after_sync();
+          qk(j + 1);
+        }
+        WAIT_OR_ABORT(L::P_READY + x, j & 1)
+        WAIT_OR_ABORT(L::V_FULL + st, ph)
+        umma::fence_after_sync();
         const uint32_t vbase = sb + L::OFF_KV + st * L::STAGE + L::K_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks)
-          umma::mma_ts(tO[x], tS[x] + ks * 8, umma::smem_desc(vbase + ks * 2048, K_SLAB, 1024), idesc_pv,
-                       !(first && ks == 0));
-      };
-      bool ok = umma::mbar_wait(bar(L::Q_FULL), 0, s_abort);
-      if (!ok) give_up();
-      for (int j = 0; ok && j < n; ++j) {
-        const int st = j % NST, ph = (j / NST) & 1;
-        WAIT_OR_ABORT(L::K_FULL + st, ph)
-        umma::fence_after_sync();
-        if (j < nt[0]) {
-          qk(0, st);
-          umma::commit(bar(L::S_FULL + 0));
-        }
-        if (has_b) {
-          if (j > 0) {
-            const int sp = (j - 1) % NST;
-            WAIT_OR_ABORT(L::P_READY + 1, (j - 1) & 1)
-            WAIT_OR_ABORT(L::V_FULL + sp, ((j - 1) / NST) & 1)
-            umma::fence_after_sync();
-            pv(1, sp, j - 1 == 0);
-            umma::commit(bar(L::V_EMPTY + sp));
-          }
-          qk(1, st);
-          umma::commit(bar(L::S_FULL + 1));
-        }
-        umma::commit(bar(L::K_EMPTY + st));
-        if (j < nt[0]) {
-          WAIT_OR_ABORT(L::P_READY + 0, j & 1)
-          WAIT_OR_ABORT(L::V_FULL + st, ph)
-          umma::fence_after_sync();
-          pv(0, st, j == 0);
-          if (!has_b) umma::commit(bar(L::V_EMPTY + st));
-          if (j == nt[0] - 1) umma::commit(bar(L::O_FINAL + 0));
-        }
-      }
-      if (has_b && !*s_abort) {
-        do {
-          const int sp = (n - 1) % NST;
-          WAIT_OR_ABORT(L::P_READY + 1, (n - 1) & 1)
-          WAIT_OR_ABORT(L::V_FULL + sp, ((n - 1) / NST) & 1)
-          umma::fence_after_sync();
-          pv(1, sp, n - 1 == 0);
-          umma::commit(bar(L::O_FINAL + 1));
-        } while (false);
+        for (int ks = 0; ks < BN / 16; ++ks)        // O += P[j & 1] . V_j : contraction over the 64 keys
+          umma::mma_ts(tO[x], tS[x] + (j & 1) * 64 + ks * 8, umma::smem_desc(vbase + ks * 2048, K_SLAB, 1024),
+                       idesc_pv, !(j == 0 && ks == 0));
+        umma::commit(bar(L::PV_DONE + x));
+        umma::commit(bar(L::V_EMPTY + 2 * st + x));
+        if (j == nx - 1) umma::commit(bar(L::O_FINAL + x));
       }
     }
   } else if (warp >= 4) {
@@ -235,7 +230,7 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
     const int x = warp >= 8 ? 1 : 0;                        // problem A or B
     const int row = (warp & 3) * 32 + lane;                 // query row of the problem == tensor-memory lane
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tSx = tS[x] + lane_sel, tOx = tO[x] + lane_sel;
+    const uint32_t tS0 = tS[x] + lane_sel, tOx = tO[x] + lane_sel;
     const int qrow = m0 + x * BM + row;                     // index of the query inside its sequence
     const int lim = min(off + qrow, kmax[x] - 1);           // last visible key
     const int nx = nt[x];
@@ -243,7 +238,8 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
     bool alive = true;
     for (int j = 0; j < nx; ++j) {
       // tensor-memory loads / stores are warp-collective: the whole warp continues or stops together
-      if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(L::S_FULL + x), j & 1, s_abort))) {
+      const uint32_t tSx = tS0 + (j & 1) * 64;                // score buffer of this tile
+      if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(L::S_FULL + 2 * x + (j & 1)), (j >> 1) & 1, s_abort))) {
         give_up();
         alive = false;
         break;
@@ -285,6 +281,13 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
         const float alpha = (m_ref == -INFINITY) ? (need ? 0.f : 1.f) : fast_exp2(m_ref - m_new);
         l *= alpha;
         if (j > 0) {
+          // O still receives P(j-1).V(j-1): the scores of this tile were issued ahead of that product
+          if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(L::PV_DONE + x), (j - 1) & 1, s_abort))) {
+            give_up();
+            alive = false;
+            break;
+          }
+          umma::fence_after_sync();
 #pragma unroll 1
           for (int c = 0; c < DV / 32; ++c) {
             uint32_t r[32];
