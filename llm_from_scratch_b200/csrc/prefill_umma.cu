@@ -1,4 +1,6 @@
 // Ragged causal prefill attention, bf16, head_dim 128, on the Blackwell tensor cores (tcgen05).
+// Packed keys are served faster by prefill_umma2.cu (see the dispatch in prefill_varlen.cu); this kernel
+// runs when part of the context comes from the paged pool.
 //
 // One CTA owns a 128-row query tile of TWO query heads that share a KV head (grouped-query
 // attention), so every K/V tile staged in shared memory feeds two independent attention problems

@@ -1,7 +1,6 @@
-// Ragged causal prefill attention on the Blackwell tensor cores (tcgen05) for the head shapes the
-// two-heads-per-CTA kernel of prefill_umma.cu does not take: 192/128 (the expanded form of multi-head
-// latent attention, MLA.py:131, with the rotary key part read from a tensor shared by all heads or from
-// the key tensor itself) and 128/128 with an odd group size.  Packed keys/values only.
+// Ragged causal prefill attention on the Blackwell tensor cores (tcgen05) over packed keys/values, head
+// dims 128/128 (any group size) and 192/128 (the expanded form of multi-head latent attention, MLA.py:131,
+// with the rotary key part read from a tensor shared by all heads or from the key tensor itself).
 //
 // One CTA owns 256 consecutive query rows of ONE head: two 128-row problems A (rows 0-127) and B
 // (rows 128-255) that walk the same K/V tiles of 64 keys, so a tile staged in shared memory is used
@@ -10,13 +9,18 @@
 //
 //   warp 0      K producer (+ both Q tiles): one thread issuing TMA tile copies (128-byte swizzle)
 //   warp 1      V producer
-//   warp 2      tensor-memory allocation; lane 0 issues every tcgen05.mma
+//   warp 2      tensor-memory allocation; lane 0 issues the tcgen05.mma of problem A
+//   warp 3      lane 0 issues the tcgen05.mma of problem B
 //   warps 4-7   softmax of A: one thread per query row, the 64 scores of a tile held in registers
 //   warps 8-11  softmax of B
 //
-// Tensor memory per problem: S 128 x 64 fp32 (bf16 P overwrites its first 32 columns and is the A
-// operand of O += P.V) and O 128 x DV fp32.  K/V tiles go through a ring of NST stages.  Rescaling of
-// O is lazy as in prefill_umma.cu.  Every wait is bounded; a timeout aborts the CTA and is reported.
+// Tensor memory per problem (256 columns): two score buffers S 128 x 64 fp32 (bf16 P overwrites the first
+// 32 columns of its buffer and is the A operand of O += P.V) and O 128 x DV fp32.  Each issuing thread puts
+// the scores of tile j + 1 into the other buffer before it waits for the probabilities of tile j, so the
+// softmax warps (which set the pace: the tensor pipe needs less than half of an iteration) find their next
+// tile ready, and one problem's waits never hold up the other's instructions.  K/V tiles go through a ring
+// of NST stages that both problems release.  Rescaling of O is lazy as in prefill_umma.cu and waits for the
+// P.V product before it.  Every wait is bounded; a timeout aborts the CTA and is reported.
 #include <cuda.h>
 
 #include "common.cuh"

@@ -112,7 +112,7 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
                        const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
                        cudaStream_t s, const void* k_tail = nullptr, int64_t k_tail_stride = 0, int tail = 0);
 
-// tcgen05 path for the other head shapes (prefill_umma2.cu): packed keys/values, 256 query rows of one head per CTA
+// tcgen05 path for packed keys/values (prefill_umma2.cu): head dims 128/128 and 192/128, 256 query rows of one head per CTA
 int prefill_umma2_tile_rows(int Hq, int Hkv, int Dqk, int Dv);
 int prefill_umma2_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride, int64_t k_stride,
                          int64_t v_stride, int64_t total_q, int64_t total_k, const int32_t* cu_q,
@@ -120,7 +120,7 @@ int prefill_umma2_launch(const void* q, const void* k, const void* v, void* out,
                          float scale, const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
                          cudaStream_t s, const void* k_tail, int64_t k_tail_stride, int tail);
 
-// tcgen05 path (prefill_umma.cu): head_dim 128, even group size
+// tcgen05 path for a paged prefix (prefill_umma.cu): head_dim 128, even group size, two heads per CTA
 int prefill_umma_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride,
                         int64_t k_stride, int64_t v_stride, int64_t total_q, int64_t total_k,
                         const int32_t* cu_q, const int32_t* cu_k,
