@@ -373,6 +373,28 @@ def test_prefill_row_pair_kernel_long_ragged_batch(Hq, Hkv, Dqk, Dv):
     assert torch.equal(planned, got)
 
 
+@pytest.mark.parametrize("Hq,Hkv,Dqk,Dv", [(4, 4, 192, 128), (4, 2, 128, 128)])
+def test_prefill_row_pair_kernel_scores_that_outgrow_the_reference_maximum(Hq, Hkv, Dqk, Dv):
+    """After a row's first key tile the kernel forms probabilities against the reference maximum the row
+    already has and only looks for a new maximum when a tile's sum shows that it is needed: keys whose
+    scores lie far above everything before them (here from position 100 on, then again from 900 on) must
+    take that path and still give the oracle's result."""
+    ops = _ops()
+    lens = [1300, 257, 90]
+    q, k, v, cu = _prefill_inputs(lens, Hq, Hkv, Dqk, Dv, torch.bfloat16, seed=91)
+    pos = torch.cat([torch.arange(n) for n in lens])
+    k = (k.float() * torch.where(pos >= 900, 60.0, torch.where(pos >= 100, 25.0, 1.0)).view(-1, 1, 1)).to(torch.bfloat16)
+    scale = Dqk ** -0.5
+    want = _oracle().prefill_varlen(q, k, v, cu, cu, scale)
+    got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), scale)
+    ops.check_status()
+    assert torch.isfinite(got.float()).all()
+    # nearly one-hot probabilities put a whole value row (|v| up to 4.5) behind one bf16 rounding of P and one
+    # of the output: the bound is two bf16 steps of that magnitude, the mean error stays far below it
+    err = (got.float().cpu() - want.float()).abs()
+    assert err.max().item() <= 5e-2 and err.mean().item() <= 3e-3, (err.max().item(), err.mean().item())
+
+
 # ----------------------------------------------------------------------------- MLA decode
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("H,r,dr", [(16, 512, 64), (8, 128, 32), (16, 256, 16)])
