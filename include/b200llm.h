@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 8
+#define B200_ABI_VERSION 9
 
 #define B200_DTYPE_F32 0
 #define B200_DTYPE_BF16 1
@@ -373,6 +373,18 @@ int b200_block_table_patch(const int32_t* patches, int32_t count, int32_t* block
 int b200_sample(const void* logits, int64_t row_stride, const float* temperatures, int64_t num_rows,
                 int32_t vocab_size, uint64_t seed, uint64_t offset, int64_t* out_tokens, int32_t dtype,
                 void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Diagnostic (no counterpart in the reference, which has no device code): runs the give-up path of the
+ * bounded barrier waits that the tcgen05 / TMA kernels share.  One CTA holds tensor memory, arms a barrier
+ * that can never complete, and waits on it from two threads: one with `poll_limit` polls (1..65536), one
+ * with the kernels' default limit.  Nothing faults and nothing loops without bound.  Afterwards
+ *   result[0] = 0 and result[1] = poll_limit : the short wait ran out at its limit,
+ *   result[2] = 0 and result[3] < 2^22       : the other wait left through the CTA's abort flag,
+ *   result[4] = 1                            : tensor memory was allocated and has been freed,
+ * and *status holds B200_ERR_TIMEOUT (read and clear it with b200_read_status).  result: device int32[5].
+ * ------------------------------------------------------------------------------------------- */
+int b200_selftest_bounded_wait(int32_t poll_limit, int32_t* result, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -201,20 +201,27 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tenso
 
 // Waits for the phase with the given parity to complete.  Bounded: gives up after `limit` polls
 // (each poll may itself suspend for a short hardware-defined time) or as soon as `*abort_flag`
-// (shared memory) is set by another thread, and returns false.
+// (shared memory) is set by another thread, and returns false.  `polls_out` (diagnostics; may be
+// null) receives the number of polls made.
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volatile int* abort_flag,
-                                          int limit = 1 << 22) {
-  for (int it = 0; it < limit; ++it) {
+                                          int limit = 1 << 22, int* polls_out = nullptr) {
+  int it = 0;
+  bool ok = false;
+  for (; it < limit; ++it) {
     uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
         : "r"(mbar), "r"(parity)
         : "memory");
-    if (done) return true;
-    if ((it & 63) == 63 && *abort_flag) return false;
+    if (done) {
+      ok = true;
+      break;
+    }
+    if ((it & 63) == 63 && *abort_flag) break;
   }
-  return false;
+  if (polls_out != nullptr) *polls_out = it;
+  return ok;
 }
 
 }  // namespace umma

@@ -23,7 +23,10 @@ workloads whose pool never runs dry (outside that the reference raises or drops 
 The default keeps the same allocation order and hashing but counts references from 1, so blocks
 are released exactly when their last user finishes, released blocks keep their contents and can be
 revived by a later prefix hit, and ``can_append`` asks for a free block on the same step on which
-``append`` takes one.
+``append`` takes one.  A prefix hit never covers the whole prompt: when every block of a prompt whose
+length is a multiple of the block size is cached, the last block is recomputed, so that the prefill
+step has at least one query token per sequence (the reference would emit none and sample the
+request's first token from another sequence's logits).
 """
 from __future__ import annotations
 
@@ -149,11 +152,14 @@ class BlockManager:
         blocks, free, used, h2b = self.blocks, self._free, self.used_block_ids, self.hash_to_block_id
         table = seq.block_table
         cached = 0
+        total = len(ids)
         for i in range(seq.num_blocks):
             token_ids = ids[i * bs:(i + 1) * bs]
             h = chain[i] if len(token_ids) == bs else -1
             block_id = h2b.get(h, -1)
-            if block_id != -1 and blocks[block_id].token_ids == token_ids:
+            # a hit on the block that ends the prompt would leave no token to run through the model (the
+            # step samples from the last prompt token's logits): that block is recomputed into a fresh one
+            if block_id != -1 and blocks[block_id].token_ids == token_ids and cached + bs < total:
                 cached += bs
                 block = blocks[block_id]
                 if block_id in used:

@@ -16,6 +16,7 @@ _DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
 
 _status: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, str], torch.Tensor] = {}
+_retired_workspaces: list[torch.Tensor] = []   # outgrown buffers that captured graphs may still address
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -61,12 +62,41 @@ def check_status(device: torch.device | None = None) -> None:
         check(host[0], "device-side check")
 
 
+def selftest_bounded_wait(poll_limit: int = 1024, device: torch.device | None = None) -> list[int]:
+    """Diagnostic: makes a bounded barrier wait run out inside one small CTA (``b200_selftest_bounded_wait``).
+    Returns the five result words; the device status word then holds the time-out code, so the next
+    ``check_status`` raises (``read_status_code`` reads and clears it without raising)."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    result = torch.full((5,), -1, dtype=torch.int32, device=device)
+    check(lib.b200_selftest_bounded_wait(poll_limit, result.data_ptr(), status_word(device).data_ptr(), _stream()),
+          "selftest_bounded_wait")
+    return result.tolist()
+
+
+def read_status_code(device: torch.device | None = None) -> int:
+    """Synchronises the current stream and returns (and clears) the device status word: 0 or a B200_ERR_* code."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    host = array.array("i", [0])
+    addr, _ = host.buffer_info()
+    check(lib.b200_read_status(status_word(device).data_ptr(), addr, _stream()), "read_status")
+    return host[0]
+
+
 def workspace(device: torch.device, nbytes: int, tag: str) -> torch.Tensor:
-    """Grow-only scratch buffer per (device, op); allocated outside any graph capture."""
+    """Scratch buffer per (device, op); allocated outside any graph capture.
+
+    A captured CUDA graph has the address of the buffer it was captured with baked in, so a buffer
+    that has been handed out is never freed: when a later call needs more, a larger one (at least
+    twice the size, so all retired buffers together stay below the live one) replaces it for new
+    calls and the old one is kept alive for the graphs that still write to it.  No kernel keeps
+    state in its scratch between calls, so old and new buffers can be in use side by side."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (idx, tag)
     w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
+        if w is not None:
+            _retired_workspaces.append(w)
+            nbytes = max(nbytes, 2 * w.numel())
         w = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
         _workspaces[key] = w
     return w

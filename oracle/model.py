@@ -131,15 +131,18 @@ class OracleModel:
         W = self.w[p + ".kv_up_proj_fused.weight"]
         w_uk = W[:self.d].view(H, hd, r)
         w_uv = W[self.d:].view(H, hd, r)
-        q_abs = torch.einsum("qhd,hdk->qhk", q_nope, w_uk)
-        score = torch.einsum("qhk,tk->hqt", q_abs, ckv) + torch.einsum("qhd,td->hqt", q_rope, cpe)
+        # the reference's einsums carry a batch axis (MLA.py:153-178); it is kept (size 1) because the CPU
+        # bf16 kernels behind einsum pick their blocking by operand shape, and outputs are compared bit for bit
+        q_abs = torch.einsum("bqhd,hdk->bqhk", q_nope.unsqueeze(0), w_uk)
+        score = torch.einsum("bqhk,btk->bhqt", q_abs, ckv.unsqueeze(0)) + \
+            torch.einsum("bqhd,btd->bhqt", q_rope.unsqueeze(0), cpe.unsqueeze(0))
         score = score / (hd + dr) ** 0.5
         if mask is not None:
             full = torch.ones(L, total, dtype=torch.bool)
             full[:, :L] = mask
-            score = score.masked_fill(~full.unsqueeze(0), float("-inf"))
-        lat = torch.einsum("hqt,tk->hqk", F.softmax(score, dim=-1), ckv)
-        o = torch.einsum("hqk,hdk->qhd", lat, w_uv)
+            score = score.masked_fill(~full.view(1, 1, L, total), float("-inf"))
+        lat = torch.einsum("bhqt,btk->bhqk", F.softmax(score, dim=-1), ckv.unsqueeze(0))
+        o = torch.einsum("bhqk,hdk->bqhd", lat, w_uv)[0]
         return self._lin(o.contiguous().view(L, -1), p + ".output_proj")
 
     # ------------------------------------------------------------------ model

@@ -10,7 +10,7 @@ Called from make_golden.py (build container only).  Writes:
   c1_model.npz     the fp32 GQA+SwiGLU decoder of the first benchmark configuration, seed 0:
                    8 prompts, 64 greedy tokens each, last-step logits, parameter checksums
   moe_model.npz    a small GQA+MoE decoder (fp32 and CPU-autocast bf16 logits)
-  mla_model.npz    a small MLA+MoE decoder
+  mla_model.npz    a small MLA+MoE decoder (the same)
 """
 from __future__ import annotations
 
@@ -160,10 +160,9 @@ def write_small_model(name, att):
         t, lg = _greedy(model, p, 12)
         streams.append(t)
         last.append(_np(lg))
-        if att == "GQA":
-            tb, lb = _greedy(model, p, 12, autocast=True)
-            streams_bf.append(tb)
-            last_bf.append(_np(lb))
+        tb, lb = _greedy(model, p, 12, autocast=True)
+        streams_bf.append(tb)
+        last_bf.append(_np(lb))
     extra = {}
     if streams_bf:
         extra = dict(streams_bf16=np.array(streams_bf), last_logits_bf16=np.stack(last_bf))

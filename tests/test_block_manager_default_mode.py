@@ -149,3 +149,31 @@ def test_default_mode_invariants_under_pressure(reqs, num_blocks):
     assert sched.is_finished()
     assert all(s.is_finished and s.num_completion_tokens == s.max_tokens - 1 for s in all_seqs)
     assert sched.block_manager.num_free_blocks == num_blocks
+
+
+def test_a_fully_cached_prompt_still_has_a_token_to_run():
+    """A repeated prompt whose length is a multiple of the block size hits on every block; the last block is
+    recomputed into a fresh one so that the prefill step has a query token (and a logits row) for the request."""
+    bm = BlockManager(8, 16)
+    a, b = Sequence(list(range(32))), Sequence(list(range(32)))
+    bm.allocate(a)
+    bm.allocate(b)
+    assert a.num_cached_tokens == 0 and b.num_cached_tokens == 16
+    assert b.block_table[0] == a.block_table[0] and b.block_table[1] != a.block_table[1]
+    check_pool(bm, [a, b])
+    md = metadata.prepare_prefill([a, b], 16)
+    assert md.cu_seqlens_q.tolist() == [0, 32, 48] and md.cu_seqlens_k.tolist() == [0, 32, 64]
+    assert md.last_token_index.tolist() == [31, 47]
+    assert md.slot_mapping[32:].tolist() == [b.block_table[1] * 16 + i for i in range(16)]
+    # a single-block prompt repeated: nothing may be reused
+    c, d = Sequence(list(range(100, 116))), Sequence(list(range(100, 116)))
+    bm.allocate(c)
+    bm.allocate(d)
+    assert d.num_cached_tokens == 0 and d.block_table != c.block_table
+    # a longer prompt sharing the same first two blocks reuses both
+    e = Sequence(list(range(40)))
+    bm.allocate(e)
+    assert e.num_cached_tokens == 32
+    for s in (a, b, c, d, e):
+        bm.deallocate(s)
+    check_pool(bm, [])

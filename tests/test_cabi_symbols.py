@@ -29,7 +29,8 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} declared in b200llm.h but not exported"
     assert set(_lib.SIGNATURES) == set(declared_functions())
-    assert _lib.lib.b200_abi_version() == 8
+    want = int(re.search(r"#define\s+B200_ABI_VERSION\s+(\d+)", open(HEADER).read()).group(1))
+    assert _lib.lib.b200_abi_version() == want >= 9
     assert _lib.lib.b200_strerror(-3) == b"unsupported shape or dtype"
 
 

@@ -260,3 +260,97 @@ def test_decode_windows_give_the_step_by_step_streams(kind):
     assert streams[4] == streams[1]
     assert [len(s) for s in streams[1]] == [m - 1 for m in (40, 7, 23, 2, 31, 40, 12, 35)]
     assert steps[4] < steps[1] / 2          # far fewer scheduling decisions
+
+
+def test_decode_window_with_a_stop_token_inside_a_window_leaves_the_same_pool():
+    """decode_window = 8, block size 16: one request meets its stop token in the middle of a window while others
+    cross a block boundary in the same window and others run out of max_tokens; streams, the free list (in
+    order) and the reference counts at the end equal those of the step-by-step loop."""
+    from llm_from_scratch_b200.engine import SamplingParams
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    cfg = dict(C1, num_layers=2)
+    weights = init_reference_order(ModelConfig.from_dict(cfg), 3)
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, cfg["vocab_size"], (int(n),), generator=g).tolist() for n in (12, 30, 47, 9, 61, 14)]
+    limits = (40, 21, 33, 6, 29, 40)
+    probe = make_engine(cfg, weights, eager=False, max_num_batched_tokens=512)
+    free_run = probe.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=True) for m in limits])
+    probe.exit()
+    stop = free_run["token_ids"][0][12]            # request 0 stops at its 13th token: inside the second window
+    assert stop not in free_run["token_ids"][0][:12]
+    sps = [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=False) for m in limits]
+    result = {}
+    for window in (1, 8):
+        eng = make_engine(cfg, weights, eager=False, max_num_batched_tokens=512, decode_window=window, eos=stop)
+        streams = eng.generate(prompts, sps)["token_ids"]
+        bm = eng.scheduler.block_manager
+        result[window] = (streams, list(bm.free_block_ids), [b.ref_count for b in bm.blocks], sorted(bm.used_block_ids))
+        eng.exit()
+    from llm_from_scratch_b200 import ops
+    ops.check_status()
+    assert result[8][0] == result[1][0]
+    assert len(result[1][0][0]) == 13 and result[1][0][0][-1] == stop
+    assert result[8][3] == result[1][3] == [] and result[8][2] == result[1][2]
+    assert sorted(result[8][1]) == sorted(result[1][1])
+
+
+def test_a_repeated_block_multiple_prompt_decodes_like_a_cold_run():
+    """The same 32-token prompt (two full blocks) sent twice: the second request hits on the first block only
+    (the last block of a fully cached prompt is recomputed), runs at least one token through the model, and
+    produces the cold run's tokens — alone in its step and packed with another request."""
+    from llm_from_scratch_b200.engine import SamplingParams
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    weights = init_reference_order(ModelConfig.from_dict(C1), 0)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, 10000, (32,), generator=g).tolist()
+    other = torch.randint(0, 10000, (21,), generator=g).tolist()
+    cold = make_engine(C1, weights)
+    want, _ = greedy_run(cold, [prompt], 8)
+    eng = make_engine(C1, weights)
+    first, _ = greedy_run(eng, [prompt], 8)
+    assert first == want
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    again = eng.add_request(prompt, sp)                       # alone in its prefill step
+    batch, is_prefill = eng.scheduler.schedule()
+    assert is_prefill and batch == [again] and again.num_cached_tokens == 16
+    eng.scheduler.postprocess(batch, eng.model_runner.run_logits(batch, True).argmax(-1).tolist())
+    third, fourth = eng.add_request(other, sp), eng.add_request(prompt, sp)   # packed behind another request
+    while not eng.is_finished():
+        batch, is_prefill = eng.scheduler.schedule()
+        eng.scheduler.postprocess(batch, eng.model_runner.run_logits(batch, is_prefill).argmax(-1).tolist())
+    assert again.completion_token_ids == want[0] and fourth.completion_token_ids == want[0]
+    assert len(third.completion_token_ids) == 8
+
+
+def test_scratch_outgrown_after_graph_capture_does_not_disturb_the_graphs():
+    """Graphs are captured with the scratch buffers of their batch sizes; a later eager decode call that needs
+    more scratch gets a new buffer while the old one stays alive for the graphs: replays before and after the
+    larger call give the same tokens."""
+    from llm_from_scratch_b200 import ops
+    from llm_from_scratch_b200.engine import SamplingParams
+    from llm_from_scratch_b200.model import ModelConfig, init_reference_order
+    from llm_from_scratch_b200.workloads import deal_blocks
+    cfg = dict(vocab_size=500, context_length=256, d_model=256, num_layers=2, num_heads=4, num_kv_heads=2, d_ff=192,
+               attention_type="GQA", use_moe=True, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1)
+    weights = init_reference_order(ModelConfig.from_dict(cfg), 5)
+    g = torch.Generator().manual_seed(14)
+    prompts = [torch.randint(0, 500, (int(n),), generator=g).tolist() for n in (40, 7, 90)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    eng = make_engine(cfg, weights, dtype=torch.bfloat16, eager=False, max_num_batched_tokens=512)
+    before = eng.generate(prompts, sp)["token_ids"]
+    held = dict(ops._workspaces)
+    # an eager decode call on the same device with far more sequences than any captured bucket
+    case = deal_blocks([33] * 3000, 16, np.random.default_rng(0))
+    kc = torch.randn(case.num_blocks, 16, 2, 64, device="cuda").bfloat16()
+    q = torch.randn(3000, 4, 64, device="cuda").bfloat16()
+    ops.paged_decode_gqa(q, kc, kc, torch.from_numpy(case.block_tables).cuda(),
+                         torch.from_numpy(case.context_lens).cuda(), 0.125)
+    torch.cuda.synchronize()
+    grown = [k for k, w in ops._workspaces.items() if k in held and w.data_ptr() != held[k].data_ptr()]
+    assert grown, "the larger call was expected to outgrow a scratch buffer"
+    assert all(any(r.data_ptr() == held[k].data_ptr() for r in ops._retired_workspaces) for k in grown)
+    junk = torch.full((64 << 20,), 0x7f, dtype=torch.uint8, device="cuda")   # would land in freed scratch, if any were freed
+    after = eng.generate(prompts, sp)["token_ids"]
+    del junk
+    eng.exit()
+    assert after == before

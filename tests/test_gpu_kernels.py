@@ -748,21 +748,9 @@ def test_moe_route_many_ctas_is_a_stable_counting_sort():
 
 
 def _grouped_reference(x, w, offs, bias, swiglu):
-    """Per-expert fp32 matmuls with the bf16 roundings of the tensor-op sequence."""
-    import torch.nn.functional as Fn
-    E = w.shape[0]
-    n_out = w.shape[1] // 2 if swiglu else w.shape[1]
-    out = torch.zeros(x.shape[0], n_out, dtype=torch.bfloat16, device=x.device)
-    lo = 0
-    for e in range(E):
-        hi = int(offs[e])
-        if hi > lo:
-            h = (x[lo:hi].float() @ w[e].float().t()).bfloat16()
-            if bias is not None:
-                h = h + bias[e]
-            out[lo:hi] = Fn.silu(h[:, :n_out]) * h[:, n_out:] if swiglu else h
-        lo = hi
-    return out
+    """The CPU oracle's per-expert loop (fp32 products on the host, bf16 roundings of the tensor-op sequence)."""
+    from oracle.moe import grouped_linear
+    return grouped_linear(x, w, offs.cpu().tolist(), bias, swiglu).to(x.device)
 
 
 @pytest.mark.parametrize("counts,k,n,swiglu", [
@@ -963,3 +951,32 @@ def test_mla_prefill_benchmark_step_sampled_sequences():
         one = torch.tensor([0, b - a], dtype=torch.int32)
         want = _oracle().prefill_varlen(q[a:b].cpu(), k_full, v[a:b].cpu(), one, one, scale)
         assert_close(out[a:b], want, torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- bounded waits
+def test_a_barrier_wait_that_runs_out_is_reported_and_leaves_the_device_usable():
+    """The give-up path shared by the tcgen05 / TMA kernels, run on purpose by the diagnostic entry point: a wait
+    with a short poll limit times out, the CTA's other waiter leaves through the abort flag, tensor memory is
+    freed, the status word reads B200_ERR_TIMEOUT — and the kernels that allocate all 512 tensor-memory
+    columns of an SM run correctly right afterwards on every SM."""
+    from oracle import attention as orc
+    ops = _ops()
+    ops.check_status()
+    for limit in (64, 1000):
+        res = ops.selftest_bounded_wait(limit)
+        assert res[0] == 0 and res[1] == limit, res          # ran out exactly at its limit
+        assert res[2] == 0 and 0 < res[3] < (1 << 22), res   # left early, through the flag
+        assert res[4] == 1, res
+        assert ops.read_status_code() == -9                  # B200_ERR_TIMEOUT, and the word is cleared
+        assert ops.read_status_code() == 0
+    # a tcgen05 prefill on every SM (300 CTAs of 512 tensor-memory columns each) still runs and is right
+    Hq, Hkv, D = 8, 2, 128
+    lens = [700, 1, 333, 2048, 129]
+    T = sum(lens)
+    q, k, v = (_randn((T, h, D), 50 + i, torch.bfloat16) for i, h in enumerate((Hq, Hkv, Hkv)))
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), D ** -0.5)
+    ops.check_status()
+    rows = torch.tensor([0, 699, 700, 701, 1033, 1034, 2000, T - 130, T - 1])
+    want = orc.prefill_varlen(q, k, v, cu, cu, D ** -0.5)
+    assert (got.float().cpu()[rows] - want[rows]).abs().max().item() <= 2e-2
