@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the paged GQA decode attention step on B200.
+"""Benchmark of the continuous-batching decode path on B200; the headline is the paged GQA decode attention step.
 
 Workload (per GPU): 256 sequences, context lengths log-uniform in [128, 8192], 32 query heads,
 8 KV heads, head_dim 128, KV block size 16, bf16; the physical pool is a random permutation of
@@ -15,6 +15,15 @@ decode-attention call over the whole batch (one new token per sequence).
   roofline  algorithmic bytes of one call / its measured duration, against the measured HBM copy
             peak of this pool's B200s.
 
+  secondary the other kernels of the path on their benchmark shapes (store_kvcache, ragged prefill with the
+            scatter, MLA decode, MLA prefill, MoE expert GEMMs), timed in this process, each with its algorithmic
+            bytes or FLOPs and the fraction of the measured peak; 1 GPU only
+  engine    the GQA+MoE decoder through the engine on the 2048-request continuous-batching job: output tokens/s,
+            wall time per decode step, and the decode steps' fraction of the HBM roofline from the live contexts.
+            Under torchrun both the fixed job (2048 requests over all replicas) and the weak job (2048 per replica)
+
+The step region is timed ``REGIONS`` times; ms_per_step is the median region, min and max are reported beside it.
+
 ``--impl reference`` times the CPU oracle (the reference's fp32 torch arithmetic applied to the
 gathered pool) on the host cores instead.  With N > 1 (torchrun) every rank runs an independent
 replica of the workload on its own GPU: requests shard, nothing is exchanged.
@@ -24,6 +33,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import subprocess
 import sys
 import threading
 import time
@@ -36,6 +46,9 @@ sys.path.insert(0, ROOT)
 
 HQ, HKV, D, BS, BATCH = 32, 8, 128, 16, 256
 CPU_SAMPLE_SEQS = 64
+DECODE_KERNEL = "paged_decode_bf16_kernel<128,1> (+ combine, timed together)"
+DECODE_LAUNCHES_PER_CALL = 2
+REGIONS = 5   # the --steps region is timed this many times; the median is reported
 # DRAM bytes read + written by one ncu-captured launch of the decode kernel over 130,732 context tokens
 NCU_DRAM_BYTES_PER_CONTEXT_TOKEN = (536_459_520 + 4_956_544) / 130_732
 
@@ -134,6 +147,117 @@ def time_cpu_oracle(sample, repeats=1):
     return best
 
 
+def bf16_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def reference_arm(args, case, config, n_gpus):
+    """The reference's CPU arithmetic for this step (gather + fp32 softmax attention) on a bounded sample of
+    the same workload; inputs synthesised on the host.  Prints the JSON line."""
+    torch.set_num_threads(os.cpu_count() or 1)   # torchrun pins OMP_NUM_THREADS=1; use every host core
+    g = torch.Generator().manual_seed(1)
+    nseq = CPU_SAMPLE_SEQS
+    lens = case.context_lens[:nseq]
+    nblk = int(((lens + BS - 1) // BS).sum())
+    k_host = torch.randn(nblk, BS, HKV, D, generator=g).to(torch.bfloat16)
+    v_host = torch.randn(nblk, BS, HKV, D, generator=g).to(torch.bfloat16)
+    q_host = torch.randn(nseq, HQ, D, generator=g).to(torch.bfloat16)
+    tables, pos = [], 0
+    for i in range(nseq):
+        n = int((lens[i] + BS - 1) // BS)
+        tables.append(list(range(pos, pos + n)))
+        pos += n
+    sample = (q_host, k_host, v_host, tables, lens)
+    # all requested steps unless that would run for more than ~2.5 minutes on these cores: every
+    # step repeats the same bounded sample, so fewer steps change the noise, not the figure
+    t0 = time.perf_counter()
+    time_cpu_oracle(sample)
+    est = time.perf_counter() - t0
+    warm = max(0, min(args.warmup, 3) - 1)
+    for _ in range(warm):
+        time_cpu_oracle(sample)
+    steps = max(1, min(args.steps, int(150.0 / max(est, 1e-3))))
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        time_cpu_oracle(sample)
+        times.append(time.perf_counter() - t0)
+    dt = float(np.median(times))
+    val = nseq / dt
+    cores = torch.get_num_threads()
+    desc = f"first {nseq} of the {BATCH} sequences ({int(lens.sum())} context tokens) per step, median of {steps} steps"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode tokens/s", "value": val, "unit": "tokens/s",
+        "n_gpus": n_gpus, "steps": steps, "warmup": warm + 1, "requested_steps": args.steps,
+        "ms_per_step": 1e3 * dt, "ms_per_step_min": 1e3 * min(times), "ms_per_step_max": 1e3 * max(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": desc},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def cpu_leg_in_a_fresh_process(batch: int):
+    """The CPU baseline of the b200 arm: the reference arm itself (same function, same sample), run in a process of
+    its own before this one touches CUDA, so that neither pinned-memory, NVML nor CUDA runtime threads share the
+    host cores with it.  Returns the parsed line, or a dict with 'error'."""
+    env = {k: v for k, v in os.environ.items() if k not in ("OMP_NUM_THREADS", "MKL_NUM_THREADS")}
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        env.pop(k, None)
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--gpus", "1", "--steps", "5",
+           "--warmup", "3", "--batch", str(batch)]
+    try:
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        for ln in reversed(r.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+        return {"error": (r.stderr or r.stdout)[-300:]}
+    except Exception as e:   # noqa: BLE001 - the baseline is reported, never needed
+        return {"error": repr(e)}
+
+
+def secondary_kernels(steps_scale: float = 1.0) -> dict:
+    """The other kernels of the path on their benchmark shapes, each with its roofline fraction."""
+    from llm_from_scratch_b200 import microbench
+    hbm, hbm_kind = hbm_peak()
+    burst, sustained, tf_kind = bf16_peaks()
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops_burst": burst, "bf16_tflops_sustained": sustained,
+                     "kind": f"of {hbm_kind}"}}
+
+    def hbm_bound(res):
+        res["roofline"] = {"bound": "hbm", "achieved": res["gbs"], "peak": hbm, "unit": "GB/s", "frac": res["gbs"] / hbm}
+        return res
+
+    def tensor_bound(res, tflops):
+        res["roofline"] = {"bound": "tensor", "achieved": tflops, "peak": burst, "unit": "TFLOP/s",
+                           "frac": tflops / burst, "frac_of_sustained": tflops / sustained}
+        return res
+
+    n = lambda k: max(3, int(k * steps_scale))
+    out["store"] = hbm_bound(microbench.store(steps=n(50), warmup=5))
+    torch.cuda.empty_cache()
+    pf = microbench.prefill(steps=n(5), warmup=3)
+    pf["lengths"] = pf.pop("lengths")          # realised lengths of the 64 sequences, longest first
+    out["prefill"] = tensor_bound(pf, pf["tflops"])
+    out["prefill"]["attention_only_frac"] = pf["attention_only_tflops"] / burst
+    torch.cuda.empty_cache()
+    out["mla_decode"] = hbm_bound(microbench.mla_decode(steps=n(50), warmup=5))
+    torch.cuda.empty_cache()
+    mp = microbench.mla_prefill(steps=n(20), warmup=3)
+    out["mla_prefill"] = tensor_bound(mp, mp["tflops"])
+    torch.cuda.empty_cache()
+    out["moe_experts"] = hbm_bound(microbench.moe_experts(steps=n(20), warmup=3))
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     global BATCH, CPU_SAMPLE_SEQS
     ap = argparse.ArgumentParser()
@@ -143,6 +267,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg (profiling runs)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary kernels (profiling runs)")
+    ap.add_argument("--no-engine", action="store_true", help="skip the engine job (profiling runs)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "mla_prefill", "store", "moe_experts", "engine", "engine_mla", "engine_step"],
                     help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
                          "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
@@ -194,51 +320,14 @@ def main():
               "parallelism": f"replicas x{n_gpus} (requests shard, no collective)"}
 
     if args.impl == "reference":
-        if rank != 0:
-            return
-        torch.set_num_threads(os.cpu_count() or 1)   # torchrun pins OMP_NUM_THREADS=1; use every host core
-        # The reference's CPU arithmetic for this step (gather + fp32 softmax attention) on a
-        # bounded sample of the same workload; inputs synthesised on the host.
-        g = torch.Generator().manual_seed(1)
-        nseq = CPU_SAMPLE_SEQS
-        lens = case.context_lens[:nseq]
-        nblk = int(((lens + BS - 1) // BS).sum())
-        k_host = torch.randn(nblk, BS, HKV, D, generator=g).to(torch.bfloat16)
-        v_host = torch.randn(nblk, BS, HKV, D, generator=g).to(torch.bfloat16)
-        q_host = torch.randn(nseq, HQ, D, generator=g).to(torch.bfloat16)
-        tables, pos = [], 0
-        for i in range(nseq):
-            n = int((lens[i] + BS - 1) // BS)
-            tables.append(list(range(pos, pos + n)))
-            pos += n
-        sample = (q_host, k_host, v_host, tables, lens)
-        # all requested steps unless that would run for more than ~2.5 minutes on these cores: every
-        # step repeats the same bounded sample, so fewer steps change the noise, not the figure
-        t0 = time.perf_counter()
-        time_cpu_oracle(sample)
-        est = time.perf_counter() - t0
-        warm = max(0, min(args.warmup, 3) - 1)
-        for _ in range(warm):
-            time_cpu_oracle(sample)
-        steps = max(1, min(args.steps, int(150.0 / max(est, 1e-3))))
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            time_cpu_oracle(sample)
-        dt = time.perf_counter() - t0
-        val = nseq * steps / dt
-        cores = torch.get_num_threads()
-        desc = f"first {nseq} of the {BATCH} sequences ({int(lens.sum())} context tokens) per step"
-        print(json.dumps({
-            "impl": "reference", "metric": "decode tokens/s", "value": val, "unit": "tokens/s",
-            "n_gpus": n_gpus, "steps": steps, "warmup": warm + 1, "requested_steps": args.steps,
-            "ms_per_step": 1e3 * dt / steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config,
-            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
-                             "sample": desc},
-            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }))
+        if rank == 0:
+            reference_arm(args, case, config, n_gpus)
         return
+
+    # the CPU baseline runs first, in a process of its own, while this process has not touched CUDA yet
+    cpu_line = None
+    if n_gpus == 1 and not args.no_cpu_baseline:
+        cpu_line = cpu_leg_in_a_fresh_process(BATCH)
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the b200 arm")
@@ -273,6 +362,25 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_regions(step_fn, wall: bool):
+        """REGIONS x args.steps calls of step_fn; per region the device time between two events on the launching
+        stream (and, for the host-input leg, the wall time if longer), max over ranks.  ms per step per region."""
+        res = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(REGIONS):
+            barrier()
+            t0 = time.perf_counter()
+            e0.record()
+            for _ in range(args.steps):
+                step_fn()
+            e1.record()
+            barrier()
+            ms = e0.elapsed_time(e1)
+            if wall:
+                ms = max(ms, (time.perf_counter() - t0) * 1e3)   # host-side stalls between steps count
+            res.append(reduce_max(ms) / args.steps)
+        return res
+
     # ---------------------------------------------------------------- kernel-resident timing
     for _ in range(args.warmup):
         ops.paged_decode_gqa(q, kc, vc, bt, cl, scale, out=out)
@@ -280,21 +388,19 @@ def main():
     sampler = ClockSampler(physical_gpu_index(local_rank))
     barrier()
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        ops.paged_decode_gqa(q, kc, vc, bt, cl, scale, out=out)
-    e1.record()
-    barrier()
-    ms_total = reduce_max(e0.elapsed_time(e1))
-    ms_step = ms_total / args.steps
+    kernel_ms = timed_regions(lambda: ops.paged_decode_gqa(q, kc, vc, bt, cl, scale, out=out), wall=False)
+    ms_step = float(np.median(kernel_ms))
 
     # ---------------------------------------------------------------- end-to-end with host inputs
-    # The step's inputs live in one pinned host buffer and are shipped with a single copy (as the engine's
-    # model runner does with its step metadata); typed views of the device copy go to the kernels.
+    # The engine's own input path (engine/model_runner.py of this package): the block table is resident on the
+    # device; a step ships, in ONE copy from one pinned buffer, the new tokens' q / k / v, slot_mapping,
+    # context_lens and the (row, column, block id) triples of the table entries that changed — one new block
+    # per sequence every 16 steps — which b200_block_table_patch applies; then store_kvcache, attention, and the
+    # output is copied back.  The KV pool is engine state and stays resident, as weights do.
+    max_patches = BATCH
     fields = [("q", torch.bfloat16, (BATCH, HQ, D)), ("k", torch.bfloat16, (BATCH, HKV, D)),
               ("v", torch.bfloat16, (BATCH, HKV, D)), ("slots", torch.int64, (BATCH,)),
-              ("cl", torch.int64, (BATCH,)), ("bt", torch.int32, tuple(case.block_tables.shape))]
+              ("cl", torch.int64, (BATCH,)), ("patches", torch.int32, (max_patches, 3))]
     offs, total = {}, 0
     for name, dt, shape in fields:
         offs[name] = total
@@ -315,38 +421,61 @@ def main():
     hv_["v"].copy_(torch.randn(BATCH, HKV, D).to(torch.bfloat16))
     hv_["slots"].copy_(torch.from_numpy(case.slot_mapping))
     hv_["cl"].copy_(torch.from_numpy(case.context_lens))
-    hv_["bt"].copy_(torch.from_numpy(case.block_tables))
     hout = torch.empty(BATCH, HQ, D, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in hv_.values())
-    d2h = hout.numel() * hout.element_size()
+    # table entries a step of a steady batch changes: the sequences that enter a new block on that step, i.e.
+    # (length + step) % 16 == 1; the workload itself stays fixed, so a patch rewrites the entry's own value
+    last_col = (case.context_lens - 1) // BS
+    patch_rows = [np.nonzero((case.context_lens + t) % BS == 1)[0] for t in range(BS)]
+    patch_np = hv_["patches"].numpy()
+    bt_dev = bt.clone()
+    e2e_state = {"t": 0, "h2d": 0}
+    fixed_bytes = sum(hv_[n].numel() * hv_[n].element_size() for n in ("q", "k", "v", "slots", "cl"))
+    patch_end = offs["patches"]
 
     def e2e_step():
-        dbuf.copy_(hbuf, non_blocking=True)
+        rows = patch_rows[e2e_state["t"] % BS]
+        e2e_state["t"] += 1
+        m = len(rows)
+        patch_np[:m, 0] = rows
+        patch_np[:m, 1] = last_col[rows]
+        patch_np[:m, 2] = case.block_tables[rows, last_col[rows]]
+        nbytes = patch_end + m * 12
+        e2e_state["h2d"] += fixed_bytes + m * 12
+        dbuf[:nbytes].copy_(hbuf[:nbytes], non_blocking=True)
+        if m:
+            ops.block_table_patch(dv_["patches"], m, bt_dev)
         ops.store_kvcache(dv_["k"], dv_["v"], kc, vc, dv_["slots"])
-        ops.paged_decode_gqa(dv_["q"], kc, vc, dv_["bt"], dv_["cl"], scale, out=out)
+        ops.paged_decode_gqa(dv_["q"], kc, vc, bt_dev, dv_["cl"], scale, out=out)
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
-    e2e_ms = float("nan")
+    e2e_ms, h2d, d2h = None, 0, hout.numel() * hout.element_size()
     if not args.no_e2e:
         for _ in range(args.warmup):
             e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        e0.record()
-        for _ in range(args.steps):
-            e2e_step()
-        e1.record()
-        barrier()
-        e2e_ms = reduce_max(max(e0.elapsed_time(e1), 0.0))
-        e2e_wall_ms = reduce_max((time.perf_counter() - t0) * 1e3)
-        e2e_ms = max(e2e_ms, e2e_wall_ms)  # host-side stalls between steps count
+        e2e_state["h2d"], calls0 = 0, e2e_state["t"]
+        e2e_ms = timed_regions(e2e_step, wall=True)
+        h2d = e2e_state["h2d"] / max(e2e_state["t"] - calls0, 1)
+        assert torch.equal(bt_dev, bt), "patches must leave the benchmark's block table as it was"
     sampler.stop()
     sampler.join(timeout=2)
     ops.check_status(dev)
+    clocks = sampler.summary()
+    del kc, vc, q, bt, cl, out, dbuf, bt_dev
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- the rest of the path
+    secondary = None
+    if n_gpus == 1 and not args.no_secondary:
+        secondary = secondary_kernels()
+    engine = None
+    if not args.no_engine:
+        from llm_from_scratch_b200 import microbench
+        engine = microbench.engine_jobs(hbm_peak_gbs=hbm_peak()[0])
 
     if rank != 0:
         if dist is not None:
+            dist.barrier()
             dist.destroy_process_group()
         return
 
@@ -358,6 +487,9 @@ def main():
     line = {
         "metric": "decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": n_gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "timing": {"regions": REGIONS, "steps_per_region": args.steps, "ms_per_step_median": ms_step,
+                   "ms_per_step_min": min(kernel_ms), "ms_per_step_max": max(kernel_ms),
+                   "how": "CUDA events on the launching stream around each region, max over ranks"},
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": config,
         "per_gpu_tokens_per_s": value / n_gpus,
@@ -368,24 +500,30 @@ def main():
                      # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the 64-sequence
                      # case (541.4 MB for 130,732 context tokens), scaled by context tokens to this launch
                      "traffic": NCU_DRAM_BYTES_PER_CONTEXT_TOKEN * case.total_tokens,
-                     "kernel": "paged_decode_bf16_kernel<128,1> (+ combine, timed together)"},
-        "e2e": None if args.no_e2e else {
-            "value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": 2 * args.steps,
-        "clocks": sampler.summary(),
+                     "kernel": DECODE_KERNEL},
+        "e2e": None if e2e_ms is None else {
+            "value": tokens_per_step / (float(np.median(e2e_ms)) * 1e-3), "unit": "tokens/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": float(np.median(e2e_ms)),
+            "ms_per_step_min": min(e2e_ms), "ms_per_step_max": max(e2e_ms),
+            "input_path": "device-resident block table + per-step patches, one pinned H2D copy, one D2H copy"},
+        "gpu_launches": DECODE_LAUNCHES_PER_CALL * args.steps,
+        "gpu_launches_note": f"per timed region of {args.steps} steps; {REGIONS} regions",
+        "clocks": clocks,
     }
-    if n_gpus == 1 and not args.no_cpu_baseline:
-        torch.set_num_threads(os.cpu_count() or 1)
-        nseq = CPU_SAMPLE_SEQS
-        sample = cpu_oracle_sample(case, q.cpu(), kc, vc, nseq)
-        time_cpu_oracle(sample)  # warm-up
-        dt = time_cpu_oracle(sample, repeats=3)
-        line["cpu_baseline"] = {
-            "value": nseq / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"first {nseq} of the {BATCH} sequences ({int(sample[4].sum())} context tokens), best of 3"}
+    if cpu_line is not None:
+        if "error" in cpu_line:
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": "failed: " + cpu_line["error"]}
+        else:
+            line["cpu_baseline"] = dict(cpu_line["cpu_baseline"],
+                                        how="the reference arm of this file run in a fresh process before CUDA start-up")
+    if secondary is not None:
+        line["secondary"] = secondary
+    if engine:
+        line["engine"] = engine
     print(json.dumps(line))
     if dist is not None:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -236,9 +236,9 @@ int b200_add_rmsnorm(const void* x, const void* residual, const float* weight, v
  * Everything GroupedQueryAttention.forward does between its projections and the attention call
  * (model/attention/GQA.py:81-102), plus the store_kvcache scatter, in one pass over the fused
  * projection output qkv [num_tokens, >= (Hq + 2 Hkv) * D] (token stride in elements):
- *   q, k: RMSNorm over the whole projected vector (eps as given: the machine epsilon of the dtype in
- *   the reference), rounded to the dtype, then half-split RoPE (model/attention/utils.py:34-45) in
- *   fp32 at positions[t] using rope_table [rope_positions, D] = cat(cos, sin), rounded to the dtype;
+ *   q, k: RMSNorm over the whole projected vector (eps as given: the reference's layers have eps=None,
+ *   which torch evaluates in fp32 with the fp32 machine epsilon when the weight is fp32), rounded to the
+ *   dtype, then half-split RoPE (model/attention/utils.py:34-45) in fp32 at positions[t] using rope_table [rope_positions, D] = cat(cos, sin), rounded to the dtype;
  *   q_out [num_tokens, Hq, D], k_out [num_tokens, Hkv, D];
  *   if k_cache != NULL: k_cache[slot] = k_out row, v_cache[slot] = raw v row, slot < 0 skipped.
  * ------------------------------------------------------------------------------------------- */

@@ -41,7 +41,7 @@ class LLMEngine:
         # wall time per step component: host scheduling, model run (incl. metadata upload and the
         # device-to-host read of the sampled tokens), host post-processing
         self.timing = dict(schedule_s=0.0, run_prefill_s=0.0, run_decode_s=0.0, postprocess_s=0.0,
-                           prefill_steps=0, decode_steps=0)
+                           prefill_steps=0, decode_steps=0, decode_seq_steps=0, decode_ctx_tokens=0)
 
     def exit(self) -> None:
         self.model_runner.exit()
@@ -90,6 +90,9 @@ class LLMEngine:
             self.scheduler.postprocess(seqs, token_ids)
             processed = sum(len(s) for s in seqs) if is_prefill else len(seqs)
         self.timing["postprocess_s"] += time.perf_counter() - t2
+        if not is_prefill:
+            self.timing["decode_seq_steps"] = getattr(runner, "decode_seq_steps", 0)
+            self.timing["decode_ctx_tokens"] = getattr(runner, "decode_ctx_tokens", 0)
         outputs = [(s.seq_id, s.completion_token_ids) for s in seqs if s.is_finished]
         return outputs, processed, is_prefill
 

@@ -101,6 +101,10 @@ class ModelRunner:
         self.graph_vars: dict[str, torch.Tensor] = {}
         self.prefill_graphs: dict[int, tuple] = {}
         self.decode_builder = None
+        # sums over the decode steps replayed from graphs: sequences stepped and context tokens attended to
+        # (what the decode kernels had to read), for throughput and memory-roofline reports
+        self.decode_seq_steps = 0
+        self.decode_ctx_tokens = 0
         c = self.model_config
         if c.attention_type == "MLA":    # prefill runs the expanded form: 192-wide keys, 128-wide values
             self.prefill_tile_rows = ops.prefill_tile_rows(c.num_heads, c.num_heads, c.head_dim + c.rope_dim,
@@ -237,6 +241,8 @@ class ModelRunner:
                                             h["block_tables"], patches=h["patches"])
         h["slot_mapping"][n:bucket] = -1
         h["context_lens"][n:bucket] = 0
+        self.decode_seq_steps += n
+        self.decode_ctx_tokens += int(h["context_lens"][:n].sum())
         if patched >= 0:
             nbytes = self.graph_patches_offset + patched * 12
         else:
@@ -274,6 +280,10 @@ class ModelRunner:
             else:
                 hist[j, :n].copy_(v["greedy"][:n])
         tokens = hist[:steps, :n].tolist()
+        # steps after the first (counted by _replay_decode): every context is one token longer per step
+        self.decode_ctx_tokens += (steps - 1) * int(self.graph_host_np["context_lens"][:n].sum()) \
+            + n * steps * (steps - 1) // 2
+        self.decode_seq_steps += n * (steps - 1)
         reset_context()
         return tokens
 

@@ -38,6 +38,7 @@ class ReplicaReport:
     prefill_tokens: int = 0
     decode_tokens: int = 0
     steps: int = 0
+    timing: dict = field(default_factory=dict)        # the engine's per-component wall times for this shard
 
 
 def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaReport:
@@ -49,6 +50,7 @@ def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaRep
     at t = 0.
     """
     rep = ReplicaReport(rank=rank)
+    before = dict(getattr(engine, "timing", {}))
     t0 = time.perf_counter()
     if arrivals is None:
         seqs = [engine.add_request(tok, sp) for tok, sp in shard]
@@ -74,6 +76,7 @@ def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaRep
         else:
             rep.decode_tokens += n
     rep.wall_s = time.perf_counter() - t0
+    rep.timing = {k: v - before.get(k, 0) for k, v in getattr(engine, "timing", {}).items()}
     rep.token_ids = [s.completion_token_ids for s in seqs]
     return rep
 

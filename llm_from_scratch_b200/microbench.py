@@ -241,6 +241,131 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
                 decode_window=decode_window, rank0_timing=timing)
 
 
+def decode_step_bytes(model: dict, seq_steps: int, ctx_tokens: int, steps: int, itemsize: int = 2) -> float:
+    """Bytes the decode steps of a GQA(+MoE) decoder must move, summed over ``steps`` steps that advanced
+    ``seq_steps`` sequences in total over ``ctx_tokens`` context tokens in total:
+
+    * per step, every weight the step touches, once: the attention projections, the MoE gate, the shared
+      expert, the routed experts that at least one token selected (expected count for a step of the average
+      batch size with uniform routing: E (1 - (1 - k/E)^batch)), and the lm_head matrix;
+    * per context token, its K and V rows in every layer (read); per stepped sequence, the new K/V rows
+      (written), its embedding row (fp32) and its logits row (written by the GEMM, read by the argmax).
+    Activations between the layers' kernels are left out: they are a small fraction of this and mostly stay
+    in the 126 MB L2."""
+    d, L, H, Hkv = model["d_model"], model["num_layers"], model["num_heads"], model["num_kv_heads"]
+    hd, dff, V = d // H, model["d_ff"], model["vocab_size"]
+    E, K = model.get("n_routed_experts", 0), model.get("num_experts_per_tok", 0)
+    attn = d * (H * hd + 2 * Hkv * hd) + (H * hd + 2 * Hkv * hd) + H * hd * d + d
+    expert = 3 * d * dff + 2 * dff + d
+    batch = seq_steps / max(steps, 1)
+    if model.get("use_moe"):
+        touched = E * (1.0 - (1.0 - K / E) ** batch)
+        ffn = d * E + touched * expert + model.get("n_shared_experts", 0) * expert
+    else:
+        ffn = expert
+    weights = (L * (attn + ffn) + V * d + V) * itemsize
+    kv_row = L * 2 * Hkv * hd * itemsize
+    return steps * weights + ctx_tokens * kv_row + seq_steps * (kv_row + d * 4 + 2 * V * itemsize)
+
+
+def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: int = 1,
+                hbm_peak_gbs: float = 6542.1) -> dict:
+    """The continuous-batching benchmark through the engine (GQA+MoE decoder of ``C3_MODEL``, bf16, random init
+    seed 0, KV block 16, at most 256 sequences and 8192 batched tokens per step, all requests present at
+    t = 0), as the two jobs a multi-GPU run can mean.  Every rank of the process group is an independent
+    replica with its own scheduler, block pool and KV cache; nothing is exchanged while a job runs.
+
+    * ``fixed``: ``requests`` requests in total; replica r serves requests r, r + N, ...  (strong scaling)
+    * ``weak``:  ``requests`` requests per replica, each replica its own seeded stream   (weak scaling)
+
+    With one replica the two are the same job and it runs once.  Rates are tokens of all replicas over the
+    slowest replica's wall time.  Returns {} on ranks other than 0."""
+    import itertools
+    import os
+    import time
+
+    import torch.distributed as dist
+
+    from .engine import SamplingParams, Sequence
+    from .engine.llm_engine import LLMEngine
+    from .engine.replicas import serve_shard, shard_requests
+    from .workloads import c3_requests
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1 and dist.is_initialized()
+    Sequence.counter = itertools.count()
+    cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
+               max_num_batched_tokens=8192, max_cached_blocks=pool_blocks, eos=-1, device=f"cuda:{local_rank}",
+               max_model_length=2048, seed=0, decode_window=decode_window)
+    t0 = time.perf_counter()
+    eng = LLMEngine(cfg)
+    build_s = time.perf_counter() - t0
+
+    def run(job: str):
+        if job == "fixed":
+            prompts, outs, _ = c3_requests(requests, seed=3)
+            shard = shard_requests(list(zip(prompts, outs)), world, rank)
+        else:
+            prompts, outs, _ = c3_requests(requests, seed=1000 + rank)
+            shard = list(zip(prompts, outs))
+        reqs = [(p, SamplingParams(temperature=0.0, max_tokens=int(n) + 1, ignore_eos=True)) for p, n in shard]
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()                      # replicas start the job together
+        rep = serve_shard(eng, reqs, rank)
+        torch.cuda.synchronize()
+        ops.check_status()
+        gen = sum(len(t) for t in rep.token_ids)
+        assert gen == int(sum(n for _, n in shard)), (gen, job)
+        t = rep.timing
+        nbytes = decode_step_bytes(C3_MODEL, t["decode_seq_steps"], t["decode_ctx_tokens"], t["decode_steps"])
+        mine = dict(wall_s=rep.wall_s, generated=gen, prompt=sum(len(p) for p, _ in shard), steps=rep.steps,
+                    decode_steps=t["decode_steps"], prefill_steps=t["prefill_steps"], run_decode_s=t["run_decode_s"],
+                    run_prefill_s=t["run_prefill_s"], schedule_s=t["schedule_s"], postprocess_s=t["postprocess_s"],
+                    decode_seq_steps=t["decode_seq_steps"], decode_ctx_tokens=t["decode_ctx_tokens"],
+                    decode_bytes=nbytes)
+        rows = [mine]
+        if distributed:
+            rows = [None] * world if rank == 0 else None
+            dist.gather_object(mine, rows, dst=0)
+        if rank != 0:
+            return None
+        wall = max(r["wall_s"] for r in rows)
+        gen_all, prompt_all = sum(r["generated"] for r in rows), sum(r["prompt"] for r in rows)
+        fracs = [r["decode_bytes"] / r["run_decode_s"] / 1e9 / hbm_peak_gbs for r in rows]
+        return dict(
+            requests=requests * (world if job == "weak" else 1), replicas=world, generated_tokens=gen_all,
+            prompt_tokens=prompt_all, wall_s=wall, replica_wall_s=[round(r["wall_s"], 4) for r in rows],
+            output_tokens_per_s=gen_all / wall, total_tokens_per_s=(gen_all + prompt_all) / wall,
+            decode_steps=[r["decode_steps"] for r in rows], prefill_steps=[r["prefill_steps"] for r in rows],
+            decode_step_ms=max(1e3 * r["run_decode_s"] / max(r["decode_steps"], 1) for r in rows),
+            mean_decode_batch=sum(r["decode_seq_steps"] for r in rows) / max(sum(r["decode_steps"] for r in rows), 1),
+            mean_context_tokens_per_step=sum(r["decode_ctx_tokens"] for r in rows) / max(sum(r["decode_steps"] for r in rows), 1),
+            # bytes the decode steps had to move (weights touched + KV of the live contexts + logits) over the wall
+            # time of those steps (host share included), against the measured HBM copy peak
+            decode_hbm_frac=min(fracs), decode_hbm_frac_by_replica=[round(f, 4) for f in fracs],
+            decode_gbs=min(r["decode_bytes"] / r["run_decode_s"] / 1e9 for r in rows),
+            host_s=dict(schedule=rows[0]["schedule_s"], postprocess=rows[0]["postprocess_s"]),
+            prefill_tokens_per_s=rows[0]["prompt"] / max(rows[0]["run_prefill_s"], 1e-9))
+
+    out = dict(model="GQA+MoE decoder: d_model 1024, 16 layers, 16/4 heads, head_dim 64, 16 experts top-2 + shared, "
+                     "d_ff 704, vocab 32000, bf16, random init seed 0",
+               workload=f"{requests} requests at t=0, prompts U[64,1024], outputs geometric(256) cap 1024, max 256 "
+                        "seqs / 8192 tokens per step per replica, KV block 16",
+               replicas=world, kv_pool_blocks=pool_blocks, engine_build_s=build_s,
+               cuda_graphs=bool(eng.model_runner.graphs), decode_window=decode_window)
+    fixed = run("fixed")
+    weak = run("weak") if world > 1 else None
+    eng.exit()
+    if rank != 0:
+        return {}
+    out["fixed"] = fixed
+    out["weak"] = weak if weak is not None else "one replica: the same job as fixed"
+    return out
+
+
 def engine_step(steps: int = 0, warmup: int = 0, batch: int = 1024) -> dict:
     """Kernel shares of one decode step and one prefill step of the GQA+MoE engine at steady state
     (``batch`` requests of the continuous-batching workload, all at t = 0): the engine runs normally and

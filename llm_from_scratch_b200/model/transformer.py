@@ -6,7 +6,7 @@ it, with the layer arithmetic of the reference's dense-batch model:
 
 * residual stream with fused add + RMSNorm          model/transformer.py:90-118, model/utils.py:54-67
 * GQA: biased q/k/v projections, RMSNorm over the whole projected q / k vector with
-  eps = finfo(dtype).eps, half-split RoPE, K cached after norm + RoPE, V raw   model/attention/GQA.py:79-130
+  the fp32 machine epsilon (eps=None), half-split RoPE, K cached after norm + RoPE, V raw   model/attention/GQA.py:79-130
 * MLA: absorbed form, one latent row [kv_norm(kv_down(x)) | rope(k_rope(x))] cached per token,
   kv_up_proj_fused biases unused                     model/attention/MLA.py:114-178
 * SwiGLU MLP with biases, sigmoid-score top-k MoE with renormalised weights, experts applied in
@@ -64,8 +64,9 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.
 
 
 def _vector_norm(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """nn.RMSNorm(eps=None) over the last dim: eps = finfo(x.dtype).eps, result in x.dtype."""
-    eps = torch.finfo(x.dtype).eps
+    """nn.RMSNorm(eps=None) over the last dim as the reference's mode evaluates it (fp32 weight): fp32
+    arithmetic with the fp32 machine epsilon, one rounding to x.dtype at the end."""
+    eps = ops.VECTOR_NORM_EPS
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight).to(x.dtype)
 
@@ -319,9 +320,9 @@ class MLAAttention(nn.Module):
     def forward(self, x, ctx, positions, out=None):
         T, H, hd, r, dr = x.shape[0], self.H, self.hd, self.r, self.dr
         x = x.to(self.dtype)
-        fused = self.fused and self.dtype == torch.bfloat16
+        fused = self.fused and ops.mla_prologue_supported(hd, dr, r, self.dtype)
         qd = F.linear(x, self.w_qd, self.b_qd)
-        qc = ops.add_rmsnorm(qd, self.q_norm, torch.finfo(self.dtype).eps) if fused else _vector_norm(qd, self.q_norm)
+        qc = ops.add_rmsnorm(qd, self.q_norm, ops.VECTOR_NORM_EPS) if fused else _vector_norm(qd, self.q_norm)
         qf = F.linear(qc, self.w_qu, self.b_qu)
         kvp = F.linear(x, self.w_kv, self.b_kv)
         if fused:

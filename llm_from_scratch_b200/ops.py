@@ -14,6 +14,11 @@ from ._lib import lib, check
 
 _DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
 
+# Epsilon of the reference's q / k / latent RMSNorm layers, nn.RMSNorm(eps=None) (GQA.py:39-40, MLA.py:71-72).
+# With fp32 parameters and a bf16 activation (the reference's autocast mode) torch evaluates that layer in
+# fp32 with the fp32 machine epsilon and rounds once at the end; in fp32 it is the same number.
+VECTOR_NORM_EPS = float(torch.finfo(torch.float32).eps)
+
 _status: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, str], torch.Tensor] = {}
 _retired_workspaces: list[torch.Tensor] = []   # outgrown buffers that captured graphs may still address
@@ -389,7 +394,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torc
         raise ValueError("slot_mapping must be int64 [T]")
     q = torch.empty(T, num_q_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
     k = torch.empty(T, num_kv_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
-    eps = torch.finfo(qkv.dtype).eps
+    eps = VECTOR_NORM_EPS
     check(lib.b200_qk_norm_rope_store(
         qkv.data_ptr(), qkv.stride(0), q_norm_w.data_ptr(), k_norm_w.data_ptr(), rope_table.data_ptr(),
         rope_table.shape[0], positions.data_ptr(), q.data_ptr(), k.data_ptr(),
@@ -399,6 +404,14 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torc
         "qk_norm_rope_store")
     v = qkv[:, wq + wk:].view(T, num_kv_heads, head_dim)
     return q, k, v
+
+
+def mla_prologue_supported(head_dim: int, rope_dim: int, kv_lora_rank: int, dtype: torch.dtype) -> bool:
+    """Shapes the fused MLA pre-attention kernel takes (16-byte chunks everywhere, a rotation partner a whole
+    number of lanes away); other shapes run the same stage as separate tensor operations on the device."""
+    rpc = rope_dim // 8
+    return (dtype == torch.bfloat16 and head_dim % 8 == 0 and rope_dim % 16 == 0 and kv_lora_rank % 8 == 0
+            and rpc & (rpc - 1) == 0 and rpc <= 32)
 
 
 def mla_prologue(q_up: torch.Tensor, kv_down: torch.Tensor, kv_norm_w: torch.Tensor, rope_table: torch.Tensor,
@@ -439,7 +452,7 @@ def mla_prologue(q_up: torch.Tensor, kv_down: torch.Tensor, kv_norm_w: torch.Ten
         rows.data_ptr(), latent_cache.data_ptr() if use_cache else None,
         slot_mapping.data_ptr() if use_cache else None,
         (latent_cache.numel() // (kv_lora_rank + rope_dim)) if use_cache else 0, T, num_heads, head_dim, rope_dim,
-        kv_lora_rank, float(torch.finfo(q_up.dtype).eps), _dt(q_up), status_word(dev).data_ptr(), _stream()),
+        kv_lora_rank, VECTOR_NORM_EPS, _dt(q_up), status_word(dev).data_ptr(), _stream()),
         "mla_prologue")
     return q, rows
 

@@ -51,7 +51,9 @@ class OracleModel:
         return (w * xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dt), xf.to(dt)
 
     def _nn_rms(self, x, name):
-        """torch.nn.RMSNorm with eps=None: eps = finfo(x.dtype).eps (GQA.py:39-40, MLA.py:71-72)."""
+        """torch.nn.RMSNorm with eps=None (GQA.py:39-40, MLA.py:71-72): the operator the reference calls, so
+        whatever epsilon and rounding torch applies (for a bf16 input with an fp32 weight: fp32 arithmetic,
+        fp32 machine epsilon, one rounding at the end) is applied here too."""
         w = self.w[name + ".weight"]
         return F.rms_norm(x, (x.shape[-1],), w, None)
 

@@ -552,11 +552,9 @@ def test_qk_norm_rope_store_matches_oracle_and_scatter(dtype, Hq, Hkv, D):
     pos = torch.from_numpy(np.random.default_rng(0).integers(0, 128, size=T).astype(np.int64))
     slots = torch.from_numpy(np.random.default_rng(1).permutation(nb * bs)[:T].astype(np.int64))
     slots[3] = -1
-    eps = torch.finfo(dtype).eps
 
-    def vec_norm(x, w):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w).to(dtype)
+    def vec_norm(x, w):     # the reference's nn.RMSNorm(eps=None) with an fp32 weight
+        return torch.nn.functional.rms_norm(x, (x.shape[-1],), w, None).to(dtype)
     q = vec_norm(qkv[:, :Hq * D], qw).view(T, Hq, D).transpose(0, 1)
     k = vec_norm(qkv[:, Hq * D:(Hq + Hkv) * D], kw).view(T, Hkv, D).transpose(0, 1)
     v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
@@ -594,12 +592,10 @@ def test_mla_prologue_matches_oracle(H, hd, dr, r, width):
     pos = torch.from_numpy(np.random.default_rng(2).integers(0, 96, size=T).astype(np.int64))
     slots = torch.from_numpy(np.random.default_rng(3).permutation(nb * bs)[:T].astype(np.int64))
     slots[5] = -1
-    eps = torch.finfo(dtype).eps
     q_nope = qf[:, :H * hd].view(T, H, hd)
     q_rope = orc.apply_rope(qf[:, H * hd:].view(T, H, dr).transpose(0, 1).float(), pos, table).transpose(0, 1)
     want_q = torch.cat([q_nope, q_rope.to(dtype)], dim=-1)
-    cf = kvp[:, :r].float()
-    c = (cf * torch.rsqrt(cf.pow(2).mean(-1, keepdim=True) + eps) * w).to(dtype)
+    c = torch.nn.functional.rms_norm(kvp[:, :r], (r,), w, None).to(dtype)   # nn.RMSNorm(eps=None), fp32 weight
     pe = orc.apply_rope(kvp[:, r:].float().unsqueeze(0), pos, table).squeeze(0).to(dtype)
     want_rows = torch.cat([c, pe], dim=-1)
 
