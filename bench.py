@@ -241,20 +241,30 @@ def secondary_kernels(steps_scale: float = 1.0) -> dict:
         return res
 
     n = lambda k: max(3, int(k * steps_scale))
-    out["store"] = hbm_bound(microbench.store(steps=n(50), warmup=5))
-    torch.cuda.empty_cache()
-    pf = microbench.prefill(steps=n(5), warmup=3)
+
+    def clocked(fn, **kw):
+        """Runs one secondary benchmark with the SM clock sampled beside it."""
+        smp = ClockSampler(physical_gpu_index(torch.cuda.current_device()), period=0.005)
+        smp.start()
+        res = fn(**kw)
+        smp.stop()
+        smp.join(timeout=2)
+        c = smp.summary()
+        res["clocks"] = {"sm_mhz": c.get("sm_mhz"), "reasons": c.get("reasons", [])}
+        torch.cuda.empty_cache()
+        return res
+
+    # memory-bound kernels first: the long tensor-core runs heat the part up and the power cap then lowers the
+    # SM clock, which the kernels that are bound by on-chip pipes (MLA decode) would inherit
+    out["store"] = hbm_bound(clocked(microbench.store, steps=n(50), warmup=5))
+    out["mla_decode"] = hbm_bound(clocked(microbench.mla_decode, steps=n(50), warmup=5))
+    out["moe_experts"] = hbm_bound(clocked(microbench.moe_experts, steps=n(20), warmup=3))
+    mp = clocked(microbench.mla_prefill, steps=n(20), warmup=3)
+    out["mla_prefill"] = tensor_bound(mp, mp["tflops"])
+    pf = clocked(microbench.prefill, steps=n(5), warmup=3)
     pf["lengths"] = pf.pop("lengths")          # realised lengths of the 64 sequences, longest first
     out["prefill"] = tensor_bound(pf, pf["tflops"])
     out["prefill"]["attention_only_frac"] = pf["attention_only_tflops"] / burst
-    torch.cuda.empty_cache()
-    out["mla_decode"] = hbm_bound(microbench.mla_decode(steps=n(50), warmup=5))
-    torch.cuda.empty_cache()
-    mp = microbench.mla_prefill(steps=n(20), warmup=3)
-    out["mla_prefill"] = tensor_bound(mp, mp["tflops"])
-    torch.cuda.empty_cache()
-    out["moe_experts"] = hbm_bound(microbench.moe_experts(steps=n(20), warmup=3))
-    torch.cuda.empty_cache()
     return out
 
 
@@ -425,23 +435,25 @@ def main():
     # table entries a step of a steady batch changes: the sequences that enter a new block on that step, i.e.
     # (length + step) % 16 == 1; the workload itself stays fixed, so a patch rewrites the entry's own value
     last_col = (case.context_lens - 1) // BS
-    patch_rows = [np.nonzero((case.context_lens + t) % BS == 1)[0] for t in range(BS)]
+    patch_sets = []
+    for t in range(BS):
+        rows = np.nonzero((case.context_lens + t) % BS == 1)[0]
+        patch_sets.append(np.stack([rows, last_col[rows], case.block_tables[rows, last_col[rows]]], axis=1).astype(np.int32))
     patch_np = hv_["patches"].numpy()
     bt_dev = bt.clone()
     e2e_state = {"t": 0, "h2d": 0}
     fixed_bytes = sum(hv_[n].numel() * hv_[n].element_size() for n in ("q", "k", "v", "slots", "cl"))
-    patch_end = offs["patches"]
+    # (host view, device view) of the buffer prefix a step with m patches ships
+    prefix = {len(p_): (hbuf[:offs["patches"] + len(p_) * 12], dbuf[:offs["patches"] + len(p_) * 12]) for p_ in patch_sets}
 
     def e2e_step():
-        rows = patch_rows[e2e_state["t"] % BS]
+        pt = patch_sets[e2e_state["t"] % BS]
         e2e_state["t"] += 1
-        m = len(rows)
-        patch_np[:m, 0] = rows
-        patch_np[:m, 1] = last_col[rows]
-        patch_np[:m, 2] = case.block_tables[rows, last_col[rows]]
-        nbytes = patch_end + m * 12
+        m = len(pt)
+        patch_np[:m] = pt
         e2e_state["h2d"] += fixed_bytes + m * 12
-        dbuf[:nbytes].copy_(hbuf[:nbytes], non_blocking=True)
+        src, dst = prefix[m]
+        dst.copy_(src, non_blocking=True)
         if m:
             ops.block_table_patch(dv_["patches"], m, bt_dev)
         ops.store_kvcache(dv_["k"], dv_["v"], kc, vc, dv_["slots"])

@@ -158,6 +158,12 @@ int b200_paged_decode_gqa_static(const void* q, const void* k_cache, const void*
  *   shapes the grid any more, so a step with fixed buffer sizes can be captured in a CUDA graph:
  *   pass num_seqs = the capacity of cu_seqlens (unused trailing sequences have length 0).
  *   A plan whose tile_rows does not match the kernel chosen for the shape is ignored.
+ *   slot_mapping (may be NULL): int64, one slot per new token (the rows of k / v; -1 = skip), as prepare_prefill
+ *   builds it (model_runner.py:226-230).  When given, the call also performs the step's store_kvcache:
+ *   k_cache[slot] = k row, v_cache[slot] = v row for the pool [num_blocks, block_size, Hkv, D] (k, v, k_cache,
+ *   v_cache, block_size and num_blocks are then required, with or without block_tables, and head_dim_qk must
+ *   equal head_dim_v).  The scatter is enqueued ahead of the attention grid inside this call, so keys read
+ *   through block_tables include the new tokens.
  * ------------------------------------------------------------------------------------------- */
 int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                         int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
@@ -167,8 +173,9 @@ int b200_prefill_varlen(const void* q, const void* k, const void* v, void* out,
                         int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim_qk,
                         int32_t head_dim_v, float scale, const void* k_cache, const void* v_cache,
                         const int32_t* block_tables, int64_t bt_stride, int32_t block_size,
-                        int64_t num_blocks, const int32_t* plan, int32_t plan_tile_rows,
-                        int32_t plan_capacity, int32_t dtype, int32_t* status, void* stream);
+                        int64_t num_blocks, const int64_t* slot_mapping, const int32_t* plan,
+                        int32_t plan_tile_rows, int32_t plan_capacity, int32_t dtype, int32_t* status,
+                        void* stream);
 
 /* The same attention for keys stored in two parts, as the expanded form of multi-head latent attention
  * has them (model/attention/MLA.py:93-95,131: k = [k_nope of the head | k_rope shared by all heads]):

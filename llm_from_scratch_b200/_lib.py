@@ -36,7 +36,7 @@ SIGNATURES = {
                                                _i32, _i32, _i32, _i32, _f32, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b200_prefill_varlen": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32,
                                    _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _i64, _i32,
-                                   _i64, _vp, _i32, _i32, _i32, _vp, _vp]),
+                                   _i64, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b200_prefill_tile_rows": (_i32, [_i32, _i32, _i32, _i32, _i32]),
     "b200_prefill_plan_bytes": (_sz, [_i64, _i32, _i32]),
     "b200_prefill_plan": (_i32, [_vp, _i32, _i32, _i32, _vp, _sz, _vp, _vp]),

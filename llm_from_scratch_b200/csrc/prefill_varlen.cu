@@ -264,8 +264,8 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
                                    int32_t head_dim_v, float scale, const void* k_cache,
                                    const void* v_cache, const int32_t* block_tables,
                                    int64_t bt_stride, int32_t block_size, int64_t num_blocks,
-                                   const int32_t* plan, int32_t plan_tile_rows, int32_t plan_capacity,
-                                   int32_t dtype, int32_t* status, void* stream) {
+                                   const int64_t* slot_mapping, const int32_t* plan, int32_t plan_tile_rows,
+                                   int32_t plan_capacity, int32_t dtype, int32_t* status, void* stream) {
   using namespace b200;
   if (num_seqs < 0 || max_seqlen_q < 0 || max_seqlen_k < 0 || num_q_heads <= 0 ||
       num_kv_heads <= 0 || head_dim_qk <= 0 || head_dim_v <= 0)
@@ -282,6 +282,19 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
       return B200_ERR_ARG;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (slot_mapping != nullptr) {
+    // the step's store_kvcache scatter rides in this call: the new tokens' rows go into the pool first (its
+    // own launch, ahead of the attention grid in the stream), so a paged prefix read sees them
+    if (!k || !v || !k_cache || !v_cache || block_size <= 0 || num_blocks <= 0) return B200_ERR_ARG;
+    if (head_dim_qk != head_dim_v) return B200_ERR_UNSUPPORTED;
+    const int64_t rows = block_tables == nullptr && total_k_tokens < total_q_tokens ? total_k_tokens : total_q_tokens;
+    if (rows > 2147483647LL) return B200_ERR_TOO_LARGE;
+    const int rc = b200_store_kvcache(k, v, k_token_stride, v_token_stride, const_cast<void*>(k_cache),
+                                      const_cast<void*>(v_cache), slot_mapping, static_cast<int32_t>(rows),
+                                      num_kv_heads, head_dim_qk, num_blocks * block_size, dtype, status, stream);
+    if (rc != B200_OK) return rc;
+  }
 
   if (dtype == B200_DTYPE_BF16) {
     if (block_tables == nullptr) {

@@ -187,8 +187,12 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
                    cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int,
                    max_seqlen_k: int, scale: float, k_cache: torch.Tensor | None = None,
                    v_cache: torch.Tensor | None = None, block_tables: torch.Tensor | None = None,
-                   out: torch.Tensor | None = None, plan: "PrefillPlan | None" = None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, plan: "PrefillPlan | None" = None,
+                   slot_mapping: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention over packed ragged sequences.
+
+    ``slot_mapping`` (int64, one slot per row of k / v): the same call first scatters the new tokens' k / v
+    rows into ``k_cache`` / ``v_cache`` (the step's store_kvcache), with or without ``block_tables``.
 
     q: [Tq, Hq, Dqk].  Without ``block_tables``: k [Tk, Hkv, Dqk], v [Tk, Hkv, Dv] are the packed
     keys/values.  With ``block_tables`` (a cached prefix exists) keys/values are read from the
@@ -216,6 +220,13 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
         kcp = vcp = btp = 0
         bts = bs = nb = 0
         total_k = k.shape[0]
+        if slot_mapping is not None:
+            if k_cache is None or v_cache is None or k_cache.shape != v_cache.shape or k_cache.dim() != 4 \
+                    or k_cache.shape[2:] != (Hkv, Dqk) or k_cache.dtype != q.dtype \
+                    or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+                raise ValueError("the fused scatter needs contiguous caches [num_blocks, block_size, Hkv, D] of q's dtype")
+            nb, bs = k_cache.shape[0], k_cache.shape[1]
+            kcp, vcp = k_cache.data_ptr(), v_cache.data_ptr()
     else:
         if k_cache is None or v_cache is None:
             raise ValueError("paged prefill needs k_cache and v_cache")
@@ -230,7 +241,15 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
         kp = vp = 0
         ks = vs = 0
         total_k = 0
+        if slot_mapping is not None:
+            if k is None or v is None or k.shape != (Tq, Hkv, Dqk) or v.shape != (Tq, Hkv, Dv) or k.stride(1) != Dqk \
+                    or v.stride(1) != Dv or k.stride(2) != 1 or v.stride(2) != 1:
+                raise ValueError("the fused scatter needs the new tokens' k / v [Tq, Hkv, D]")
+            kp, vp, ks, vs, total_k = k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), Tq
         kcp, vcp, btp, bts = k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(), block_tables.stride(0)
+    if slot_mapping is not None and (slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous()
+                                     or slot_mapping.numel() != min(Tq, total_k)):
+        raise ValueError("slot_mapping must be a contiguous int64 tensor with one entry per new token")
     if out is None:
         out = torch.empty((Tq, Hq, Dv), dtype=q.dtype, device=q.device)
     elif out.shape != (Tq, Hq, Dv) or out.dtype != q.dtype or not out.is_contiguous():
@@ -239,6 +258,7 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | No
                                   cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
                                   int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, Dqk, Dv,
                                   float(scale), kcp, vcp, btp, bts, bs, nb,
+                                  slot_mapping.data_ptr() if slot_mapping is not None else None,
                                   plan.buffer.data_ptr() if plan is not None else None,
                                   plan.tile_rows if plan is not None else 0,
                                   plan.capacity if plan is not None else 0, _dt(q),

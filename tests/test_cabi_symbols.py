@@ -41,7 +41,7 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.b200_paged_decode_gqa(None, None, None, None, None, 0, None, 1, 7, 2, 64, 16, 1, 1.0,
                                      None, 0, 1, None, None) == -1  # 7 heads not divisible by 2
     assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, 1, 1, None, None, 1, 1, 1, 4, 4, 64, 64,
-                                   1.0, None, None, None, 0, 0, 0, None, 0, 0, 5, None, None) == -3  # bad dtype
+                                   1.0, None, None, None, 0, 0, 0, None, None, 0, 0, 5, None, None) == -3  # bad dtype
     assert lib.b200_prefill_tile_rows(32, 8, 128, 128, 1) == 256      # tcgen05 kernel, two row tiles per CTA
     assert lib.b200_prefill_tile_rows(16, 16, 192, 128, 1) == 256     # tcgen05 kernel, two row tiles per CTA
     assert lib.b200_prefill_tile_rows(16, 4, 64, 64, 1) == 64         # mma.sync kernel
