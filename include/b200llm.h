@@ -17,6 +17,9 @@
  *     never synchronises the host, so every call can be captured in a CUDA graph;
  *   - metadata dtypes are exactly the reference's: slot_mapping and context_lens int64,
  *     block_tables and cu_seqlens int32; -1 is legal padding in slot_mapping and block_tables;
+ *   - calls are reentrant and take no locks.  The only process-wide state is a few per-device caches (SM count,
+ *     "shared-memory limit raised" flags, the address of the built-in scratch array) that are filled on first
+ *     use without synchronisation: concurrent first calls from several host threads store identical values;
  *   - return value: 0 on success, a negative B200_ERR_* code for argument / launch errors that
  *     are detected on the host.  Faults detected on the device (a block id or slot outside the
  *     pool) never dereference the bad address: the access is skipped and a B200_ERR_* code is
@@ -101,9 +104,13 @@ int b200_store_kvcache(const void* k, const void* v, int64_t k_token_stride,
  *   block_tables  [batch, bt_stride] int32, entries beyond ceil(context_len/block_size) are
  *                 never read (-1 or stale values are fine)
  *   context_lens  [batch] int64, includes the token being decoded; <= 0 writes a zero row
- *   workspace     b200_paged_decode_gqa_workspace_bytes(...) bytes, 256-byte aligned; holds
- *                 split-context partial results, no state survives the call
+ *   workspace     b200_paged_decode_gqa_workspace_bytes(...) bytes, 256-byte aligned; holds the arrival
+ *                 counters and partial results of contexts split across thread blocks.  Its first
+ *                 B200_DECODE_COUNTER_BYTES must be zero when the buffer is first used (one cudaMemset after
+ *                 allocating it); every call leaves them zero again, whatever the shapes of successive calls.
+ *                 The rest needs no initialisation.  Two calls that overlap on the GPU need two workspaces.
  * ------------------------------------------------------------------------------------------- */
+#define B200_DECODE_COUNTER_BYTES ((size_t)256 << 10)
 size_t b200_paged_decode_gqa_workspace_bytes(int32_t batch, int32_t num_q_heads,
                                              int32_t num_kv_heads, int32_t head_dim,
                                              int32_t dtype);
@@ -122,12 +129,15 @@ int b200_paged_decode_gqa(const void* q, const void* k_cache, const void* v_cach
  * the library until the process exits.  It is meant for hosts that gave all
  * device memory to the KV pool, or that may not call an allocator on the decode path.
  *   - calls no cudaMalloc/cudaFree or any allocating routine;
- *   - returns B200_ERR_TOO_LARGE when b200_paged_decode_gqa_workspace_bytes(...) for the shape
- *     exceeds the capacity (nothing is launched);
+ *   - returns B200_ERR_TOO_LARGE when the call would take the split-context kernel (bf16, block_size 16,
+ *     head_dim 32/64/128, 16-byte aligned q and caches) and b200_paged_decode_gqa_workspace_bytes(...) for
+ *     the shape exceeds the capacity (nothing is launched); shapes served by the general kernel need no
+ *     scratch and are never refused;
  *   - the first call on each device looks up the array's device address (a host-side symbol query,
  *     made with that device current); make that first call before starting any stream capture;
  *   - all calls share the array: calls that overlap on the GPU (two streams, two threads) race on
- *     it.  Nothing in it has to be cleared between calls.
+ *     it.  Nothing in it has to be cleared between calls (the counters at its head start at zero when the
+ *     library is loaded and every call returns them to zero).
  * ------------------------------------------------------------------------------------------- */
 #define B200_STATIC_SCRATCH_BYTES ((size_t)8 << 20)
 int b200_paged_decode_gqa_static(const void* q, const void* k_cache, const void* v_cache,

@@ -4,10 +4,17 @@
 // ---------------------------------------------------------------------------------------------
 // The work is the flat list of all KV blocks of all sequences, in (sequence, block) order.  It is
 // cut into gridDim.x equal contiguous ranges, one per persistent CTA, so every CTA streams the
-// same number of bytes whatever the mix of context lengths ("split-K" falls out of the cut: a
-// sequence that crosses a cut is finished by the combine kernel).  Each CTA recomputes the cut
-// from context_lens itself, so the launch needs no host-side knowledge of the lengths and can be
-// captured in a CUDA graph.
+// same number of bytes whatever the mix of context lengths ("split-K" falls out of the cut).  Each
+// CTA recomputes the cut from context_lens itself, so the launch needs no host-side knowledge of
+// the lengths and can be captured in a CUDA graph.
+//
+// A sequence that crosses a cut is finished inside the same launch: every warp that completes a
+// piece writes its unnormalised (max, sum, O) partials, fences, and bumps an arrival counter of
+// its (sequence, KV head); the warp whose arrival completes the count merges the pieces in fixed
+// CTA order (so the result does not depend on which warp came last), writes the output rows and
+// returns the counter to zero.  The counters occupy the first kDecodeCounterBytes of the workspace,
+// which must be zero when the buffer is first used; every launch leaves them zero.  Batches with
+// more (sequence, KV head) pairs than counters fall back to a separate merge kernel.
 //
 // A CTA has one warp per KV head; the warps of a CTA walk the same blocks, so between them they
 // read each 16-token block of the pool as one contiguous Hkv*D*16*2-byte segment of K and one of
@@ -28,6 +35,8 @@ namespace b200 {
 namespace {
 
 constexpr int kTok = 16;    // tokens per KV block on the fast path
+constexpr size_t kDecodeCounterBytes = 256 * 1024;  // arrival counters at the head of the workspace
+constexpr int64_t kDecodeCounters = kDecodeCounterBytes / sizeof(int32_t);
 constexpr int kStages = 3;  // (K,V) tiles in flight per warp
 constexpr int kMaxFastThreads = 512;
 
@@ -44,7 +53,8 @@ struct DecodeArgs {
   float scale_log2;  // softmax scale * log2(e)
   float* part_o;     // [grid][2][Hq][D]   unnormalised partial outputs
   float* part_ml;    // [grid][2][Hq][2]   running max (log2 domain) and sum
-  int32_t* seq_info; // [batch][2]         first / last CTA of a split sequence, or -1
+  int32_t* seq_info; // [batch][2]         first / last CTA of a split sequence, or -1 (separate merge kernel)
+  int32_t* counters; // [batch][Hkv]       arrivals per (sequence, KV head), zero between launches; null = separate merge
   int32_t* status;
 };
 
@@ -57,6 +67,49 @@ __device__ __forceinline__ int swizzle_chunk(int c, int t) {
   constexpr int CPR = D / 8;
   if (CPR >= 8) return c ^ (t & 7);
   return c ^ ((t >> 1) & (CPR - 1));  // CPR == 4: two rows share a 128-byte line
+}
+
+// Merge of the `np` pieces of (sequence `seq`, KV head `h`) by one warp: pieces live in the partial slots of
+// CTAs first .. first + np - 1 (slot 1 in the CTA where the sequence starts, slot 0 in the others).  Four
+// fp32 columns per lane, 32 / (D / 4) heads per pass.  Loads bypass L1: other SMs wrote the data.
+template <int D>
+__device__ __forceinline__ void merge_split_sequence(const DecodeArgs& a, int seq, int h, int G, int first,
+                                                     int np, int lane) {
+  constexpr int LPH = D / 4;    // lanes per head
+  constexpr int HPP = 32 / LPH; // heads per pass
+  const int64_t n = static_cast<int64_t>(a.Hq) * D;
+  const int col = (lane % LPH) * 4;
+  for (int hb = 0; hb < G; hb += HPP) {
+    const int hl = hb + lane / LPH;
+    const bool active = hl < G;
+    const int head = h * G + (active ? hl : 0);
+    float M = -INFINITY;
+    for (int p = 0; p < np; ++p) {
+      const int64_t slot = static_cast<int64_t>(first + p) * 2 + (p == 0 ? 1 : 0);
+      M = fmaxf(M, __ldcg(a.part_ml + (slot * a.Hq + head) * 2));
+    }
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < np; ++p) {
+      const int64_t slot = static_cast<int64_t>(first + p) * 2 + (p == 0 ? 1 : 0);
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (slot * a.Hq + head) * 2));
+      const float w = exp2f(ml.x - M);
+      const float4 x = __ldcg(reinterpret_cast<const float4*>(a.part_o + slot * n + head * D + col));
+      L += w * ml.y;
+      acc.x += w * x.x;
+      acc.y += w * x.y;
+      acc.z += w * x.z;
+      acc.w += w * x.w;
+    }
+    if (active) {
+      const float inv = 1.f / L;
+      uint2 packed;
+      packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+      packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.out) + (static_cast<int64_t>(seq) * a.Hq + head) * D +
+                                col) = packed;
+    }
+  }
 }
 
 template <int D, int NT>
@@ -84,9 +137,19 @@ paged_decode_bf16_kernel(const DecodeArgs a) {
     local += num_kv_blocks(a.lens[i], a.bt_stride, kTok);
   int T;
   block_inclusive_scan(local, s_scan, &T);
-  // the combine kernel is launched as a programmatic dependent: let its CTAs be placed while this grid
-  // runs (they wait for this grid's completion before they read anything)
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  if (a.counters == nullptr) {
+    // the merge kernel is launched as a programmatic dependent: let its CTAs be placed while this grid
+    // runs (they wait for this grid's completion before they read anything)
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  } else {
+    // rows of empty contexts are zero (no piece of them exists to write anything)
+    for (int i = p; i < B; i += P) {
+      if (a.lens[i] > 0) continue;
+      uint32_t* row = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(a.out) +
+                                                  static_cast<int64_t>(i) * a.Hq * D);
+      for (int e = threadIdx.x; e < a.Hq * D / 2; e += blockDim.x) row[e] = 0u;
+    }
+  }
   const int Q = (T + P - 1) / P;
   const int start = p * Q;
   if (Q == 0 || start >= T) return;
@@ -345,10 +408,29 @@ paged_decode_bf16_kernel(const DecodeArgs a) {
           }
         }
       }
-      if (seq_end && warp == 0 && lane == 0) {
+      if (a.counters == nullptr) {
+        if (seq_end && warp == 0 && lane == 0) {
+          const int seq_start_flat = start + j - C.blk;
+          a.seq_info[2 * C.seq] = whole ? -1 : seq_start_flat / Q;
+          a.seq_info[2 * C.seq + 1] = whole ? -1 : p;
+        }
+      } else if (!whole) {
+        // this warp's piece of (sequence, KV head) is in the workspace: publish it, count the arrival, and
+        // merge if every other piece has arrived already
         const int seq_start_flat = start + j - C.blk;
-        a.seq_info[2 * C.seq] = whole ? -1 : seq_start_flat / Q;
-        a.seq_info[2 * C.seq + 1] = whole ? -1 : p;
+        const int first = seq_start_flat / Q;
+        const int np = (seq_start_flat + C.nblk - 1) / Q - first + 1;
+        __threadfence();
+        __syncwarp();
+        int32_t* cnt = a.counters + static_cast<int64_t>(C.seq) * a.Hkv + h;
+        int arrived = 0;
+        if (lane == 0) arrived = atomicAdd(cnt, 1);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived == np - 1) {
+          __threadfence();
+          merge_split_sequence<D>(a, C.seq, h, G, first, np, lane);
+          if (lane == 0) *cnt = 0;   // ready for the next launch
+        }
       }
     }
     if (j + 1 < cnt) advance(C);
@@ -596,6 +678,8 @@ FastPlan fast_plan(int Hq, int Hkv, int D, int bs, int dtype) {
 
 template <int D, int NT>
 int launch_fast(const DecodeArgs& a, const FastPlan& pl, int grid, cudaStream_t s) {
+  // per-device "shared-memory limit raised" flags: written without a lock; two host threads racing here both
+  // make the same idempotent cudaFuncSetAttribute call and both store true
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -623,7 +707,8 @@ extern "C" size_t b200_paged_decode_gqa_workspace_bytes(int32_t batch, int32_t n
   int sms = sm_count_cached();
   if (sms <= 0) sms = 148;
   const size_t grid = static_cast<size_t>(sms) * pl.ctas_per_sm;
-  size_t bytes = align256(grid * 2 * num_q_heads * head_dim * sizeof(float));
+  size_t bytes = kDecodeCounterBytes;
+  bytes += align256(grid * 2 * num_q_heads * head_dim * sizeof(float));
   bytes += align256(grid * 2 * num_q_heads * 2 * sizeof(float));
   bytes += align256(static_cast<size_t>(batch) * 2 * sizeof(int32_t));
   return bytes;
@@ -675,6 +760,9 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
     const size_t grid = static_cast<size_t>(sms) * pl.ctas_per_sm;
     uint8_t* w = static_cast<uint8_t*>(workspace);
+    const bool fused_merge = static_cast<int64_t>(batch) * num_kv_heads <= kDecodeCounters;
+    a.counters = fused_merge ? reinterpret_cast<int32_t*>(w) : nullptr;
+    w += kDecodeCounterBytes;
     a.part_o = reinterpret_cast<float*>(w);
     w += align256(grid * 2 * num_q_heads * head_dim * sizeof(float));
     a.part_ml = reinterpret_cast<float*>(w);
@@ -688,7 +776,7 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
       rc = pl.nt == 1 ? launch_fast<64, 1>(a, pl, gi, s) : launch_fast<64, 2>(a, pl, gi, s);
     else
       rc = pl.nt == 1 ? launch_fast<32, 1>(a, pl, gi, s) : launch_fast<32, 2>(a, pl, gi, s);
-    if (rc != B200_OK) return rc;
+    if (rc != B200_OK || fused_merge) return rc;
     return launch_combine(a, batch, s);
   }
 
@@ -716,9 +804,11 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
 // symbol, so the device address is looked up once per device with cudaGetSymbolAddress (with that
 // device current) and cached; that first call per device does the lookup and should therefore be
 // made before any stream capture starts.  All calls share the one array and it keeps whatever the
-// previous call left in it: nothing in it needs to start at zero, because every slot that a call
-// reads was written earlier in that same call, but two calls that overlap on the GPU (different
-// streams, or different host threads) would overwrite each other's partial results.
+// previous call left in it.  Only its first 256 KiB (the arrival counters of split sequences) must be zero
+// when a call starts: the array is zero when the library is loaded and every call returns the counters it
+// touched to zero, so nothing has to be cleared between calls; the partial results behind them are written
+// before they are read within one call.  Two calls that overlap on the GPU (different streams, or different
+// host threads) would corrupt each other's counters and partial results.
 // ---------------------------------------------------------------------------------------------
 namespace b200 {
 namespace {
@@ -727,6 +817,8 @@ constexpr size_t kStaticScratchBytes = B200_STATIC_SCRATCH_BYTES;  // 8 MiB per 
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 
 int static_scratch_address(void** out) {
+  // per-device cache of the symbol's address: written without a lock; racing host threads look up and
+  // store the same value
   static void* cached[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_ERR_NO_DEVICE;
@@ -754,10 +846,14 @@ extern "C" int b200_paged_decode_gqa_static(const void* q, const void* k_cache,
                                             int64_t num_blocks, float scale, int32_t dtype,
                                             int32_t* status, void* stream) {
   using namespace b200;
-  if (batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0) {
-    const size_t need = b200_paged_decode_gqa_workspace_bytes(batch, num_q_heads, num_kv_heads,
-                                                              head_dim, dtype);
-    if (need > kStaticScratchBytes) return B200_ERR_TOO_LARGE;
+  if (batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0 && block_size > 0) {
+    // refuse only what would really use more scratch than the array holds: the same test the callee makes
+    // before it takes the split-context path (other shapes run the one-CTA-per-head kernel, which needs none)
+    const FastPlan pl = fast_plan(num_q_heads, num_kv_heads, head_dim, block_size, dtype);
+    const bool fast = pl.ok && aligned16(q) && aligned16(k_cache) && aligned16(v_cache);
+    if (fast && b200_paged_decode_gqa_workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, dtype) >
+                    kStaticScratchBytes)
+      return B200_ERR_TOO_LARGE;
   }
   void* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);

@@ -93,8 +93,9 @@ def workspace(device: torch.device, nbytes: int, tag: str) -> torch.Tensor:
     A captured CUDA graph has the address of the buffer it was captured with baked in, so a buffer
     that has been handed out is never freed: when a later call needs more, a larger one (at least
     twice the size, so all retired buffers together stay below the live one) replaces it for new
-    calls and the old one is kept alive for the graphs that still write to it.  No kernel keeps
-    state in its scratch between calls, so old and new buffers can be in use side by side."""
+    calls and the old one is kept alive for the graphs that still write to it.  Buffers start zero-filled
+    (the decode kernels keep arrival counters at the head of theirs, which every call returns to zero);
+    nothing else survives a call, so old and new buffers can be in use side by side."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (idx, tag)
     w = _workspaces.get(key)
@@ -102,7 +103,7 @@ def workspace(device: torch.device, nbytes: int, tag: str) -> torch.Tensor:
         if w is not None:
             _retired_workspaces.append(w)
             nbytes = max(nbytes, 2 * w.numel())
-        w = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        w = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
         _workspaces[key] = w
     return w
 

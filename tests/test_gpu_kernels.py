@@ -976,3 +976,40 @@ def test_a_barrier_wait_that_runs_out_is_reported_and_leaves_the_device_usable()
     rows = torch.tensor([0, 699, 700, 701, 1033, 1034, 2000, T - 130, T - 1])
     want = orc.prefill_varlen(q, k, v, cu, cu, D ** -0.5)
     assert (got.float().cpu()[rows] - want[rows]).abs().max().item() <= 2e-2
+
+
+# ----------------------------------------------------------------------------- split contexts merged in the launch
+def test_split_contexts_are_merged_inside_the_decode_launch_and_counters_return_to_zero():
+    """Contexts cut across thread blocks are merged by the last piece to arrive: calls of different shapes share
+    one scratch buffer back to back, every call matches the oracle, repeated calls are bit-identical (the merge
+    order is fixed), and the arrival counters at the head of the buffer are zero after every call.  A batch with
+    more (sequence, KV head) pairs than counters takes the separate merge kernel and matches as well."""
+    ops, orc = _ops(), _oracle()
+    from llm_from_scratch_b200.workloads import deal_blocks
+    shapes = [((32, 8, 128), [9000, 3, 4100, 0, 16, 17, 2500]), ((16, 4, 64), [700, 1300, 250, 1, 999, 64] * 8),
+              ((8, 8, 32), [5000, 5000, 33]), ((32, 8, 128), [6000, 1])]
+    for (Hq, Hkv, D), lens in shapes:
+        case = deal_blocks(lens, 16, np.random.default_rng(len(lens)), pad_blocks=2)
+        q = _randn((len(lens), Hq, D), 61, torch.bfloat16)
+        kc = _randn((case.num_blocks, 16, Hkv, D), 62, torch.bfloat16)
+        vc = _randn((case.num_blocks, 16, Hkv, D), 63, torch.bfloat16)
+        bt, cl = torch.from_numpy(case.block_tables).cuda(), torch.from_numpy(case.context_lens).cuda()
+        got = ops.paged_decode_gqa(q.cuda(), kc.cuda(), vc.cuda(), bt, cl, D ** -0.5)
+        again = ops.paged_decode_gqa(q.cuda(), kc.cuda(), vc.cuda(), bt, cl, D ** -0.5)
+        ops.check_status()
+        want = orc.paged_decode_gqa(q, kc, vc, case.block_tables, case.context_lens, D ** -0.5)
+        assert (got.float().cpu() - want).abs().max().item() <= 2e-2
+        assert torch.equal(got, again)
+        ws = ops._workspaces[(torch.cuda.current_device(), "decode")]
+        assert int(ws[:256 * 1024].view(torch.int32).abs().sum().item()) == 0
+    # 9,000 sequences x 8 KV heads: more pairs than the 65,536 counters
+    lens = [40] * 8990 + [3000] * 10
+    case = deal_blocks(lens, 16, np.random.default_rng(5), pad_blocks=2)
+    q = _randn((len(lens), 8, 64), 64, torch.bfloat16)
+    kc = _randn((case.num_blocks, 16, 8, 64), 65, torch.bfloat16)
+    bt, cl = torch.from_numpy(case.block_tables).cuda(), torch.from_numpy(case.context_lens).cuda()
+    got = ops.paged_decode_gqa(q.cuda(), kc.cuda(), kc.cuda(), bt, cl, 0.125)
+    ops.check_status()
+    rows = [0, 4000, 8989, 8990, 8999]
+    want = orc.paged_decode_gqa(q[rows], kc, kc, case.block_tables[rows], case.context_lens[rows], 0.125)
+    assert (got.float().cpu()[rows] - want).abs().max().item() <= 2e-2
