@@ -392,6 +392,20 @@ int b200_sample(const void* logits, int64_t row_stride, const float* temperature
                 void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Greedy head in two launches: the lm_head projection (TransformerLM.lm_head, model/transformer.py:160,183)
+ * fused with the greedy argmax of generate.py:62 / the T = 0 rows of the sampler:
+ *   tokens[r] = argmax_v bf16( hidden[r] . W[v] + bias[v] ), lowest v among equal maxima,
+ * i.e. what argmax over the bf16 logits of a biased linear layer returns, without writing the logits.
+ *   hidden [num_rows, k_dim] bf16 contiguous, w [vocab_size, k_dim] bf16, bias [vocab_size] bf16 or NULL,
+ *   tokens int64 [num_rows]; workspace of b200_lm_head_argmax_workspace_bytes() bytes, 256-byte aligned
+ *   (per-tile maxima; nothing survives the call).  tcgen05 kernel that streams W once; bf16 only, k_dim % 8 == 0.
+ * ------------------------------------------------------------------------------------------- */
+size_t b200_lm_head_argmax_workspace_bytes(int32_t num_rows, int32_t vocab_size);
+int b200_lm_head_argmax(const void* hidden, const void* w, const void* bias, int64_t* tokens, int32_t num_rows,
+                        int32_t vocab_size, int32_t k_dim, void* workspace, size_t workspace_bytes,
+                        int32_t dtype, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Diagnostic (no counterpart in the reference, which has no device code): runs the give-up path of the
  * bounded barrier waits that the tcgen05 / TMA kernels share.  One CTA holds tensor memory, arms a barrier
  * that can never complete, and waits on it from two threads: one with `poll_limit` polls (1..65536), one

@@ -54,6 +54,8 @@ SIGNATURES = {
     "b200_sample": (_i32, [_vp, _i64, _vp, _i64, _i32, _u64, _u64, _vp, _i32, _vp]),
     "b200_moe_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "b200_selftest_bounded_wait": (_i32, [_i32, _vp, _vp, _vp]),
+    "b200_lm_head_argmax_workspace_bytes": (_sz, [_i32, _i32]),
+    "b200_lm_head_argmax": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _sz, _i32, _vp, _vp]),
     "b200_mla_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),
     "b200_mla_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32,
                                _i64, _f32, _vp, _sz, _i32, _vp, _vp]),

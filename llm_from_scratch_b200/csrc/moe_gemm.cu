@@ -20,6 +20,11 @@
 // 128-byte swizzle) is filled by TMA and drained by tcgen05.mma; mbarriers carry full/empty; every
 // wait is bounded and a timeout aborts the CTA cleanly (status word = B200_ERR_TIMEOUT).
 // Experts with more than NPASS rows take several passes over their weight tile (L2 hits).
+//
+// Mode 2 turns the same kernel into the greedy head of the decoder (lm_head followed by argmax,
+// TransformerLM.lm_head model/transformer.py:160,183 and generate.py:62): one weight set [vocab, K], every row of
+// X belongs to it, and the epilogue keeps, per token and per 128-row vocabulary tile, only the largest logit
+// bf16(acc + bias) and its (lowest) index; a small second kernel reduces the tiles.  The logits are never written.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -45,6 +50,9 @@ struct GemmArgs {
   int32_t* status;
   int num_experts;          // routed experts; groups past them are chunks of the dense tail
   int dense_rows;           // rows after the grouped ones that all use weight set `num_experts`
+  int rows_single;          // mode 2: the row count of the single group (offsets is not read)
+  float* amax_val;          // mode 2: [tiles][rows_single] largest logit of the tile
+  int32_t* amax_idx;        // mode 2: [tiles][rows_single] its vocabulary index
 };
 
 template <int NPASS, int STAGES>
@@ -97,7 +105,10 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tm_x)) : "memory");
   }
   int e = blockIdx.y, row0, rows;
-  if (e < a.num_experts) {
+  if (a.mode == 2) {
+    row0 = 0;
+    rows = a.rows_single;
+  } else if (e < a.num_experts) {
     row0 = e ? a.offsets[e - 1] : 0;
     rows = a.offsets[e] - row0;
   } else {
@@ -245,7 +256,40 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
 #pragma unroll
         for (int j = 0; j < 16; ++j) xch[j * XCH_STRIDE + q * 32 + lane] = __uint_as_float(r[j]);
         epilogue_sync();
-        if (!swiglu) {
+        if (a.mode == 2) {
+          // 16 tokens x 8 groups of 16 vocabulary rows: first maximum of the group, then of the tile
+          const int j = et >> 3, g8 = et & 7;
+          const int tok = c0 + j;
+          float best = -INFINITY;
+          int best_i = 0x7fffffff;
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const int f = tile * BM + g8 * 16 + x;
+            if (f < a.n_out) {
+              float y = xch[j * XCH_STRIDE + g8 * 16 + x];
+              if (a.bias) y += __bfloat162float(a.bias[f]);
+              y = bf16_round(y);
+              if (y > best || best_i == 0x7fffffff) {
+                best = y;
+                best_i = f;
+              }
+            }
+          }
+#pragma unroll
+          for (int off = 1; off < 8; off <<= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+            if (ov > best || (ov == best && oi < best_i)) {
+              best = ov;
+              best_i = oi;
+            }
+          }
+          if (g8 == 0 && tok < n) {
+            const int64_t at = static_cast<int64_t>(tile) * a.rows_single + out_row0 + tok;
+            a.amax_val[at] = best;
+            a.amax_idx[at] = best_i;
+          }
+        } else if (!swiglu) {
           const int f8 = (et & 15) * 8, f = tile * BM + f8;
           const bool vec = (a.n_out & 7) == 0;
           for (int j = et >> 4; j < 16; j += 8) {
@@ -319,6 +363,35 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
   umma::fence_before_sync();
   __syncthreads();
   if (warp == 1) umma::tmem_dealloc(tmem, NPASS < 32 ? 32 : NPASS);
+}
+
+// Second stage of the greedy head: per token, the first maximum over the vocabulary tiles.  One warp per token.
+__global__ void __launch_bounds__(256)
+lm_head_argmax_finish_kernel(const float* __restrict__ val, const int32_t* __restrict__ idx, int tiles, int rows,
+                             int64_t* __restrict__ tokens) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int t = lane; t < tiles; t += 32) {      // tiles ascend with the vocabulary index: strict > keeps the first
+    const float v = val[static_cast<int64_t>(t) * rows + row];
+    const int i = idx[static_cast<int64_t>(t) * rows + row];
+    if (v > best || (v == best && i < best_i)) {
+      best = v;
+      best_i = i;
+    }
+  }
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+    if (ov > best || (ov == best && oi < best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  if (lane == 0) tokens[row] = best_i == 0x7fffffff ? 0 : best_i;
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -432,4 +505,56 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* b
   }
   const dim3 grid(tiles, num_experts + (dense_rows + 255) / 256);
   return launch<256, 4>(a, tw, tx, grid, early, s);
+}
+
+/* Greedy head: tokens[r] = argmax_v bf16(hidden[r] . W[v] + bias[v]), lowest v among equal maxima. */
+extern "C" size_t b200_lm_head_argmax_workspace_bytes(int32_t num_rows, int32_t vocab_size) {
+  if (num_rows <= 0 || vocab_size <= 0) return 0;
+  const size_t tiles = (static_cast<size_t>(vocab_size) + b200::BM - 1) / b200::BM;
+  return tiles * num_rows * (sizeof(float) + sizeof(int32_t)) + 256;
+}
+
+extern "C" int b200_lm_head_argmax(const void* hidden, const void* w, const void* bias, int64_t* tokens,
+                                   int32_t num_rows, int32_t vocab_size, int32_t k_dim, void* workspace,
+                                   size_t workspace_bytes, int32_t dtype, int32_t* status, void* stream) {
+  using namespace b200;
+  if (num_rows < 0 || vocab_size <= 0 || k_dim <= 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_BF16) return B200_ERR_UNSUPPORTED;
+  if (num_rows == 0) return B200_OK;
+  if (!hidden || !w || !tokens) return B200_ERR_ARG;
+  if (k_dim % 8 != 0 || !aligned16(hidden) || !aligned16(w)) return B200_ERR_ALIGN;
+  if (!workspace || workspace_bytes < b200_lm_head_argmax_workspace_bytes(num_rows, vocab_size)) return B200_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
+  CUtensorMap tw, tx;
+  if (!make_map(&tw, w, vocab_size, k_dim, BM) || !make_map(&tx, hidden, num_rows, k_dim, XBOX)) return B200_ERR_UNSUPPORTED;
+  const int tiles = (vocab_size + BM - 1) / BM;
+  GemmArgs a{};
+  a.n_out = vocab_size;
+  a.k_dim = k_dim;
+  a.mode = 2;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.status = status;
+  a.num_experts = 1;
+  a.rows_single = num_rows;
+  a.amax_val = static_cast<float*>(workspace);
+  a.amax_idx = reinterpret_cast<int32_t*>(a.amax_val + static_cast<size_t>(tiles) * num_rows);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(tiles, 1);
+  const int rc = num_rows <= 64 ? launch<64, 4>(a, tw, tx, grid, false, s) : launch<256, 4>(a, tw, tx, grid, false, s);
+  if (rc != B200_OK) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((num_rows + 7) / 8);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, lm_head_argmax_finish_kernel, static_cast<const float*>(a.amax_val),
+                         static_cast<const int32_t*>(a.amax_idx), tiles, static_cast<int>(num_rows), tokens) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
+  return launch_result();
 }

@@ -13,8 +13,10 @@
 // its (sequence, KV head); the warp whose arrival completes the count merges the pieces in fixed
 // CTA order (so the result does not depend on which warp came last), writes the output rows and
 // returns the counter to zero.  The counters occupy the first kDecodeCounterBytes of the workspace,
-// which must be zero when the buffer is first used; every launch leaves them zero.  Batches with
-// more (sequence, KV head) pairs than counters fall back to a separate merge kernel.
+// which must be zero when the buffer is first used; every launch leaves them zero.  That form serves
+// small batches (a decode step is then a chain of short dependent kernels, and this removes one);
+// larger batches use a separate merge kernel launched as a programmatic dependent, which merges all
+// sequences in parallel instead of lengthening the tails of the streaming CTAs.
 //
 // A CTA has one warp per KV head; the warps of a CTA walk the same blocks, so between them they
 // read each 16-token block of the pool as one contiguous Hkv*D*16*2-byte segment of K and one of
@@ -37,7 +39,9 @@ namespace {
 constexpr int kTok = 16;    // tokens per KV block on the fast path
 constexpr size_t kDecodeCounterBytes = 256 * 1024;  // arrival counters at the head of the workspace
 constexpr int64_t kDecodeCounters = kDecodeCounterBytes / sizeof(int32_t);
+constexpr int kFusedMergeMaxBatch = 32;  // batches up to this size merge split contexts inside the launch
 constexpr int kStages = 3;  // (K,V) tiles in flight per warp
+constexpr int kMinBlocksPerCta = 4;  // small problems use fewer CTAs instead of more pieces to merge
 constexpr int kMaxFastThreads = 512;
 
 struct DecodeArgs {
@@ -71,35 +75,48 @@ __device__ __forceinline__ int swizzle_chunk(int c, int t) {
 
 // Merge of the `np` pieces of (sequence `seq`, KV head `h`) by one warp: pieces live in the partial slots of
 // CTAs first .. first + np - 1 (slot 1 in the CTA where the sequence starts, slot 0 in the others).  Four
-// fp32 columns per lane, 32 / (D / 4) heads per pass.  Loads bypass L1: other SMs wrote the data.
+// fp32 columns per lane, 32 / (D / 4) heads per pass; the lanes of a head share the search for its maximum,
+// and the weighted sum takes four pieces per trip so that their loads are in flight together.  Loads bypass
+// L1: other SMs wrote the data.
 template <int D>
 __device__ __forceinline__ void merge_split_sequence(const DecodeArgs& a, int seq, int h, int G, int first,
                                                      int np, int lane) {
   constexpr int LPH = D / 4;    // lanes per head
   constexpr int HPP = 32 / LPH; // heads per pass
   const int64_t n = static_cast<int64_t>(a.Hq) * D;
-  const int col = (lane % LPH) * 4;
+  const int sub = lane % LPH;
+  const int col = sub * 4;
+  auto slot_of = [&](int p) -> int64_t { return static_cast<int64_t>(first + p) * 2 + (p == 0 ? 1 : 0); };
   for (int hb = 0; hb < G; hb += HPP) {
     const int hl = hb + lane / LPH;
     const bool active = hl < G;
     const int head = h * G + (active ? hl : 0);
     float M = -INFINITY;
-    for (int p = 0; p < np; ++p) {
-      const int64_t slot = static_cast<int64_t>(first + p) * 2 + (p == 0 ? 1 : 0);
-      M = fmaxf(M, __ldcg(a.part_ml + (slot * a.Hq + head) * 2));
-    }
+    for (int p = sub; p < np; p += LPH) M = fmaxf(M, __ldcg(a.part_ml + (slot_of(p) * a.Hq + head) * 2));
+#pragma unroll
+    for (int off = 1; off < LPH; off <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
     float L = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < np; ++p) {
-      const int64_t slot = static_cast<int64_t>(first + p) * 2 + (p == 0 ? 1 : 0);
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (slot * a.Hq + head) * 2));
-      const float w = exp2f(ml.x - M);
-      const float4 x = __ldcg(reinterpret_cast<const float4*>(a.part_o + slot * n + head * D + col));
-      L += w * ml.y;
-      acc.x += w * x.x;
-      acc.y += w * x.y;
-      acc.z += w * x.z;
-      acc.w += w * x.w;
+    for (int p0 = 0; p0 < np; p0 += 4) {
+      float2 ml[4];
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const bool in = p0 + u < np;
+        const int64_t slot = slot_of(in ? p0 + u : 0);
+        ml[u] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (slot * a.Hq + head) * 2));
+        x[u] = __ldcg(reinterpret_cast<const float4*>(a.part_o + slot * n + head * D + col));
+        if (!in) ml[u] = make_float2(-INFINITY, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float w = exp2f(ml[u].x - M);   // 0 for the padding of the last trip
+        L += w * ml[u].y;
+        acc.x += w * x[u].x;
+        acc.y += w * x[u].y;
+        acc.z += w * x[u].z;
+        acc.w += w * x[u].w;
+      }
     }
     if (active) {
       const float inv = 1.f / L;
@@ -150,7 +167,7 @@ paged_decode_bf16_kernel(const DecodeArgs a) {
       for (int e = threadIdx.x; e < a.Hq * D / 2; e += blockDim.x) row[e] = 0u;
     }
   }
-  const int Q = (T + P - 1) / P;
+  const int Q = T == 0 ? 0 : max((T + P - 1) / P, kMinBlocksPerCta);
   const int start = p * Q;
   if (Q == 0 || start >= T) return;
   const int cnt = min(Q, T - start);
@@ -760,7 +777,18 @@ extern "C" int b200_paged_decode_gqa(const void* q, const void* k_cache, const v
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
     const size_t grid = static_cast<size_t>(sms) * pl.ctas_per_sm;
     uint8_t* w = static_cast<uint8_t*>(workspace);
+    // Which merge: inside the launch for small batches, where a step is a chain of short kernels and one launch
+    // fewer shortens it (one 700-token sequence at 16/4 heads x 64: 9.1 against 10.2 us per call); a separate
+    // kernel, launched as a programmatic dependent, for large ones, where its 256 threads per sequence merge in
+    // parallel while the in-launch merges would lengthen the tail of the streaming CTAs (256 sequences of
+    // 200-1300 tokens: 41.1 against 43.6 us per call).
+#if defined(B200_DECODE_SEPARATE_MERGE)     // build-time switches for A/B timing of the two forms
+    const bool fused_merge = false;
+#elif defined(B200_DECODE_FUSED_MERGE)
     const bool fused_merge = static_cast<int64_t>(batch) * num_kv_heads <= kDecodeCounters;
+#else
+    const bool fused_merge = batch <= kFusedMergeMaxBatch;
+#endif
     a.counters = fused_merge ? reinterpret_cast<int32_t*>(w) : nullptr;
     w += kDecodeCounterBytes;
     a.part_o = reinterpret_cast<float*>(w);

@@ -205,31 +205,37 @@ class ModelRunner:
         v["context_lens"][:bs].copy_(ctx.context_lens)
         v["block_tables"][:bs, :ctx.block_tables.size(1)].copy_(ctx.block_tables)
         self.graphs[bucket].replay()
-        return v["logits"][:bs]
+        return self.model.compute_logits(v["outputs"][:bs])
 
     def run(self, seqs: list[Sequence], is_prefill: bool) -> list[int]:
+        greedy = not any(s.temperature for s in seqs)
         if not is_prefill and self.graphs and not self.enforce_eager and len(seqs) <= max(self.graphs):
-            logits = self._replay_decode(seqs)
-            if not any(s.temperature for s in seqs):
-                # all greedy: the argmax was part of the graph; reading it is the step's only sync
+            hidden = self._replay_decode(seqs)
+            if greedy:
+                # the fused head (projection + argmax) was part of the graph; reading it is the step's only sync
                 token_ids = self.graph_vars["greedy"][:len(seqs)].tolist()
                 reset_context()
                 return token_ids
-        elif is_prefill and self.prefill_graphs and (logits := self._replay_prefill(seqs)) is not None:
+        elif is_prefill and self.prefill_graphs and (hidden := self._replay_prefill(seqs)) is not None:
             self.decode_builder.invalidate(seqs)
         else:
             if is_prefill and self.decode_builder is not None:
                 self.decode_builder.invalidate(seqs)
             input_ids = self.prepare_prefill(seqs) if is_prefill else self.prepare_decode(seqs)
-            logits = self.run_model(input_ids, is_prefill)
+            with torch.inference_mode():
+                hidden = self.model(input_ids)
         with torch.inference_mode():
-            token_ids = self.sampler(logits, self.prepare_sample(seqs)).tolist()
+            if greedy:
+                token_ids = self.model.greedy_tokens(hidden).tolist()
+            else:
+                token_ids = self.sampler(self.model.compute_logits(hidden), self.prepare_sample(seqs)).tolist()
         reset_context()
         return token_ids
 
     @torch.inference_mode()
     def _replay_decode(self, seqs: list[Sequence], replay: bool = True) -> torch.Tensor:
-        """Decode step from a captured graph.  The graph's inputs live in one device buffer mirrored by
+        """Decode step from a captured graph; returns the final hidden states [n, d] (the graph has also written
+        the greedy tokens).  The graph's inputs live in one device buffer mirrored by
         one pinned host buffer: the step's metadata is written straight into the host mirror (padding
         rows: slot -1, context 0) and shipped with a single copy; nothing else runs before the replay."""
         n = len(seqs)
@@ -254,7 +260,7 @@ class ModelRunner:
                     block_tables=v["block_tables"][:n])
         if replay:
             self.graphs[bucket].replay()
-        return v["logits"][:n]
+        return v["outputs"][:n]
 
     def can_run_window(self, seqs: list[Sequence]) -> bool:
         """Whether ``run_window`` can serve this decode batch: captured graphs, all rows greedy."""
@@ -347,7 +353,8 @@ class ModelRunner:
 
     @torch.inference_mode()
     def _replay_prefill(self, seqs: list[Sequence]):
-        """Prefill step from a captured graph, or None when the batch does not fit one (a cached
+        """Prefill step from a captured graph: the hidden states of the padded batch (the context is left set for
+        the head), or None when the batch does not fit one (a cached
         prefix, which needs block tables, or more tokens / sequences than were captured)."""
         if len(seqs) > self.max_num_seqs:
             return None
@@ -379,7 +386,7 @@ class ModelRunner:
         self.prefill_dev[:end].copy_(self.prefill_host[:end], non_blocking=True)
         g.replay()
         set_context(True, cu[:n + 1], cu[:n + 1], m.max_seqlen_q, m.max_seqlen_k, slots, None, None, pos)
-        return self.model.compute_logits(self.prefill_out[:tokens])
+        return self.prefill_out[:tokens]
 
     # ------------------------------------------------------------------ CUDA graphs for decode
     @torch.inference_mode()
@@ -411,8 +418,8 @@ class ModelRunner:
         self.graph_host_np["slot_mapping"][:] = -1
         self.decode_builder = md.DecodeBatchBuilder(self.block_size, max_blocks, rows=4 * max_bs, device_rows=max_bs)
         v["outputs"] = torch.zeros(max_bs, self.model_config.d_model, dtype=self.dtype, device=dev)
-        # the graph also holds the lm_head GEMM and the greedy argmax, so a greedy step launches nothing else
-        v["logits"] = torch.zeros(max_bs, self.model_config.vocab_size, dtype=self.dtype, device=dev)
+        # the graph also holds the greedy head (lm_head projection fused with the argmax), so a greedy step
+        # launches nothing else; rows with a temperature take their logits from "outputs" after the replay
         v["greedy"] = torch.zeros(max_bs, dtype=torch.int64, device=dev)
         v["history"] = torch.zeros(self.block_size, max_bs, dtype=torch.int64, device=dev)   # run_window: tokens per step
         buckets = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
@@ -425,14 +432,13 @@ class ModelRunner:
                         block_tables=v["block_tables"][:b])
             positions = (v["context_lens"][:b] - 1).clamp_min(0)
             v["outputs"][:b] = self.model(v["input_ids"][:b], positions)       # warm-up, allocates workspaces
-            v["logits"][:b] = self.model.compute_logits(v["outputs"][:b])
+            self.model.greedy_tokens(v["outputs"][:b], out=v["greedy"][:b])
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool):
                 positions = (v["context_lens"][:b] - 1).clamp_min(0)
                 v["outputs"][:b] = self.model(v["input_ids"][:b], positions)
-                v["logits"][:b] = self.model.compute_logits(v["outputs"][:b])
-                torch.argmax(v["logits"][:b], dim=-1, out=v["greedy"][:b])
+                self.model.greedy_tokens(v["outputs"][:b], out=v["greedy"][:b])
             if pool is None:
                 pool = g.pool()
             self.graphs[b] = g

@@ -443,3 +443,18 @@ class EngineTransformerLM(nn.Module):
         if ctx.is_prefill:
             hidden = hidden[ctx.cu_seqlens_q[1:].long() - 1]
         return F.linear(hidden.to(self.dtype), self.w_head, self.b_head)
+
+    def greedy_tokens(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """argmax of ``compute_logits(hidden)`` per sequence (first maximum), int64 [num_seqs].  In bf16 the head
+        projection and the argmax are one fused pass over the head matrix (``ops.lm_head_argmax``): the logits
+        are never written; other dtypes take the logits and reduce them."""
+        ctx = get_context()
+        if ctx.is_prefill:
+            hidden = hidden[ctx.cu_seqlens_q[1:].long() - 1]
+        hidden = hidden.to(self.dtype)
+        if ops.lm_head_argmax_supported(hidden, self.w_head):
+            return ops.lm_head_argmax(hidden.contiguous(), self.w_head, self.b_head, out)
+        logits = F.linear(hidden, self.w_head, self.b_head)
+        if out is None:
+            return torch.argmax(logits, dim=-1)
+        return torch.argmax(logits, dim=-1, out=out)

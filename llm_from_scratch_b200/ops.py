@@ -554,6 +554,35 @@ def moe_grouped_gemm(x: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Ten
     return out
 
 
+def lm_head_argmax_supported(hidden: torch.Tensor, w: torch.Tensor) -> bool:
+    return (hidden.is_cuda and hidden.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and hidden.dim() == 2
+            and hidden.shape[1] % 8 == 0 and hidden.shape[0] > 0)
+
+
+def lm_head_argmax(hidden: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """Greedy tokens of hidden [R, d] under the head w [vocab, d] (+ bias [vocab]): argmax over the bf16 logits,
+    first maximum, without materialising the logits.  bf16; returns int64 [R]."""
+    dev = _cuda(hidden, w, bias, out)
+    R, d = hidden.shape
+    V = w.shape[0]
+    if hidden.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not hidden.is_contiguous() \
+            or not w.is_contiguous() or w.shape[1] != d:
+        raise ValueError("hidden [R, d] and w [vocab, d] must be contiguous bfloat16")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != V or not bias.is_contiguous()):
+        raise ValueError("bias must be contiguous bfloat16 [vocab]")
+    if out is None:
+        out = torch.empty(R, dtype=torch.int64, device=hidden.device)
+    elif out.dtype != torch.int64 or out.numel() != R or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int64 [R] tensor")
+    need = lib.b200_lm_head_argmax_workspace_bytes(R, V)
+    ws = workspace(dev, need, "lm_head")
+    check(lib.b200_lm_head_argmax(hidden.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                  out.data_ptr(), R, V, d, ws.data_ptr(), ws.numel(), _dt(hidden),
+                                  status_word(dev).data_ptr(), _stream()), "lm_head_argmax")
+    return out
+
+
 def moe_combine(expert_out: torch.Tensor, bias: torch.Tensor | None, row_expert: torch.Tensor,
                 row_weight: torch.Tensor, slot_to_row: torch.Tensor, shared: torch.Tensor | None = None):
     """Weighted sum of every token's expert rows in ascending expert order (+ bias, + shared expert),

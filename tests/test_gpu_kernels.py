@@ -818,7 +818,7 @@ def test_empty_inputs_are_no_ops():
     assert lib.b200_mla_decode(None, None, None, None, None, 1, None, 0, 16, 512, 64, 16, 2, 0.07, None, 0,
                                DTYPE_BF16, None, s) == 0
     assert lib.b200_prefill_varlen(None, None, None, None, 0, 0, 0, 0, 0, None, None, 0, 0, 0, 8, 2, 64, 64, 0.125,
-                                   None, None, None, 0, 0, 0, None, 0, 0, DTYPE_BF16, None, s) == 0
+                                   None, None, None, 0, 0, 0, None, None, 0, 0, DTYPE_BF16, None, s) == 0
     # a batch whose contexts are all empty: zero rows, no block is read
     q = torch.randn(3, 8, 64, device=dev).bfloat16()
     bt = torch.full((3, 4), -1, dtype=torch.int32, device=dev)
@@ -1013,3 +1013,38 @@ def test_split_contexts_are_merged_inside_the_decode_launch_and_counters_return_
     rows = [0, 4000, 8989, 8990, 8999]
     want = orc.paged_decode_gqa(q[rows], kc, kc, case.block_tables[rows], case.context_lens[rows], 0.125)
     assert (got.float().cpu()[rows] - want).abs().max().item() <= 2e-2
+
+
+# ----------------------------------------------------------------------------- greedy head
+@pytest.mark.parametrize("rows,vocab,d", [(1, 32000, 1024), (7, 1000, 256), (64, 32000, 1024), (65, 5000, 512),
+                                          (256, 32000, 1024), (300, 777, 128)])
+def test_lm_head_argmax_equals_argmax_of_the_bf16_logits(rows, vocab, d):
+    """Fused head (projection + first-maximum argmax, logits never written) against the CPU: logits in fp32 from
+    the bf16 operands, + bias, rounded to bf16 once (what the reference's biased bf16 Linear returns), argmax.
+    Rows whose two largest bf16 logits are closer than two rounding steps may legitimately pick either (the
+    accumulation order differs); there the chosen logit must still be within that distance of the maximum."""
+    ops = _ops()
+    h = (_randn((rows, d), 71, torch.float32)).bfloat16()
+    w = (_randn((vocab, d), 72, torch.float32) * d ** -0.5).bfloat16()
+    b = (_randn((vocab,), 73, torch.float32) * 0.1).bfloat16()
+    for bias in (b, None):
+        got = ops.lm_head_argmax(h.cuda(), w.cuda(), None if bias is None else bias.cuda()).cpu()
+        ops.check_status()
+        logits = h.float() @ w.float().t()
+        if bias is not None:
+            logits = logits + bias.float()
+        logits = logits.bfloat16().float()
+        want = logits.argmax(dim=-1)
+        top = logits.max(dim=-1).values
+        chosen = logits.gather(1, got.view(-1, 1)).squeeze(1)
+        step = top.abs() * 2.0 ** -7
+        assert (got >= 0).all() and (got < vocab).all()
+        assert ((top - chosen) <= 2 * step).all(), (top - chosen).max().item()
+        assert (got == want).float().mean().item() >= 0.97
+    # equal maxima: the lowest index wins
+    w2 = w.clone()
+    w2[5] = w2[900 % vocab] = w2[3]
+    got = ops.lm_head_argmax(h.cuda(), w2.cuda(), None).cpu()
+    logits = (h.float() @ w2.float().t()).bfloat16().float()
+    tie_rows = logits.argmax(dim=-1) == 3
+    assert (got[tie_rows] == 3).all()
