@@ -51,8 +51,7 @@ struct GemmArgs {
   int num_experts;          // routed experts; groups past them are chunks of the dense tail
   int dense_rows;           // rows after the grouped ones that all use weight set `num_experts`
   int rows_single;          // mode 2: the row count of the single group (offsets is not read)
-  float* amax_val;          // mode 2: [tiles][rows_single] largest logit of the tile
-  int32_t* amax_idx;        // mode 2: [tiles][rows_single] its vocabulary index
+  unsigned long long* amax_key;   // mode 2: [tiles][rows_single] best (logit, row) key of the tile
 };
 
 template <int NPASS, int STAGES>
@@ -247,6 +246,63 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
       if (!*s_go) break;
       umma::fence_after_sync();
       const int64_t out_row0 = static_cast<int64_t>(row0) + pass * NPASS;
+      if (a.mode == 2) {
+        // Greedy head: this thread owns vocabulary row f with one accumulator per token.  Every logit becomes a
+        // 64-bit key (order-preserving image of the bf16 logit, then the complement of f, so that the largest
+        // key is the largest logit at the lowest row).  32 tokens at a time, a butterfly over the warp's 32 rows
+        // leaves lane l with the best key of token c0 + l (31 exchanges instead of 32 x 5); the four warps then
+        // meet in shared memory.
+        const int f = tile * BM + q * 32 + lane;
+        const float bias_f = (a.bias && f < a.n_out) ? __bfloat162float(a.bias[f]) : 0.f;
+        unsigned long long* keys = reinterpret_cast<unsigned long long*>(xch);   // [4 warps][32 tokens]
+        for (int c0 = 0; c0 < N; c0 += 32) {
+          uint32_t r[32];
+          if (c0 + 32 <= N) {
+            umma::tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
+          } else {      // N is a multiple of 16: a last half chunk
+            uint32_t h[16];
+            umma::tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c0, h);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              r[j] = h[j];
+              r[j + 16] = 0;
+            }
+          }
+          unsigned long long key[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float y = bf16_round(__uint_as_float(r[j]) + bias_f);
+            uint32_t u = __float_as_uint(y);
+            u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+            key[j] = f < a.n_out ? (static_cast<unsigned long long>(u) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(f))
+                                 : 0ull;
+          }
+#pragma unroll
+          for (int sft = 16; sft >= 1; sft >>= 1) {
+            const bool upper = (lane & sft) != 0;
+#pragma unroll
+            for (int j = 0; j < sft; ++j) {
+              const unsigned long long keep = upper ? key[j + sft] : key[j];
+              const unsigned long long send = upper ? key[j] : key[j + sft];
+              const unsigned long long other = __shfl_xor_sync(0xffffffffu, send, sft);
+              key[j] = keep > other ? keep : other;
+            }
+          }
+          keys[q * 32 + lane] = key[0];
+          epilogue_sync();
+          if (q == 0) {
+            const int tok = c0 + lane;
+            unsigned long long best = keys[lane];
+#pragma unroll
+            for (int w = 1; w < 4; ++w) {
+              const unsigned long long o = keys[w * 32 + lane];
+              best = o > best ? o : best;
+            }
+            if (tok < n) a.amax_key[static_cast<int64_t>(tile) * a.rows_single + out_row0 + tok] = best;
+          }
+          epilogue_sync();
+        }
+      } else
       // 16 tokens at a time: every thread parks its feature's 16 accumulators in a [token][feature]
       // tile of shared memory, then the 128 threads walk the tile row-wise, 8 features per thread,
       // so that rounding / SwiGLU work is spread evenly and global stores are 16 bytes wide
@@ -256,40 +312,7 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
 #pragma unroll
         for (int j = 0; j < 16; ++j) xch[j * XCH_STRIDE + q * 32 + lane] = __uint_as_float(r[j]);
         epilogue_sync();
-        if (a.mode == 2) {
-          // 16 tokens x 8 groups of 16 vocabulary rows: first maximum of the group, then of the tile
-          const int j = et >> 3, g8 = et & 7;
-          const int tok = c0 + j;
-          float best = -INFINITY;
-          int best_i = 0x7fffffff;
-#pragma unroll
-          for (int x = 0; x < 16; ++x) {
-            const int f = tile * BM + g8 * 16 + x;
-            if (f < a.n_out) {
-              float y = xch[j * XCH_STRIDE + g8 * 16 + x];
-              if (a.bias) y += __bfloat162float(a.bias[f]);
-              y = bf16_round(y);
-              if (y > best || best_i == 0x7fffffff) {
-                best = y;
-                best_i = f;
-              }
-            }
-          }
-#pragma unroll
-          for (int off = 1; off < 8; off <<= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
-            if (ov > best || (ov == best && oi < best_i)) {
-              best = ov;
-              best_i = oi;
-            }
-          }
-          if (g8 == 0 && tok < n) {
-            const int64_t at = static_cast<int64_t>(tile) * a.rows_single + out_row0 + tok;
-            a.amax_val[at] = best;
-            a.amax_idx[at] = best_i;
-          }
-        } else if (!swiglu) {
+        if (!swiglu) {
           const int f8 = (et & 15) * 8, f = tile * BM + f8;
           const bool vec = (a.n_out & 7) == 0;
           for (int j = et >> 4; j < 16; j += 8) {
@@ -365,33 +388,25 @@ moe_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_w,
   if (warp == 1) umma::tmem_dealloc(tmem, NPASS < 32 ? 32 : NPASS);
 }
 
-// Second stage of the greedy head: per token, the first maximum over the vocabulary tiles.  One warp per token.
+// Second stage of the greedy head: per token, the largest key over the vocabulary tiles (largest logit, lowest
+// row among equals).  One warp per token.
 __global__ void __launch_bounds__(256)
-lm_head_argmax_finish_kernel(const float* __restrict__ val, const int32_t* __restrict__ idx, int tiles, int rows,
+lm_head_argmax_finish_kernel(const unsigned long long* __restrict__ keys, int tiles, int rows,
                              int64_t* __restrict__ tokens) {
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= rows) return;
-  float best = -INFINITY;
-  int best_i = 0x7fffffff;
-  for (int t = lane; t < tiles; t += 32) {      // tiles ascend with the vocabulary index: strict > keeps the first
-    const float v = val[static_cast<int64_t>(t) * rows + row];
-    const int i = idx[static_cast<int64_t>(t) * rows + row];
-    if (v > best || (v == best && i < best_i)) {
-      best = v;
-      best_i = i;
-    }
+  unsigned long long best = 0ull;
+  for (int t = lane; t < tiles; t += 32) {
+    const unsigned long long k = keys[static_cast<int64_t>(t) * rows + row];
+    best = k > best ? k : best;
   }
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
-    if (ov > best || (ov == best && oi < best_i)) {
-      best = ov;
-      best_i = oi;
-    }
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
+    best = o > best ? o : best;
   }
-  if (lane == 0) tokens[row] = best_i == 0x7fffffff ? 0 : best_i;
+  if (lane == 0) tokens[row] = best == 0ull ? 0 : static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(best));
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -511,7 +526,7 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* b
 extern "C" size_t b200_lm_head_argmax_workspace_bytes(int32_t num_rows, int32_t vocab_size) {
   if (num_rows <= 0 || vocab_size <= 0) return 0;
   const size_t tiles = (static_cast<size_t>(vocab_size) + b200::BM - 1) / b200::BM;
-  return tiles * num_rows * (sizeof(float) + sizeof(int32_t)) + 256;
+  return tiles * num_rows * sizeof(unsigned long long) + 256;
 }
 
 extern "C" int b200_lm_head_argmax(const void* hidden, const void* w, const void* bias, int64_t* tokens,
@@ -536,8 +551,7 @@ extern "C" int b200_lm_head_argmax(const void* hidden, const void* w, const void
   a.status = status;
   a.num_experts = 1;
   a.rows_single = num_rows;
-  a.amax_val = static_cast<float*>(workspace);
-  a.amax_idx = reinterpret_cast<int32_t*>(a.amax_val + static_cast<size_t>(tiles) * num_rows);
+  a.amax_key = static_cast<unsigned long long*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(tiles, 1);
   const int rc = num_rows <= 64 ? launch<64, 4>(a, tw, tx, grid, false, s) : launch<256, 4>(a, tw, tx, grid, false, s);
@@ -551,8 +565,8 @@ extern "C" int b200_lm_head_argmax(const void* hidden, const void* w, const void
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, lm_head_argmax_finish_kernel, static_cast<const float*>(a.amax_val),
-                         static_cast<const int32_t*>(a.amax_idx), tiles, static_cast<int>(num_rows), tokens) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, lm_head_argmax_finish_kernel, static_cast<const unsigned long long*>(a.amax_key),
+                         tiles, static_cast<int>(num_rows), tokens) != cudaSuccess) {
     cudaGetLastError();
     return B200_ERR_LAUNCH;
   }
