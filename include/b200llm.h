@@ -311,6 +311,21 @@ int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t nu
                    int32_t identity_tail, void* workspace, size_t workspace_bytes, int32_t dtype,
                    void* stream);
 
+/* The gate projection, the routing above and (optionally) the gather of the routed rows in ONE launch, for
+ * batches of at most 256 tokens (decode): gate_logits = bf16(x . gate_weight^T) (Gate.forward, moe.py:49-52),
+ * then exactly b200_moe_route.  x [num_tokens, d_model] bf16 contiguous, gate_weight [num_experts, d_model] bf16.
+ * gathered (may be NULL): [num_tokens*top_k (+ num_tokens with identity_tail), d_model], row i = x[sorted_token[i]]
+ * (the index_select that feeds b200_moe_grouped_gemm); one thread block copies the rows, so pass it for small
+ * batches only.  workspace: b200_moe_gate_route_workspace_bytes() bytes, 256-byte aligned, zero when first
+ * used (its first word is a ticket counter that every call returns to zero).  More than 256 tokens, another
+ * dtype or d_model % 8 != 0: B200_ERR_UNSUPPORTED (use a GEMM and b200_moe_route). */
+size_t b200_moe_gate_route_workspace_bytes(void);
+int b200_moe_gate_route(const void* x, const void* gate_weight, const float* expert_bias, int32_t num_tokens,
+                        int32_t num_experts, int32_t top_k, int32_t d_model, int32_t* sorted_token,
+                        int32_t* sorted_expert, void* sorted_weight, int32_t* expert_offsets,
+                        int32_t* slot_to_row, int32_t identity_tail, void* gathered, void* workspace,
+                        size_t workspace_bytes, int32_t dtype, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * SwiGLU of fused up-projection rows (model/architecture/mlp.py:61-67: w2(silu(w1 x) * w3 x)):
  *   h [num_rows, 2*d_ff] = [w1 x | w3 x];  act [num_rows, d_ff] = silu(h1 + b1) * (h3 + b3).

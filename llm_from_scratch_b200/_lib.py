@@ -47,6 +47,9 @@ SIGNATURES = {
                                        _i32, _i32, _i32, _f32, _i32, _vp, _vp]),
     "b200_moe_route_workspace_bytes": (_sz, [_i32, _i32]),
     "b200_moe_route": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _sz, _i32, _vp]),
+    "b200_moe_gate_route_workspace_bytes": (_sz, []),
+    "b200_moe_gate_route": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp,
+                                   _sz, _i32, _vp]),
     "b200_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     "b200_moe_grouped_gemm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "b200_decode_advance": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _vp, _vp, _vp]),

@@ -200,6 +200,25 @@ qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
   const T* qr = static_cast<const T*>(a.qkv) + t * a.qkv_stride;
   const T* kr = qr + Wq;
   const T* vr = kr + Wk;
+  // position, slot and the rotation coefficients first: they do not depend on the row's norm, so their two
+  // dependent round trips run under the loads and reductions below instead of after them.  A lane's eight
+  // elements sit at the same offset of their head in every 256-element chunk (256 is a multiple of D), so one
+  // set of eight cosines and sines serves all chunks of q and k.
+  int64_t pos = a.positions[t];
+  int64_t slot = a.k_cache ? a.slots[t] : -1;
+  if (pos < 0 || pos >= a.max_pos) {
+    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
+    pos = pos < 0 ? 0 : a.max_pos - 1;
+  }
+  const float* cs = a.rope + pos * a.D;
+  const int j0 = (lane * 8) % a.D;
+  const bool first = j0 < half;
+  const int jj = first ? j0 : j0 - half;
+  const float4 c0 = *reinterpret_cast<const float4*>(cs + jj), c1 = *reinterpret_cast<const float4*>(cs + jj + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(cs + half + jj);
+  const float4 s1 = *reinterpret_cast<const float4*>(cs + half + jj + 4);
+  const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
   float sq = 0.f, sk = 0.f;
   for (int c = lane * 8; c < Wq; c += 256) {
     Bf16x8 u;
@@ -221,13 +240,6 @@ qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
   }
   const float iq = rsqrtf(warp_sum(sq) / static_cast<float>(Wq) + a.eps);
   const float ik = rsqrtf(warp_sum(sk) / static_cast<float>(Wk) + a.eps);
-  int64_t pos = a.positions[t];
-  if (pos < 0 || pos >= a.max_pos) {
-    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
-    pos = pos < 0 ? 0 : a.max_pos - 1;
-  }
-  const float* cs = a.rope + pos * a.D;
-  int64_t slot = a.k_cache ? a.slots[t] : -1;
   if (slot >= a.num_slots) {
     if (lane == 0) report(a.status, B200_ERR_BOUNDS);
     slot = -1;
@@ -238,14 +250,6 @@ qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
     u.u = *reinterpret_cast<const uint4*>(src + c);
     const float4 w0 = *reinterpret_cast<const float4*>(nw + c), w1 = *reinterpret_cast<const float4*>(nw + c + 4);
     const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    const int j = c % a.D;
-    const bool first = j < half;
-    const int jj = first ? j : j - half;
-    const float4 c0 = *reinterpret_cast<const float4*>(cs + jj), c1 = *reinterpret_cast<const float4*>(cs + jj + 4);
-    const float4 s0 = *reinterpret_cast<const float4*>(cs + half + jj);
-    const float4 s1 = *reinterpret_cast<const float4*>(cs + half + jj + 4);
-    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float xv = __bfloat162float(__float2bfloat16(__bfloat162float(u.b[i]) * inv * ww[i]));

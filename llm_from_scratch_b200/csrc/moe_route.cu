@@ -54,6 +54,27 @@ struct MaskOf<64> {
 __device__ __forceinline__ int lowest_bit(uint32_t m) { return __ffs(static_cast<int>(m)) - 1; }
 __device__ __forceinline__ int lowest_bit(unsigned long long m) { return __ffsll(static_cast<long long>(m)) - 1; }
 
+// bit e set: the token routes to expert e; `biased` holds logits + bias of the E experts (-inf beyond E).
+template <int EMAX>
+__device__ __forceinline__ typename MaskOf<EMAX>::type top_k_mask(const float (&biased)[EMAX], int E, int K) {
+  using M = typename MaskOf<EMAX>::type;
+  M taken = 0;
+  for (int k = 0; k < K; ++k) {            // k maxima, lower index first among equals
+    int best = -1;
+    float bv = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      const bool open = e < E && !((taken >> e) & M(1));
+      if (open && (best < 0 || biased[e] > bv)) {
+        best = e;
+        bv = biased[e];
+      }
+    }
+    taken |= M(1) << best;
+  }
+  return taken;
+}
+
 // bit e set: token t routes to expert e.  EMAX (>= E) is a compile-time bound so that the biased
 // logits live in registers.
 template <typename T, int EMAX>
@@ -113,66 +134,71 @@ __global__ void __launch_bounds__(kTok) moe_count_kernel(const RouteArgs a) {
   }
 }
 
-template <typename T, int EMAX>
-__global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
-  __shared__ int32_t warp_cnt[kWarps][kMaxE];   // rows of expert e owned by warp w
-  __shared__ int32_t warp_pre[kWarps][kMaxE];   // ... by the warps before w
-  __shared__ int32_t tot_s[kMaxE], bef_s[kMaxE];
-  __shared__ int32_t base[kMaxE];               // first output row of this CTA's rows of expert e
+// Shared memory of the scatter step.
+struct ScatterSmem {
+  int32_t warp_cnt[kWarps][kMaxE];   // rows of expert e owned by warp w
+  int32_t warp_pre[kWarps][kMaxE];   // ... by the warps before w
+  int32_t tot_s[kMaxE], bef_s[kMaxE];
+  int32_t base[kMaxE];               // first output row of this CTA's rows of expert e
+};
+
+// routing weights of the selected experts of one token (ascending expert order): sigmoid scores of the
+// logits, renormalised over the selection when K > 1, with the roundings of the dtype
+template <typename T, typename M, typename LogitOf>
+__device__ __forceinline__ void routing_weights(M taken, int K, LogitOf logit_of, int* sel, float* wsel) {
+  float sum = 0.f;
+  int n = 0;
+  for (M rest = taken; rest != 0 && n < kMaxK; rest &= rest - 1, ++n) {   // set bits, ascending
+    const int e = lowest_bit(rest);
+    sel[n] = e;
+    wsel[n] = round_to<T>(1.f / (1.f + expf(-logit_of(e))));
+    sum += wsel[n];
+  }
+  if (K > 1) {
+    const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
+    for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
+  }
+}
+
+// The counting sort of one CTA's 256 tokens: thread `threadIdx.x` owns token t with expert mask `taken`,
+// experts sel[] and weights wsel[]; cta / num_ctas place the CTA among those that share the sort (their
+// per-expert counts are in a.cta_counts when num_ctas > 1).  Every thread of the CTA must call it.
+template <typename T, typename M>
+__device__ __forceinline__ void scatter_rows(const RouteArgs& a, ScatterSmem& sm, int t, M taken, const int* sel,
+                                             const float* wsel, int cta, int num_ctas) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int E = a.E, K = a.K;
-  const int t = blockIdx.x * kTok + tid;
-  using M = typename MaskOf<EMAX>::type;
-  const M taken = t < a.T ? select_mask<T, EMAX>(a, t) : M(0);
   int ranks[kMaxK];
-  warp_counts(taken, E, warp_cnt, ranks);
-  // routing weights of the selected experts, ascending expert order (before the barrier: independent of it)
-  int sel[kMaxK];
-  float wsel[kMaxK];
-  if (t < a.T) {
-    const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * E;
-    float sum = 0.f;
-    int n = 0;
-    for (M rest = taken; rest != 0 && n < kMaxK; rest &= rest - 1, ++n) {   // set bits, ascending
-      const int e = lowest_bit(rest);
-      sel[n] = e;
-      wsel[n] = round_to<T>(1.f / (1.f + expf(-to_float<T>(row[e]))));
-      sum += wsel[n];
-    }
-    if (K > 1) {
-      const float denom = round_to<T>(round_to<T>(sum) + 1e-10f);
-      for (int k = 0; k < K; ++k) wsel[k] = round_to<T>(wsel[k] / denom);
-    }
-  }
+  warp_counts(taken, E, sm.warp_cnt, ranks);
   __syncthreads();
   // rows of every expert in all CTAs (tot) and in the CTAs before this one (bef); prefix over warps
   for (int i = tid; i < kWarps * E; i += kTok) {
     const int w = i / E, e = i - w * E;
     int pre = 0;
-    for (int x = 0; x < w; ++x) pre += warp_cnt[x][e];
-    warp_pre[w][e] = pre;
+    for (int x = 0; x < w; ++x) pre += sm.warp_cnt[x][e];
+    sm.warp_pre[w][e] = pre;
   }
   if (tid < E) {
     int tot = 0, bef = 0;
-    if (gridDim.x > 1) {
-      for (int c = 0; c < static_cast<int>(gridDim.x); ++c) {
+    if (num_ctas > 1) {
+      for (int c = 0; c < num_ctas; ++c) {
         const int v = a.cta_counts[c * E + tid];
         tot += v;
-        if (c < static_cast<int>(blockIdx.x)) bef += v;
+        if (c < cta) bef += v;
       }
     } else {
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) tot += warp_cnt[w][tid];
+      for (int w = 0; w < kWarps; ++w) tot += sm.warp_cnt[w][tid];
     }
-    tot_s[tid] = tot;
-    bef_s[tid] = bef;
+    sm.tot_s[tid] = tot;
+    sm.bef_s[tid] = bef;
   }
   __syncthreads();
   if (warp == 0) {       // exclusive scan of the expert totals, 32 experts per trip
     int carry = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
       const int e = e0 + lane;
-      const int v = e < E ? tot_s[e] : 0;
+      const int v = e < E ? sm.tot_s[e] : 0;
       int x = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -180,8 +206,8 @@ __global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
         if (lane >= o) x += y;
       }
       if (e < E) {
-        base[e] = carry + x - v + bef_s[e];
-        if (blockIdx.x == 0) a.offsets[e] = carry + x;
+        sm.base[e] = carry + x - v + sm.bef_s[e];
+        if (cta == 0) a.offsets[e] = carry + x;
       }
       carry += __shfl_sync(0xffffffffu, x, 31);
     }
@@ -192,11 +218,132 @@ __global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
   T* wout = static_cast<T*>(a.sorted_weight);
   for (int k = 0; k < K; ++k) {
     const int e = sel[k];
-    const int pos = base[e] + warp_pre[warp][e] + ranks[k];
+    const int pos = sm.base[e] + sm.warp_pre[warp][e] + ranks[k];
     a.sorted_token[pos] = t;
     a.sorted_expert[pos] = e;
     wout[pos] = from_float<T>(wsel[k]);
     a.slot_to_row[t * K + k] = pos;
+  }
+}
+
+template <typename T, int EMAX>
+__global__ void __launch_bounds__(kTok) moe_scatter_kernel(const RouteArgs a) {
+  __shared__ ScatterSmem sm;
+  const int t = blockIdx.x * kTok + threadIdx.x;
+  using M = typename MaskOf<EMAX>::type;
+  const M taken = t < a.T ? select_mask<T, EMAX>(a, t) : M(0);
+  int sel[kMaxK];
+  float wsel[kMaxK];
+  if (t < a.T) {
+    const T* row = static_cast<const T*>(a.logits) + static_cast<int64_t>(t) * a.E;
+    routing_weights<T>(taken, a.K, [&](int e) { return to_float<T>(row[e]); }, sel, wsel);
+  }
+  scatter_rows<T>(a, sm, t, taken, sel, wsel, blockIdx.x, gridDim.x);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Gate projection + routing (+ row gather) in one launch, for batches of at most 256 tokens (decode):
+//   logits[t, e] = bf16( x[t] . gate_w[e] )        Gate.forward, moe.py:49-52 (a bias-free matmul)
+// followed by exactly the selection, weights and counting sort of the kernels above.  Phase 1: a warp per
+// token computes the E dot products (x row in registers, gate rows through L1), selects the experts and
+// leaves (mask, weights) in the workspace; CTAs take a ticket when they are done.  Phase 2: the CTA that
+// takes the last ticket sorts all tokens (one thread per token), and when `gathered` is given copies the
+// rows of x into sorted order (+ the identity tail) — worth doing here only for small batches, where one
+// SM copies the few rows faster than another launch would start.
+struct GateRouteArgs {
+  RouteArgs r;                      // logits unused
+  const __nv_bfloat16* x;           // [T, d]
+  const __nv_bfloat16* gate_w;      // [E, d]
+  int d;
+  int32_t* ticket;                  // zero between launches
+  unsigned long long* masks;        // [T]
+  float* weights;                   // [T][kMaxK]
+  __nv_bfloat16* gathered;          // [T*K (+ T), d] or null
+};
+
+constexpr int kGateWarps = 8;       // tokens per CTA in phase 1
+
+template <int EMAX>
+__global__ void __launch_bounds__(kTok) moe_gate_route_kernel(const GateRouteArgs g) {
+  using T = __nv_bfloat16;
+  using M = typename MaskOf<EMAX>::type;
+  __shared__ ScatterSmem sm;
+  __shared__ int s_last;
+  const RouteArgs& a = g.r;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int E = a.E, d = g.d;
+  {
+    const int t = blockIdx.x * kGateWarps + warp;
+    if (t < a.T) {
+      float acc[EMAX];
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e) acc[e] = 0.f;
+      const T* xr = g.x + static_cast<int64_t>(t) * d;
+      for (int c = lane * 8; c < d; c += 256) {
+        union { uint4 u; T b[8]; } xv;
+        xv.u = *reinterpret_cast<const uint4*>(xr + c);
+        float xf[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xf[i] = __bfloat162float(xv.b[i]);
+#pragma unroll
+        for (int e = 0; e < EMAX; ++e) {
+          if (e < E) {
+            union { uint4 u; T b[8]; } wv;
+            wv.u = __ldg(reinterpret_cast<const uint4*>(g.gate_w + static_cast<int64_t>(e) * d + c));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e] = fmaf(xf[i], __bfloat162float(wv.b[i]), acc[e]);
+          }
+        }
+      }
+      float biased[EMAX];
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e) {
+        acc[e] = round_to<T>(warp_sum(acc[e]));     // every lane holds the logit
+        biased[e] = e < E ? round_to<T>(acc[e] + round_to<T>(a.bias[e])) : -INFINITY;
+      }
+      const M taken = top_k_mask<EMAX>(biased, E, a.K);
+      int sel[kMaxK];
+      float wsel[kMaxK];
+      routing_weights<T>(taken, a.K, [&](int e) {
+        float v = 0.f;
+#pragma unroll
+        for (int x = 0; x < EMAX; ++x) v = x == e ? acc[x] : v;
+        return v; }, sel, wsel);
+      if (lane == 0) {
+        g.masks[t] = static_cast<unsigned long long>(taken);
+        for (int k = 0; k < a.K; ++k) g.weights[t * kMaxK + k] = wsel[k];
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(g.ticket, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid == 0) *g.ticket = 0;     // ready for the next launch
+  const int t = tid;
+  M taken = 0;
+  int sel[kMaxK];
+  float wsel[kMaxK];
+  if (t < a.T) {
+    taken = static_cast<M>(__ldcg(g.masks + t));
+    int n = 0;
+    for (M rest = taken; rest != 0 && n < kMaxK; rest &= rest - 1, ++n) {
+      sel[n] = lowest_bit(rest);
+      wsel[n] = __ldcg(g.weights + t * kMaxK + n);
+    }
+  }
+  scatter_rows<T>(a, sm, t, taken, sel, wsel, 0, 1);
+  if (g.gathered == nullptr) return;
+  __syncthreads();                   // sorted_token is complete (written by this CTA)
+  const int rows = a.T * a.K + (a.identity_tail ? a.T : 0);
+  const int per_row = d / 8;         // 16-byte pieces per row
+  for (int i = tid; i < rows * per_row; i += kTok) {
+    const int r = i / per_row, c = i - r * per_row;
+    const int src = a.sorted_token[r];
+    reinterpret_cast<uint4*>(g.gathered + static_cast<int64_t>(r) * d)[c] =
+        *reinterpret_cast<const uint4*>(g.x + static_cast<int64_t>(src) * d + c * 8);
   }
 }
 
@@ -377,6 +524,54 @@ extern "C" int b200_moe_route(const void* gate_logits, const float* expert_bias,
     else ROUTE_LAUNCH(__nv_bfloat16, 64);
   }
 #undef ROUTE_LAUNCH
+  return launch_result();
+}
+
+extern "C" size_t b200_moe_gate_route_workspace_bytes(void) {
+  return 256 + b200::kTok * sizeof(unsigned long long) + b200::kTok * b200::kMaxK * sizeof(float);
+}
+
+extern "C" int b200_moe_gate_route(const void* x, const void* gate_weight, const float* expert_bias,
+                                   int32_t num_tokens, int32_t num_experts, int32_t top_k, int32_t d_model,
+                                   int32_t* sorted_token, int32_t* sorted_expert, void* sorted_weight,
+                                   int32_t* expert_offsets, int32_t* slot_to_row, int32_t identity_tail,
+                                   void* gathered, void* workspace, size_t workspace_bytes, int32_t dtype,
+                                   void* stream) {
+  using namespace b200;
+  if (num_tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts || d_model <= 0) return B200_ERR_ARG;
+  if (dtype != B200_DTYPE_BF16 || num_experts > kMaxE || top_k > kMaxK || num_tokens > kTok || d_model % 8 != 0)
+    return B200_ERR_UNSUPPORTED;
+  if (num_tokens == 0) return B200_ERR_UNSUPPORTED;   // the plain routing entry point writes the empty offsets
+  if (!x || !gate_weight || !expert_bias || !sorted_token || !sorted_expert || !sorted_weight || !expert_offsets ||
+      !slot_to_row)
+    return B200_ERR_ARG;
+  if (!aligned16(x) || !aligned16(gate_weight) || (gathered && !aligned16(gathered))) return B200_ERR_ALIGN;
+  if (!workspace || workspace_bytes < b200_moe_gate_route_workspace_bytes()) return B200_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200_ERR_ALIGN;
+  GateRouteArgs g{};
+  g.r.bias = expert_bias;
+  g.r.T = num_tokens;
+  g.r.E = num_experts;
+  g.r.K = top_k;
+  g.r.sorted_token = sorted_token;
+  g.r.sorted_expert = sorted_expert;
+  g.r.sorted_weight = sorted_weight;
+  g.r.offsets = expert_offsets;
+  g.r.slot_to_row = slot_to_row;
+  g.r.identity_tail = identity_tail != 0;
+  g.x = static_cast<const __nv_bfloat16*>(x);
+  g.gate_w = static_cast<const __nv_bfloat16*>(gate_weight);
+  g.d = d_model;
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  g.ticket = reinterpret_cast<int32_t*>(w);
+  g.masks = reinterpret_cast<unsigned long long*>(w + 256);
+  g.weights = reinterpret_cast<float*>(w + 256 + kTok * sizeof(unsigned long long));
+  g.gathered = static_cast<__nv_bfloat16*>(gathered);
+  const int grid = (num_tokens + kGateWarps - 1) / kGateWarps;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (num_experts <= 16) moe_gate_route_kernel<16><<<grid, kTok, 0, s>>>(g);
+  else if (num_experts <= 32) moe_gate_route_kernel<32><<<grid, kTok, 0, s>>>(g);
+  else moe_gate_route_kernel<64><<<grid, kTok, 0, s>>>(g);
   return launch_result();
 }
 

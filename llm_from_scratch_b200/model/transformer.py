@@ -195,21 +195,37 @@ class MoE(nn.Module):
         T = x.shape[0]
         small = (T * self.K <= self.own_gemm_max_rows_per_expert * self.E and x.shape[1] % 8 == 0
                  and self.d_ff % 8 == 0)
+        fused_gate = T <= ops.MOE_GATE_ROUTE_MAX_TOKENS and x.is_contiguous()
+        in_kernel_gather = fused_gate and T <= ops.MOE_GATE_ROUTE_GATHER_MAX_TOKENS
+
+        def route(identity_tail):
+            """(sorted_token, experts, weights, offsets, slot_to_row, rows of x in sorted order)"""
+            if fused_gate:     # gate projection + routing (+ the gather for small batches) in one launch
+                tok, experts, w, offs, inv, xs = ops.moe_gate_route(x, self.gate_w, self.gate_bias, self.K,
+                                                                    identity_tail=identity_tail, gather=in_kernel_gather)
+            else:
+                tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K,
+                                                           identity_tail=identity_tail)
+                xs = None
+            if xs is None:
+                xs = x.index_select(0, tok)
+            return tok, experts, w, offs, inv, xs
+
+        # early launch of a grouped GEMM needs its offsets and weights complete before the kernel in front of it
+        # started: true behind the separate gather, not when the routing launch itself is that kernel
+        early_up = not in_kernel_gather
         if small and self.w13_all is not None:
-            # decode sizes with a shared expert: its rows (every token) ride in the same two launches as
-            # the routed rows, as one more weight set; biases are added in the GEMM epilogues
-            tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K,
-                                                       identity_tail=True)
-            xs = x.index_select(0, tok)                              # [T*K routed rows | T shared rows]
-            # early_launch: offs and the weights are older than the gather / the up-projection before each GEMM
-            act = ops.moe_grouped_gemm(xs, self.w13_all, offs, self.b13_all, swiglu=True, dense_rows=T, early_launch=True)
+            # decode sizes with a shared expert: its rows (every token, gathered through the identity tail of the
+            # routing) ride in the same two launches as the routed rows, as one more weight set; biases are added
+            # in the GEMM epilogues
+            tok, experts, w, offs, inv, xs = route(True)           # [T*K routed rows | T shared rows]
+            act = ops.moe_grouped_gemm(xs, self.w13_all, offs, self.b13_all, swiglu=True, dense_rows=T, early_launch=early_up)
             y = ops.moe_grouped_gemm(act, self.w2_all, offs, self.b2_all, dense_rows=T, early_launch=True)
             R = T * self.K
             return ops.moe_combine(y[:R], None, experts, w, inv, y[R:])
-        tok, experts, w, offs, inv = ops.moe_route((x @ self.gate_w.t()).contiguous(), self.gate_bias, self.K)
-        xs = x.index_select(0, tok)
+        tok, experts, w, offs, inv, xs = route(False)
         if small:
-            act = ops.moe_grouped_gemm(xs, self.w13, offs, self.b13, swiglu=True, early_launch=True)
+            act = ops.moe_grouped_gemm(xs, self.w13, offs, self.b13, swiglu=True, early_launch=early_up)
             y = ops.moe_grouped_gemm(act, self.w2, offs, early_launch=True)
         else:
             act = ops.swiglu(torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs), self.b13, experts)

@@ -505,6 +505,39 @@ def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int, 
     return tok, exp, w, offs, inv
 
 
+MOE_GATE_ROUTE_MAX_TOKENS = 256
+MOE_GATE_ROUTE_GATHER_MAX_TOKENS = 32   # up to here the routing launch also copies the routed rows
+
+
+def moe_gate_route(x: torch.Tensor, gate_w: torch.Tensor, expert_bias: torch.Tensor, top_k: int,
+                   identity_tail: bool = False, gather: bool = False):
+    """Gate projection + ``moe_route`` in one launch for at most 256 bf16 tokens.  Returns (sorted_token,
+    sorted_expert, sorted_weight, expert_offsets, slot_to_row, gathered): ``gathered`` is x[sorted_token]
+    when ``gather`` is set (meant for small batches: one thread block copies the rows), else None."""
+    dev = _cuda(x, gate_w, expert_bias)
+    T, d = x.shape
+    E = gate_w.shape[0]
+    if x.dtype != torch.bfloat16 or gate_w.dtype != torch.bfloat16 or not x.is_contiguous() \
+            or not gate_w.is_contiguous() or gate_w.shape[1] != d:
+        raise ValueError("x [T, d] and gate_w [E, d] must be contiguous bfloat16")
+    if expert_bias.dtype != torch.float32 or expert_bias.numel() != E:
+        raise ValueError("expert_bias must be fp32 [E]")
+    n = T * top_k
+    rows = n + (T if identity_tail else 0)
+    tok = torch.empty(rows, dtype=torch.int32, device=dev)
+    exp = torch.empty(n, dtype=torch.int32, device=dev)
+    w = torch.empty(n, dtype=x.dtype, device=dev)
+    offs = torch.empty(E, dtype=torch.int32, device=dev)
+    inv = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+    xs = torch.empty(rows, d, dtype=x.dtype, device=dev) if gather else None
+    ws = workspace(dev, int(lib.b200_moe_gate_route_workspace_bytes()), "moe_gate_route")
+    check(lib.b200_moe_gate_route(x.data_ptr(), gate_w.data_ptr(), expert_bias.data_ptr(), T, E, top_k, d,
+                                  tok.data_ptr(), exp.data_ptr(), w.data_ptr(), offs.data_ptr(), inv.data_ptr(),
+                                  1 if identity_tail else 0, xs.data_ptr() if xs is not None else None,
+                                  ws.data_ptr(), ws.numel(), _dt(x), _stream()), "moe_gate_route")
+    return tok, exp, w, offs, inv, xs
+
+
 def swiglu(h: torch.Tensor, bias: torch.Tensor | None = None, row_expert: torch.Tensor | None = None):
     """act = silu(h[:, :F] + b1) * (h[:, F:] + b3) for h [rows, 2F]; ``bias`` [experts, 2F] is indexed by
     ``row_expert`` [rows] int32 (row 0 without it); every intermediate is rounded to the dtype."""

@@ -1048,3 +1048,42 @@ def test_lm_head_argmax_equals_argmax_of_the_bf16_logits(rows, vocab, d):
     logits = (h.float() @ w2.float().t()).bfloat16().float()
     tie_rows = logits.argmax(dim=-1) == 3
     assert (got[tie_rows] == 3).all()
+
+
+# ----------------------------------------------------------------------------- gate projection + routing in one launch
+@pytest.mark.parametrize("T,E,K,d,tail,gather", [(1, 16, 2, 1024, True, True), (7, 16, 2, 1024, True, True),
+                                                  (32, 16, 2, 1024, False, True), (200, 16, 2, 1024, True, False),
+                                                  (256, 32, 4, 2048, True, False), (33, 64, 8, 512, False, True),
+                                                  (9, 4, 2, 128, True, True)])
+def test_gate_projection_and_routing_in_one_launch(T, E, K, d, tail, gather):
+    """b200_moe_gate_route against the two-step form (bf16 gate logits computed on the CPU in fp32 and rounded
+    once, then b200_moe_route): the sort invariants always hold; selection and weights agree wherever the two
+    logit computations do not disagree about a near-tie; the gathered rows are x[sorted_token]; two calls in a
+    row share the scratch (its ticket returns to zero)."""
+    ops = _ops()
+    x = _randn((T, d), 81, torch.bfloat16)
+    gw = (_randn((E, d), 82, torch.float32) * d ** -0.5).bfloat16()
+    bias = (0.05 * _randn((E,), 83, torch.float32))
+    logits = (x.float() @ gw.float().t()).bfloat16()
+    for _ in range(2):
+        tok, experts, w, offs, inv, xs = ops.moe_gate_route(x.cuda(), gw.cuda(), bias.cuda(), K, identity_tail=tail,
+                                                            gather=gather)
+    ops.check_status()
+    tok2, experts2, w2, offs2, inv2 = ops.moe_route(logits.cuda(), bias.cuda(), K, identity_tail=tail)
+    n = T * K
+    assert offs[-1].item() == n and torch.equal(offs, experts.bincount(minlength=E).cumsum(0).int())
+    key = experts.long() * T + tok[:n].long()
+    assert (key[1:] > key[:-1]).all()
+    rows = inv.long().reshape(-1)
+    assert torch.equal(tok[rows].view(T, K).long(), torch.arange(T, device="cuda").view(T, 1).expand(T, K))
+    if tail:
+        assert torch.equal(tok[n:], torch.arange(T, device="cuda", dtype=torch.int32))
+    sel, sel2 = experts[rows].view(T, K), experts2[inv2.long().reshape(-1)].view(T, K)
+    same = (sel == sel2).all(dim=1)
+    assert same.float().mean().item() >= 0.97, same.float().mean().item()
+    wa, wb = w[rows].view(T, K).float(), w2[inv2.long().reshape(-1)].view(T, K).float()
+    assert (wa[same] - wb[same]).abs().max().item() <= 8e-3 if same.any() else True
+    if gather:
+        assert xs is not None and torch.equal(xs.cpu(), x[tok.cpu().long()])
+    else:
+        assert xs is None
