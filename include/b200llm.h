@@ -318,7 +318,7 @@ int b200_moe_route(const void* gate_logits, const float* expert_bias, int32_t nu
  * (the index_select that feeds b200_moe_grouped_gemm); one thread block copies the rows, so pass it for small
  * batches only.  workspace: b200_moe_gate_route_workspace_bytes() bytes, 256-byte aligned, zero when first
  * used (its first word is a ticket counter that every call returns to zero).  More than 256 tokens, another
- * dtype or d_model % 8 != 0: B200_ERR_UNSUPPORTED (use a GEMM and b200_moe_route). */
+ * dtype, d_model % 8 != 0 or a gate matrix above 160 KiB: B200_ERR_UNSUPPORTED (use a GEMM and b200_moe_route). */
 size_t b200_moe_gate_route_workspace_bytes(void);
 int b200_moe_gate_route(const void* x, const void* gate_weight, const float* expert_bias, int32_t num_tokens,
                         int32_t num_experts, int32_t top_k, int32_t d_model, int32_t* sorted_token,

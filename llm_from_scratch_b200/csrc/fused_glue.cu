@@ -190,26 +190,42 @@ add_rmsnorm_bf16_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
 
 // Hq*D and Hkv*D multiples of 256, D in {32, 64, 128, 256}: a lane's 8 elements and their RoPE
 // partners (half a head away) sit in the same 256-element chunk, (D/2)/8 lanes apart.
+// NQ / NK = number of 256-element chunks of the q / k row (compile-time, so that the whole row sits in
+// registers and every global load of the token is in flight before the first one is waited for).
+template <int NQ, int NK>
 __global__ void __launch_bounds__(kWarpRows * 32)
 qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
   using T = __nv_bfloat16;
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarpRows + (threadIdx.x >> 5);
   if (t >= num_tokens) return;
-  const int Wq = a.Hq * a.D, Wk = a.Hkv * a.D, half = a.D / 2, partner = half / 8;
+  constexpr int Wq = NQ * 256, Wk = NK * 256;
+  const int half = a.D / 2, partner = half / 8;
   const T* qr = static_cast<const T*>(a.qkv) + t * a.qkv_stride;
   const T* kr = qr + Wq;
   const T* vr = kr + Wk;
-  // position, slot and the rotation coefficients first: they do not depend on the row's norm, so their two
-  // dependent round trips run under the loads and reductions below instead of after them.  A lane's eight
-  // elements sit at the same offset of their head in every 256-element chunk (256 is a multiple of D), so one
-  // set of eight cosines and sines serves all chunks of q and k.
+  // position and slot first, then the row: the rotation coefficients (a second round trip behind the
+  // position) are fetched while the row's loads are still in flight
   int64_t pos = a.positions[t];
   int64_t slot = a.k_cache ? a.slots[t] : -1;
+  Bf16x8 qv[NQ], kv[NK];
+  uint4 vv[NK];
+#pragma unroll
+  for (int j = 0; j < NQ; ++j) qv[j].u = *reinterpret_cast<const uint4*>(qr + j * 256 + lane * 8);
+#pragma unroll
+  for (int j = 0; j < NK; ++j) kv[j].u = *reinterpret_cast<const uint4*>(kr + j * 256 + lane * 8);
+  const bool store = slot >= 0 && slot < a.num_slots;
+  if (a.k_cache && slot >= a.num_slots && lane == 0) report(a.status, B200_ERR_BOUNDS);
+  if (store) {
+#pragma unroll
+    for (int j = 0; j < NK; ++j) vv[j] = *reinterpret_cast<const uint4*>(vr + j * 256 + lane * 8);
+  }
   if (pos < 0 || pos >= a.max_pos) {
     if (lane == 0) report(a.status, B200_ERR_BOUNDS);
     pos = pos < 0 ? 0 : a.max_pos - 1;
   }
+  // a lane's eight elements sit at the same offset of their head in every chunk (256 is a multiple of D): one
+  // set of eight cosines and sines serves all chunks of q and k
   const float* cs = a.rope + pos * a.D;
   const int j0 = (lane * 8) % a.D;
   const bool first = j0 < half;
@@ -220,34 +236,27 @@ qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
   const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
   const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
   float sq = 0.f, sk = 0.f;
-  for (int c = lane * 8; c < Wq; c += 256) {
-    Bf16x8 u;
-    u.u = *reinterpret_cast<const uint4*>(qr + c);
+#pragma unroll
+  for (int j = 0; j < NQ; ++j) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float f = __bfloat162float(u.b[i]);
+      const float f = __bfloat162float(qv[j].b[i]);
       sq += f * f;
     }
   }
-  for (int c = lane * 8; c < Wk; c += 256) {
-    Bf16x8 u;
-    u.u = *reinterpret_cast<const uint4*>(kr + c);
+#pragma unroll
+  for (int j = 0; j < NK; ++j) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float f = __bfloat162float(u.b[i]);
+      const float f = __bfloat162float(kv[j].b[i]);
       sk += f * f;
     }
   }
   const float iq = rsqrtf(warp_sum(sq) / static_cast<float>(Wq) + a.eps);
   const float ik = rsqrtf(warp_sum(sk) / static_cast<float>(Wk) + a.eps);
-  if (slot >= a.num_slots) {
-    if (lane == 0) report(a.status, B200_ERR_BOUNDS);
-    slot = -1;
-  }
   // one 256-element chunk of q or k: normalise, round, rotate, round
-  auto rotate = [&](const T* src, const float* nw, float inv, int c) -> uint4 {
-    Bf16x8 u, o;
-    u.u = *reinterpret_cast<const uint4*>(src + c);
+  auto rotate = [&](const Bf16x8& u, const float* nw, float inv, int c) -> uint4 {
+    Bf16x8 o;
     const float4 w0 = *reinterpret_cast<const float4*>(nw + c), w1 = *reinterpret_cast<const float4*>(nw + c + 4);
     const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
@@ -259,16 +268,20 @@ qk_norm_rope_store_bf16_warp_kernel(const QkArgs a, int64_t num_tokens) {
     return o.u;
   };
   T* qo = static_cast<T*>(a.q_out) + t * Wq;
-  for (int c = lane * 8; c < Wq; c += 256) *reinterpret_cast<uint4*>(qo + c) = rotate(qr, a.q_norm_w, iq, c);
+#pragma unroll
+  for (int j = 0; j < NQ; ++j)
+    *reinterpret_cast<uint4*>(qo + j * 256 + lane * 8) = rotate(qv[j], a.q_norm_w, iq, j * 256 + lane * 8);
   T* ko = static_cast<T*>(a.k_out) + t * Wk;
-  T* kc = slot >= 0 ? static_cast<T*>(a.k_cache) + slot * Wk : nullptr;
-  T* vc = slot >= 0 ? static_cast<T*>(a.v_cache) + slot * Wk : nullptr;
-  for (int c = lane * 8; c < Wk; c += 256) {
-    const uint4 o = rotate(kr, a.k_norm_w, ik, c);
+  T* kc = store ? static_cast<T*>(a.k_cache) + slot * Wk : nullptr;
+  T* vc = store ? static_cast<T*>(a.v_cache) + slot * Wk : nullptr;
+#pragma unroll
+  for (int j = 0; j < NK; ++j) {
+    const int c = j * 256 + lane * 8;
+    const uint4 o = rotate(kv[j], a.k_norm_w, ik, c);
     *reinterpret_cast<uint4*>(ko + c) = o;
-    if (kc) {
+    if (store) {
       *reinterpret_cast<uint4*>(kc + c) = o;
-      *reinterpret_cast<uint4*>(vc + c) = *reinterpret_cast<const uint4*>(vr + c);
+      *reinterpret_cast<uint4*>(vc + c) = vv[j];
     }
   }
 }
@@ -368,8 +381,16 @@ extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_token_stride
       aligned16(qkv) && aligned16(q_norm_weight) && aligned16(k_norm_weight) && aligned16(rope_table) &&
       aligned16(q_out) && aligned16(k_out) && (!k_cache || (aligned16(k_cache) && aligned16(v_cache)))) {
     const int wgrid = static_cast<int>((num_tokens + kWarpRows - 1) / kWarpRows);
-    qk_norm_rope_store_bf16_warp_kernel<<<wgrid, kWarpRows * 32, 0, s>>>(a, num_tokens);
-    return launch_result();
+    const int nq = Wq / 256, nk = Wk / 256;
+#define QK_LAUNCH(NQ, NK)                                                                       \
+  if (nq == NQ && nk == NK) {                                                                   \
+    qk_norm_rope_store_bf16_warp_kernel<NQ, NK><<<wgrid, kWarpRows * 32, 0, s>>>(a, num_tokens); \
+    return launch_result();                                                                     \
+  }
+    // (q chunks, k chunks) of the row widths in use: 16/4 heads x 64, 32/8 x 128, 8/2 x 128, 16/16 x 64, 4/2 x 64 ...
+    QK_LAUNCH(4, 1) QK_LAUNCH(16, 4) QK_LAUNCH(4, 4) QK_LAUNCH(8, 2) QK_LAUNCH(8, 8) QK_LAUNCH(2, 1) QK_LAUNCH(1, 1)
+    QK_LAUNCH(2, 2) QK_LAUNCH(8, 1) QK_LAUNCH(8, 4) QK_LAUNCH(16, 2) QK_LAUNCH(16, 8)
+#undef QK_LAUNCH
   }
   if (dtype == B200_DTYPE_F32)
     qk_norm_rope_store_kernel<float><<<grid, kThreads, 0, s>>>(a);

@@ -262,6 +262,7 @@ struct GateRouteArgs {
 };
 
 constexpr int kGateWarps = 8;       // tokens per CTA in phase 1
+constexpr size_t kGateSmemMax = 160 * 1024;   // largest gate matrix staged in shared memory
 
 template <int EMAX>
 __global__ void __launch_bounds__(kTok) moe_gate_route_kernel(const GateRouteArgs g) {
@@ -272,26 +273,58 @@ __global__ void __launch_bounds__(kTok) moe_gate_route_kernel(const GateRouteArg
   const RouteArgs& a = g.r;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int E = a.E, d = g.d;
+  extern __shared__ uint4 s_gate[];            // the gate matrix [E, d] bf16: every warp of the CTA reads all of it
   {
+    // this warp's token row first (up to 8 pieces per lane in flight), then the gate matrix, eight independent
+    // loads per thread per trip: everything the phase reads from global memory is requested before anything
+    // waits for it
+    constexpr int kXPieces = 8;                  // d <= 2048 keeps the row in registers
     const int t = blockIdx.x * kGateWarps + warp;
-    if (t < a.T) {
+    const bool live = t < a.T;
+    uint4 xrow[kXPieces];
+    const uint4* xr = reinterpret_cast<const uint4*>(g.x + static_cast<int64_t>(live ? t : 0) * d);
+#pragma unroll
+    for (int j = 0; j < kXPieces; ++j) {
+      const int c = lane + 32 * j;               // 16-byte piece index within the row
+      xrow[j] = (live && c * 8 < d) ? xr[c] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(g.gate_w);
+    const int pieces = E * d / 8;
+    for (int base = 0; base < pieces; base += kTok * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * kTok + tid;
+        v[u] = i < pieces ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * kTok + tid;
+        if (i < pieces) s_gate[i] = v[u];
+      }
+    }
+    __syncthreads();
+    if (live) {
       float acc[EMAX];
 #pragma unroll
       for (int e = 0; e < EMAX; ++e) acc[e] = 0.f;
-      const T* xr = g.x + static_cast<int64_t>(t) * d;
-      for (int c = lane * 8; c < d; c += 256) {
-        union { uint4 u; T b[8]; } xv;
-        xv.u = *reinterpret_cast<const uint4*>(xr + c);
-        float xf[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) xf[i] = __bfloat162float(xv.b[i]);
+      for (int j = 0; j < kXPieces; ++j) {
+        const int c = (lane + 32 * j) * 8;
+        if (c < d) {
+          union { uint4 u; T b[8]; } xv;
+          xv.u = xrow[j];
+          float xf[8];
 #pragma unroll
-        for (int e = 0; e < EMAX; ++e) {
-          if (e < E) {
-            union { uint4 u; T b[8]; } wv;
-            wv.u = __ldg(reinterpret_cast<const uint4*>(g.gate_w + static_cast<int64_t>(e) * d + c));
+          for (int i = 0; i < 8; ++i) xf[i] = __bfloat162float(xv.b[i]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[e] = fmaf(xf[i], __bfloat162float(wv.b[i]), acc[e]);
+          for (int e = 0; e < EMAX; ++e) {
+            if (e < E) {
+              union { uint4 u; T b[8]; } wv;
+              wv.u = s_gate[(e * d + c) / 8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[e] = fmaf(xf[i], __bfloat162float(wv.b[i]), acc[e]);
+            }
           }
         }
       }
@@ -315,13 +348,17 @@ __global__ void __launch_bounds__(kTok) moe_gate_route_kernel(const GateRouteArg
       }
     }
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) s_last = atomicAdd(g.ticket, 1) == static_cast<int>(gridDim.x) - 1;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  if (tid == 0) *g.ticket = 0;     // ready for the next launch
+  if (gridDim.x > 1) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(g.ticket, 1) == static_cast<int>(gridDim.x) - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *g.ticket = 0;     // ready for the next launch
+  } else {
+    __syncthreads();                 // a single CTA: its own writes are visible to it after the barrier
+  }
   const int t = tid;
   M taken = 0;
   int sel[kMaxK];
@@ -539,7 +576,8 @@ extern "C" int b200_moe_gate_route(const void* x, const void* gate_weight, const
                                    void* stream) {
   using namespace b200;
   if (num_tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts || d_model <= 0) return B200_ERR_ARG;
-  if (dtype != B200_DTYPE_BF16 || num_experts > kMaxE || top_k > kMaxK || num_tokens > kTok || d_model % 8 != 0)
+  if (dtype != B200_DTYPE_BF16 || num_experts > kMaxE || top_k > kMaxK || num_tokens > kTok || d_model % 8 != 0 ||
+      d_model > 2048)
     return B200_ERR_UNSUPPORTED;
   if (num_tokens == 0) return B200_ERR_UNSUPPORTED;   // the plain routing entry point writes the empty offsets
   if (!x || !gate_weight || !expert_bias || !sorted_token || !sorted_expert || !sorted_weight || !expert_offsets ||
@@ -569,9 +607,26 @@ extern "C" int b200_moe_gate_route(const void* x, const void* gate_weight, const
   g.gathered = static_cast<__nv_bfloat16*>(gathered);
   const int grid = (num_tokens + kGateWarps - 1) / kGateWarps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (num_experts <= 16) moe_gate_route_kernel<16><<<grid, kTok, 0, s>>>(g);
-  else if (num_experts <= 32) moe_gate_route_kernel<32><<<grid, kTok, 0, s>>>(g);
-  else moe_gate_route_kernel<64><<<grid, kTok, 0, s>>>(g);
+  const size_t smem = static_cast<size_t>(num_experts) * d_model * sizeof(__nv_bfloat16);   // the gate matrix
+  if (smem > kGateSmemMax) return B200_ERR_UNSUPPORTED;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return B200_ERR_UNSUPPORTED;
+#define GATE_LAUNCH(EMAX)                                                                                          \
+  do {                                                                                                             \
+    static bool configured[64] = {};   /* per-device flag, idempotent (see the note on statics in the header) */   \
+    if (!configured[dev]) {                                                                                        \
+      if (cudaFuncSetAttribute(moe_gate_route_kernel<EMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                               static_cast<int>(kGateSmemMax)) != cudaSuccess)                                     \
+        return B200_ERR_LAUNCH;                                                                                    \
+      configured[dev] = true;                                                                                      \
+    }                                                                                                              \
+    moe_gate_route_kernel<EMAX><<<grid, kTok, smem, s>>>(g);                                                       \
+  } while (0)
+  if (num_experts <= 16) GATE_LAUNCH(16);
+  else if (num_experts <= 32) GATE_LAUNCH(32);
+  else GATE_LAUNCH(64);
+#undef GATE_LAUNCH
   return launch_result();
 }
 

@@ -118,6 +118,11 @@ class MoE(nn.Module):
     dense_max_tokens = 512
     use_grouped = True     # bf16: grouped GEMMs over tokens sorted by expert (no host sync)
     own_gemm_max_rows_per_expert = 64   # average rows per expert up to which the weight-streaming kernel is used
+    # Gate projection + routing (+ gather) as one launch (ops.moe_gate_route).  Off: measured on B200 inside a
+    # CUDA graph the one launch takes 10.0 / 11.7 / 12.1 us at 1 / 64 / 256 tokens against 9.6 / 8.9 / 10.3 us for
+    # the library GEMM + routing kernel + gather it replaces — each of those is a single memory round trip behind
+    # a ~2.3 us launch, while the fused kernel chains four (rows and gate matrix, bias, ticket, masks).
+    fused_gate_route = False
 
     def __init__(self, p: _Params, prefix: str, cfg: ModelConfig):
         super().__init__()
@@ -195,7 +200,9 @@ class MoE(nn.Module):
         T = x.shape[0]
         small = (T * self.K <= self.own_gemm_max_rows_per_expert * self.E and x.shape[1] % 8 == 0
                  and self.d_ff % 8 == 0)
-        fused_gate = T <= ops.MOE_GATE_ROUTE_MAX_TOKENS and x.is_contiguous()
+        fused_gate = (self.fused_gate_route and T <= ops.MOE_GATE_ROUTE_MAX_TOKENS and x.is_contiguous()
+                      and x.shape[1] <= 2048
+                      and self.gate_w.numel() * 2 <= ops.MOE_GATE_ROUTE_MAX_GATE_BYTES)
         in_kernel_gather = fused_gate and T <= ops.MOE_GATE_ROUTE_GATHER_MAX_TOKENS
 
         def route(identity_tail):

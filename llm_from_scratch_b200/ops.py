@@ -506,6 +506,7 @@ def moe_route(gate_logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int, 
 
 
 MOE_GATE_ROUTE_MAX_TOKENS = 256
+MOE_GATE_ROUTE_MAX_GATE_BYTES = 160 * 1024
 MOE_GATE_ROUTE_GATHER_MAX_TOKENS = 32   # up to here the routing launch also copies the routed rows
 
 
