@@ -210,7 +210,8 @@ int b200_prefill_varlen_shared_tail(const void* q, const void* k_head, const voi
 /* Tile list for b200_prefill_varlen, computed on the device from cu_seqlens_q (one small launch per
  * step; all layers of the step reuse it).
  *   b200_prefill_tile_rows: query rows per tile of the kernel that serves this shape with packed keys
- *     (128 or 256 tcgen05, 64 mma.sync), or 0 when only the general kernel applies (no plan then).
+ *     (256 or 128 tcgen05: head dims 128 / 192+128, and head_dim 64 with query heads in groups of four;
+ *     64 mma.sync), or 0 when only the general kernel applies (no plan then).
  *   b200_prefill_plan_bytes: size of `plan` for up to total_q_tokens rows in up to num_seqs sequences;
  *     its capacity in tiles is bytes / 4 - 4.
  *   b200_prefill_plan: max_seqlen_q is a host-side upper bound of the longest sequence

@@ -114,6 +114,12 @@ int prefill_mma_launch(const void* q, const void* k, const void* v, void* out, i
 
 // tcgen05 path for packed keys/values (prefill_umma2.cu): head dims 128/128 and 192/128, 256 query rows of one head per CTA
 int prefill_umma2_tile_rows(int Hq, int Hkv, int Dqk, int Dv);
+int prefill_umma4_tile_rows(int Hq, int Hkv, int Dqk, int Dv);
+int prefill_umma4_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride, int64_t k_stride,
+                         int64_t v_stride, int64_t total_q, int64_t total_k, const int32_t* cu_q,
+                         const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv,
+                         float scale, const int32_t* plan, int plan_tile_rows, int plan_capacity, int32_t* status,
+                         cudaStream_t s);
 int prefill_umma2_launch(const void* q, const void* k, const void* v, void* out, int64_t q_stride, int64_t k_stride,
                          int64_t v_stride, int64_t total_q, int64_t total_k, const int32_t* cu_q,
                          const int32_t* cu_k, int num_seqs, int max_seqlen_q, int Hq, int Hkv, int Dqk, int Dv,
@@ -228,6 +234,8 @@ extern "C" int32_t b200_prefill_tile_rows(int32_t num_q_heads, int32_t num_kv_he
   // packed keys: the row-pair tcgen05 kernel serves 128/128 and 192/128 (the two-head kernel, 128 rows per
   // tile, only takes over for a paged prefix and then ignores a 256-row tile list)
   if (const int r = b200::prefill_umma2_tile_rows(num_q_heads, num_kv_heads, head_dim_qk, head_dim_v)) return r;
+  // head_dim 64 with query heads in groups of four per KV head: the four-heads-per-CTA tcgen05 kernel, 128 rows
+  if (const int r = b200::prefill_umma4_tile_rows(num_q_heads, num_kv_heads, head_dim_qk, head_dim_v)) return r;
   const bool mma = (head_dim_qk == head_dim_v && (head_dim_qk == 32 || head_dim_qk == 64 || head_dim_qk == 128)) ||
                    (head_dim_qk == 192 && head_dim_v == 128);
   return mma ? 64 : 0;
@@ -305,6 +313,12 @@ extern "C" int b200_prefill_varlen(const void* q, const void* k, const void* v, 
                                            max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk, head_dim_v, scale,
                                            plan, plan_tile_rows, plan_capacity, status, s, nullptr, 0, 0);
       if (rc2 != B200_ERR_UNSUPPORTED) return rc2;
+      // head_dim 64, four query heads of a KV head per CTA
+      const int rc4 = prefill_umma4_launch(q, k, v, out, q_token_stride, k_token_stride, v_token_stride,
+                                           total_q_tokens, total_k_tokens, cu_seqlens_q, cu_seqlens_k, num_seqs,
+                                           max_seqlen_q, num_q_heads, num_kv_heads, head_dim_qk, head_dim_v, scale,
+                                           plan, plan_tile_rows, plan_capacity, status, s);
+      if (rc4 != B200_ERR_UNSUPPORTED) return rc4;
     }
     const int rcu = prefill_umma_launch(q, k, v, out, q_token_stride, k_token_stride, v_token_stride,
                                         total_q_tokens, total_k_tokens, cu_seqlens_q, cu_seqlens_k, num_seqs, max_seqlen_q, num_q_heads,

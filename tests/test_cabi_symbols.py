@@ -44,7 +44,8 @@ def test_argument_errors_are_reported_without_a_gpu():
                                    1.0, None, None, None, 0, 0, 0, None, None, 0, 0, 5, None, None) == -3  # bad dtype
     assert lib.b200_prefill_tile_rows(32, 8, 128, 128, 1) == 256      # tcgen05 kernel, two row tiles per CTA
     assert lib.b200_prefill_tile_rows(16, 16, 192, 128, 1) == 256     # tcgen05 kernel, two row tiles per CTA
-    assert lib.b200_prefill_tile_rows(16, 4, 64, 64, 1) == 64         # mma.sync kernel
+    assert lib.b200_prefill_tile_rows(16, 4, 64, 64, 1) == 128        # tcgen05 kernel, four heads of a KV head per CTA
+    assert lib.b200_prefill_tile_rows(4, 2, 64, 64, 1) == 64          # group of two: mma.sync kernel
     assert lib.b200_prefill_tile_rows(16, 4, 64, 64, 0) == 0          # fp32: general kernel only
     assert lib.b200_prefill_plan_bytes(1000, 7, 64) == (4 + 16 + 7) * 4
     assert lib.b200_prefill_plan(None, 1, 10, 64, None, 0, None, None) == -1

@@ -1087,3 +1087,39 @@ def test_gate_projection_and_routing_in_one_launch(T, E, K, d, tail, gather):
         assert xs is not None and torch.equal(xs.cpu(), x[tok.cpu().long()])
     else:
         assert xs is None
+
+
+# ----------------------------------------------------------------------------- head_dim 64 prefill, four heads per CTA
+@pytest.mark.parametrize("Hq,Hkv", [(16, 4), (4, 1), (8, 1), (32, 8)])
+def test_prefill_head_dim_64_four_heads_per_cta_matches_oracle(Hq, Hkv):
+    """The tcgen05 kernel for head_dim 64 (four query heads of a KV head per CTA, 128-row tiles): ragged lengths
+    around the tile and key-tile boundaries, with the plain grid and with the device-built tile list (bit-equal),
+    against the CPU oracle."""
+    ops, orc = _ops(), _oracle()
+    D = 64
+    assert ops.prefill_tile_rows(Hq, Hkv, D, D, torch.bfloat16) == 128
+    lens = [540, 1, 127, 128, 129, 64, 65, 1000, 300, 63]
+    T = sum(lens)
+    q = _randn((T, Hq, D), 91, torch.bfloat16)
+    k = _randn((T, Hkv, D), 92, torch.bfloat16)
+    v = _randn((T, Hkv, D), 93, torch.bfloat16)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    got = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), D ** -0.5)
+    ops.check_status()
+    want = orc.prefill_varlen(q, k, v, cu, cu, D ** -0.5)
+    err = (got.float().cpu() - want).abs()
+    assert err.max().item() <= 2e-2, err.max().item()
+    assert (err.mean() / want.abs().mean()).item() <= 1e-2
+    plan = ops.prefill_plan(cu.cuda(), T, max(lens), 128)
+    again = ops.prefill_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), D ** -0.5,
+                               plan=plan)
+    ops.check_status()
+    assert torch.equal(again, got)
+    # strided q / k / v (column slices of a fused projection), as the model passes them
+    qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1).cuda()
+    qs = qkv[:, :Hq * D].view(T, Hq, D)
+    ks = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    vs = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    strided = ops.prefill_varlen(qs, ks, vs, cu.cuda(), cu.cuda(), max(lens), max(lens), D ** -0.5)
+    ops.check_status()
+    assert torch.equal(strided, got)
