@@ -263,7 +263,8 @@ def test_prefill_plan_lists_every_tile_once_and_gives_identical_output(Hq, Hkv, 
     q, k, v, cu = q.cuda(), k.cuda(), v.cuda(), cu.cuda()
     scale = D ** -0.5
     rows = ops.prefill_tile_rows(Hq, Hkv, D, D, torch.bfloat16)
-    assert rows == (256 if D == 128 else 64)      # tcgen05 row-pair kernel / mma.sync kernel
+    # tcgen05 row-pair kernel / tcgen05 four-heads-per-CTA kernel (head_dim 64, groups of four) / mma.sync kernel
+    assert rows == {128: 256, 64: 128, 32: 64}[D]
     plan = ops.prefill_plan(cu, sum(lens), max(lens), rows)
     ops.check_status()
     buf = plan.buffer.cpu().numpy()
