@@ -78,6 +78,56 @@ int64_t b200_block_hash_chain(const int32_t* token_ids_host, int64_t num_tokens,
                               uint64_t* out_hashes);
 
 /* ---------------------------------------------------------------------------------------------
+ * The KV-block pool on the host, natively: BlockManager (engine/block_manager.py:8-157) as a handle.  Blocks are
+ * handed out oldest-free-first (the reference's FIFO deque, :60-78); full blocks are sealed with the chained
+ * hash above and found again by later prompts (:85-114) after a token-by-token comparison; reference counts
+ * start at 1 (the reference starts at 0 and so leaks unshared blocks, :23-26; this is the engine's corrected
+ * default mode), a released block keeps its contents and can be revived, and a hit never covers a whole
+ * prompt.  Host-only, no GPU work; a handle is not thread-safe.
+ *   b200_pool_allocate    blocks for a new sequence (allocate, :85-114): writes ceil(num_tokens/block_size) block
+ *                         ids, *num_cached_out = tokens covered by reused blocks; returns the number of
+ *                         blocks, or B200_ERR_TOO_LARGE when the pool runs dry (state partly applied, as
+ *                         the reference's IndexError would leave it)
+ *   b200_pool_deallocate  releases a table, last block first (deallocate, :116-127)
+ *   b200_pool_append      decode-time growth (append, :136-157): see the definition's comment
+ *   b200_pool_open_block / b200_pool_seal_block  the two halves of append for several decode steps per
+ *                         scheduling decision: open ahead, seal once the tokens are known
+ *   b200_pool_lookup      the block a chained hash currently resolves to, or -1
+ *   b200_pool_snapshot    free ids oldest first (returns their number), reference counts, sealed flags, hashes
+ * ------------------------------------------------------------------------------------------- */
+void* b200_pool_create(int64_t num_blocks, int32_t block_size);
+void b200_pool_destroy(void* pool);
+int64_t b200_pool_num_free(const void* pool);
+int64_t b200_pool_allocate(void* pool, const int32_t* token_ids_host, int64_t num_tokens, int32_t* table_out_host,
+                           int64_t* num_cached_out_host);
+int b200_pool_deallocate(void* pool, const int32_t* table_host, int64_t num_blocks);
+int64_t b200_pool_append(void* pool, int32_t last_block, int32_t prev_block, int64_t num_tokens,
+                         const int32_t* last_block_tokens_host);
+int64_t b200_pool_open_block(void* pool);
+int b200_pool_seal_block(void* pool, int32_t block, int32_t prev_block, const int32_t* block_tokens_host);
+int64_t b200_pool_lookup(const void* pool, uint64_t hash);
+int64_t b200_pool_snapshot(const void* pool, int32_t* free_order_host, int32_t* ref_counts_host,
+                           uint8_t* sealed_host, uint64_t* hashes_host);
+
+/* ---------------------------------------------------------------------------------------------
+ * Step metadata on the host, natively (ModelRunner.prepare_prefill / prepare_decode, engine/model_runner.py:
+ * 202-278), written straight into caller-owned (pinned) arrays.  Block tables arrive as one flat int32 array
+ * with offsets: sequence i owns tables[table_offsets[i] : table_offsets[i + 1]].
+ *   b200_prepare_prefill  the non-cached suffix of every sequence: cu_seqlens_q / cu_seqlens_k int32 [n + 1],
+ *                         positions int64 [T] (num_cached + j for packed token j), slot_mapping int64 [T],
+ *                         max_seqlens[0..1] = longest q / k; returns T (<= capacity) or a negative code
+ *   b200_prepare_decode   one token per sequence: context_lens, slot_mapping int64 [n], block_tables int32
+ *                         [n, width] padded with -1
+ * ------------------------------------------------------------------------------------------- */
+int64_t b200_prepare_prefill(int32_t num_seqs, const int64_t* num_tokens_host, const int64_t* num_cached_host,
+                             const int64_t* table_offsets_host, const int32_t* tables_host, int32_t block_size,
+                             int32_t* cu_seqlens_q_host, int32_t* cu_seqlens_k_host, int64_t* positions_host,
+                             int64_t* slot_mapping_host, int64_t capacity, int32_t* max_seqlens_host);
+int b200_prepare_decode(int32_t num_seqs, const int64_t* num_tokens_host, const int64_t* table_offsets_host,
+                        const int32_t* tables_host, int32_t block_size, int64_t* context_lens_host,
+                        int64_t* slot_mapping_host, int32_t* block_tables_host, int64_t width);
+
+/* ---------------------------------------------------------------------------------------------
  * store_kvcache: k_cache[slot_mapping[t], :, :] = k[t, :, :] (same for v); slot < 0 is skipped.
  * Contract: engine/model_runner.py:184-190 (pool [num_blocks, block_size, Hkv, D] per layer, so a
  * slot is one row of [num_slots, Hkv*D]), :226-230 (prefill slots), :261 (decode slot) and

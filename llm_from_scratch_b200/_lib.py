@@ -25,6 +25,18 @@ SIGNATURES = {
     "b200_xxh64": (_u64, [_vp, _sz, _u64]),
     "b200_block_hash": (_u64, [_vp, _i32, _u64, _i32]),
     "b200_block_hash_chain": (_i64, [_vp, _i64, _i32, _vp]),
+    "b200_pool_create": (_vp, [_i64, _i32]),
+    "b200_pool_destroy": (None, [_vp]),
+    "b200_pool_num_free": (_i64, [_vp]),
+    "b200_pool_allocate": (_i64, [_vp, _vp, _i64, _vp, _vp]),
+    "b200_pool_deallocate": (_i32, [_vp, _vp, _i64]),
+    "b200_pool_append": (_i64, [_vp, _i32, _i32, _i64, _vp]),
+    "b200_pool_open_block": (_i64, [_vp]),
+    "b200_pool_seal_block": (_i32, [_vp, _i32, _i32, _vp]),
+    "b200_pool_lookup": (_i64, [_vp, _u64]),
+    "b200_pool_snapshot": (_i64, [_vp, _vp, _vp, _vp, _vp]),
+    "b200_prepare_prefill": (_i64, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "b200_prepare_decode": (_i32, [_i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64]),
     "b200_store_kvcache": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i64,
                                   _i32, _vp, _vp]),
     "b200_paged_decode_gqa_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),

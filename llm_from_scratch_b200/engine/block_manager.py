@@ -235,3 +235,133 @@ class BlockManager:
         block.update(h, token_ids)
         self.hash_to_block_id[h] = block.block_id
 
+
+
+class _BlockView:
+    """Read-only snapshot of one block of a ``NativeBlockManager`` (inspection and tests)."""
+    __slots__ = ("block_id", "hash", "ref_count")
+
+    def __init__(self, block_id: int, h: int, ref_count: int):
+        self.block_id, self.hash, self.ref_count = block_id, h, ref_count
+
+
+class NativeBlockManager:
+    """The default-mode pool with its inner loops in C++ (``b200_pool_*`` of the library): the hash chain, the
+    lookup with token comparison, the O(1) free list and the reference counts live behind a handle, and a call
+    per ``allocate`` / ``append`` / ``deallocate`` replaces a Python loop per block.  Same methods and the same
+    results as ``BlockManager(reference_exact=False)`` — allocation order, prefix hits, what a released block
+    keeps — which ``tests/test_native_host_path.py`` checks on random request traces.  The reference-exact mode
+    (the reference's ref-count arithmetic, reproduced for the parity recordings) stays in Python."""
+
+    reference_exact = False
+
+    def __init__(self, num_blocks: int, block_size: int):
+        import ctypes
+        import numpy as np
+        from .._lib import lib
+        self._np, self._ct, self._lib = np, ctypes, lib
+        self.block_size = block_size
+        self.num_blocks = num_blocks
+        self._h = lib.b200_pool_create(num_blocks, block_size)
+        if not self._h:
+            raise MemoryError("could not create the native block pool")
+        self._cached = ctypes.c_int64(0)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.b200_pool_destroy(h)
+
+    # ------------------------------------------------------------------ views (inspection; not on the hot path)
+    def _snapshot(self):
+        np = self._np
+        order = np.empty(self.num_blocks, dtype=np.int32)
+        refs = np.empty(self.num_blocks, dtype=np.int32)
+        sealed = np.empty(self.num_blocks, dtype=np.uint8)
+        hashes = np.empty(self.num_blocks, dtype=np.uint64)
+        n = self._lib.b200_pool_snapshot(self._h, order.ctypes.data, refs.ctypes.data, sealed.ctypes.data,
+                                         hashes.ctypes.data)
+        return order[:n], refs, sealed, hashes
+
+    @property
+    def free_block_ids(self):
+        return self._snapshot()[0].tolist()
+
+    @property
+    def num_free_blocks(self) -> int:
+        return self._lib.b200_pool_num_free(self._h)
+
+    @property
+    def used_block_ids(self) -> set:
+        return set(self._np.nonzero(self._snapshot()[1] > 0)[0].tolist())
+
+    @property
+    def blocks(self):
+        _, refs, sealed, hashes = self._snapshot()
+        return [_BlockView(i, int(hashes[i]) if sealed[i] else -1, int(refs[i])) for i in range(self.num_blocks)]
+
+    @property
+    def hash_to_block_id(self) -> dict:
+        _, _refs, sealed, hashes = self._snapshot()
+        out = {}
+        for h in set(hashes[sealed > 0].tolist()):
+            b = self._lib.b200_pool_lookup(self._h, h)
+            if b >= 0:
+                out[h] = b
+        return out
+
+    compute_hash = staticmethod(BlockManager.compute_hash)
+
+    # ------------------------------------------------------------------ prefill-time allocation
+    def can_allocate(self, seq: Sequence) -> bool:
+        return self.num_free_blocks >= seq.num_blocks
+
+    def allocate(self, seq: Sequence) -> None:
+        np = self._np
+        ids = np.asarray(seq.token_ids, dtype=np.int32)
+        table = np.empty(seq.num_blocks, dtype=np.int32)
+        n = self._lib.b200_pool_allocate(self._h, ids.ctypes.data, ids.size, table.ctypes.data,
+                                         self._ct.addressof(self._cached))
+        if n < 0:
+            raise IndexError("KV block pool exhausted")
+        seq.block_table.extend(table.tolist())
+        seq.num_cached_tokens += self._cached.value
+
+    def deallocate(self, seq: Sequence) -> None:
+        table = self._np.asarray(seq.block_table, dtype=self._np.int32)
+        if self._lib.b200_pool_deallocate(self._h, table.ctypes.data, table.size) != 0:
+            raise RuntimeError("deallocate: a block of the table is not in use")
+        seq.block_table = []
+        seq.num_cached_tokens = 0
+
+    # ------------------------------------------------------------------ decode-time growth
+    def can_append(self, seq: Sequence) -> bool:
+        return self.num_free_blocks > 0 if len(seq) % self.block_size == 1 else True
+
+    def _tokens(self, token_ids):
+        return (self._ct.c_int32 * self.block_size)(*token_ids)
+
+    def append(self, seq: Sequence) -> None:
+        n = len(seq)
+        rem = n % self.block_size
+        if rem > 1:
+            return
+        table = seq.block_table
+        toks = self._tokens(seq.token_ids[-self.block_size:]) if rem == 0 else None
+        b = self._lib.b200_pool_append(self._h, table[-1], table[-2] if len(table) > 1 else -1, n, toks)
+        if b >= 0:
+            table.append(b)
+        elif b < -1:
+            raise IndexError("KV block pool exhausted")
+
+    def open_block(self, seq: Sequence) -> None:
+        b = self._lib.b200_pool_open_block(self._h)
+        if b < 0:
+            raise IndexError("KV block pool exhausted")
+        seq.block_table.append(b)
+
+    def seal_block(self, seq: Sequence, index: int) -> None:
+        table, bs = seq.block_table, self.block_size
+        toks = self._tokens(seq.token_ids[index * bs:(index + 1) * bs])
+        if self._lib.b200_pool_seal_block(self._h, table[index], table[index - 1] if index > 0 else -1, toks) != 0:
+            raise RuntimeError("seal_block: bad block")

@@ -61,7 +61,45 @@ def pad_block_tables(seqs: list[Sequence], out: np.ndarray | None = None) -> np.
     return out
 
 
+def _flat_tables(seqs: list[Sequence]):
+    """(offsets int64 [n + 1], flat int32 block ids) of the sequences' block tables."""
+    arrays = [block_table_array(s) for s in seqs]
+    offsets = np.zeros(len(seqs) + 1, dtype=np.int64)
+    np.cumsum([a.size for a in arrays], out=offsets[1:])
+    flat = np.concatenate(arrays) if arrays else np.zeros(0, dtype=np.int32)
+    return offsets, np.ascontiguousarray(flat, dtype=np.int32)
+
+
 def prepare_prefill(seqs: list[Sequence], block_size: int) -> StepMetadata:
+    """Packs the non-cached suffix of every sequence (model_runner.py:202-249): cu_seqlens, positions and the slot
+    mapping come from the library's native builder (``b200_prepare_prefill``); ``prepare_prefill_py`` is the
+    same thing in numpy, kept as the definition and for the reference-exact mode."""
+    if Sequence.reference_exact or any(not s.block_table for s in seqs):
+        return prepare_prefill_py(seqs, block_size)
+    from .._lib import lib
+    n = len(seqs)
+    num_tokens = np.fromiter((s.num_tokens for s in seqs), dtype=np.int64, count=n)
+    cached = np.fromiter((s.num_cached_tokens for s in seqs), dtype=np.int64, count=n)
+    offsets, flat = _flat_tables(seqs)
+    total = int((num_tokens - cached).sum())
+    cu_q, cu_k = np.empty(n + 1, dtype=np.int32), np.empty(n + 1, dtype=np.int32)
+    positions, slots = np.empty(total, dtype=np.int64), np.empty(total, dtype=np.int64)
+    mx = np.zeros(2, dtype=np.int32)
+    got = lib.b200_prepare_prefill(n, num_tokens.ctypes.data, cached.ctypes.data, offsets.ctypes.data, flat.ctypes.data,
+                                   block_size, cu_q.ctypes.data, cu_k.ctypes.data, positions.ctypes.data,
+                                   slots.ctypes.data, total, mx.ctypes.data)
+    if got != total:
+        raise RuntimeError(f"prepare_prefill: the native builder returned {got} for {total} tokens")
+    ids = [np.asarray(s.token_ids[s.num_cached_tokens:], dtype=np.int64) for s in seqs]
+    return StepMetadata(
+        is_prefill=True, input_ids=np.concatenate(ids) if ids else np.zeros(0, dtype=np.int64),
+        slot_mapping=slots, positions=positions, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
+        max_seqlen_q=int(mx[0]), max_seqlen_k=int(mx[1]),
+        block_tables=pad_block_tables(seqs) if cu_q[-1] < cu_k[-1] else None,
+        last_token_index=(cu_q[1:] - 1).astype(np.int64))
+
+
+def prepare_prefill_py(seqs: list[Sequence], block_size: int) -> StepMetadata:
     """Packs the non-cached suffix of every sequence (model_runner.py:202-249).
 
     The reference produces no positions tensor; the RoPE position of packed token j of a sequence
@@ -102,6 +140,28 @@ def prepare_prefill(seqs: list[Sequence], block_size: int) -> StepMetadata:
 
 
 def prepare_decode(seqs: list[Sequence], block_size: int, tables_out: np.ndarray | None = None) -> StepMetadata:
+    """One token per running sequence (model_runner.py:253-278): context lengths, slots and the padded block tables
+    come from the library's native builder (``b200_prepare_decode``); ``prepare_decode_py`` is the numpy form."""
+    if Sequence.reference_exact or tables_out is not None or not seqs:
+        return prepare_decode_py(seqs, block_size, tables_out)
+    from .._lib import lib
+    n = len(seqs)
+    num_tokens = np.fromiter((s.num_tokens for s in seqs), dtype=np.int64, count=n)
+    offsets, flat = _flat_tables(seqs)
+    width = max(int((offsets[1:] - offsets[:-1]).max()), 1)
+    lens, slots = np.empty(n, dtype=np.int64), np.empty(n, dtype=np.int64)
+    tables = np.empty((n, width), dtype=np.int32)
+    rc = lib.b200_prepare_decode(n, num_tokens.ctypes.data, offsets.ctypes.data, flat.ctypes.data, block_size,
+                                 lens.ctypes.data, slots.ctypes.data, tables.ctypes.data, width)
+    if rc != 0:
+        raise RuntimeError(f"prepare_decode: the native builder returned {rc}")
+    return StepMetadata(
+        is_prefill=False, input_ids=np.fromiter((s.last_token for s in seqs), dtype=np.int64, count=n),
+        slot_mapping=slots, positions=lens - 1, context_lens=lens, block_tables=tables,
+        last_token_index=np.arange(n, dtype=np.int64))
+
+
+def prepare_decode_py(seqs: list[Sequence], block_size: int, tables_out: np.ndarray | None = None) -> StepMetadata:
     """One token per running sequence (model_runner.py:253-278).  With ``tables_out`` (a preallocated
     [>= n, >= widest table] int32 array) the block tables are written into its first n rows, entries
     beyond a sequence's table keep their old values, and ``block_tables`` is that row range."""

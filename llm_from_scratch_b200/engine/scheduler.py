@@ -16,18 +16,23 @@ from __future__ import annotations
 import itertools
 from collections import deque
 
-from .block_manager import BlockManager
+from .block_manager import BlockManager, NativeBlockManager
 from .sequence import Sequence, SequenceStatus
 
 
 class Scheduler:
     def __init__(self, max_num_sequences: int, max_num_batched_tokens: int, max_cached_blocks: int,
-                 block_size: int, eos: int, reference_exact: bool = False):
+                 block_size: int, eos: int, reference_exact: bool = False, native_pool: bool = True):
         self.max_num_sequences = max_num_sequences
         self.max_num_batched_tokens = max_num_batched_tokens
         self.eos = eos
         self.reference_exact = reference_exact
-        self.block_manager = BlockManager(max_cached_blocks, block_size, reference_exact)
+        # the default mode keeps its block pool in the library (C++); the reference-exact mode, which reproduces
+        # the reference's ref-count arithmetic for the parity recordings, is the Python class
+        if reference_exact or not native_pool:
+            self.block_manager = BlockManager(max_cached_blocks, block_size, reference_exact)
+        else:
+            self.block_manager = NativeBlockManager(max_cached_blocks, block_size)
         self.waiting: deque[Sequence] = deque()
         self.running: deque[Sequence] = deque()
 
