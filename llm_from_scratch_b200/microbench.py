@@ -270,7 +270,7 @@ def decode_step_bytes(model: dict, seq_steps: int, ctx_tokens: int, steps: int, 
     return steps * weights + ctx_tokens * kv_row + seq_steps * (kv_row + d * 4 + 2 * V * itemsize)
 
 
-def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: int = 1,
+def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: int = 8,
                 hbm_peak_gbs: float = 6542.1) -> dict:
     """The continuous-batching benchmark through the engine (GQA+MoE decoder of ``C3_MODEL``, bf16, random init
     seed 0, KV block 16, at most 256 sequences and 8192 batched tokens per step, all requests present at
@@ -280,7 +280,10 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
     * ``fixed``: ``requests`` requests in total; replica r serves requests r, r + N, ...  (strong scaling)
     * ``weak``:  ``requests`` requests per replica, each replica its own seeded stream   (weak scaling)
 
-    With one replica the two are the same job and it runs once.  Rates are tokens of all replicas over the
+    ``fixed`` runs twice: with one decode step per scheduling decision (the reference's loop) and, as
+    ``fixed_window``, with ``decode_window`` decode graph replays per decision (same token streams; the sampled
+    token of one step feeds the next on the device); ``weak`` runs with the window.
+    With one replica fixed and weak are the same job.  Rates are tokens of all replicas over the
     slowest replica's wall time.  Returns {} on ranks other than 0."""
     import itertools
     import os
@@ -300,12 +303,16 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
     Sequence.counter = itertools.count()
     cfg = dict(model=C3_MODEL, dtype=torch.bfloat16, block_size=16, max_num_sequences=256,
                max_num_batched_tokens=8192, max_cached_blocks=pool_blocks, eos=-1, device=f"cuda:{local_rank}",
-               max_model_length=2048, seed=0, decode_window=decode_window)
+               max_model_length=2048, seed=0, decode_window=1)
     t0 = time.perf_counter()
     eng = LLMEngine(cfg)
     build_s = time.perf_counter() - t0
 
-    def run(job: str):
+    def run(job: str, window: int):
+        eng.decode_window = window
+        # a fresh block pool: a job must not find the previous job's prompts in the prefix cache
+        bm = eng.scheduler.block_manager
+        eng.scheduler.block_manager = type(bm)(eng.model_runner.num_kv_blocks, bm.block_size)
         if job == "fixed":
             prompts, outs, _ = c3_requests(requests, seed=3)
             shard = shard_requests(list(zip(prompts, outs)), world, rank)
@@ -338,6 +345,7 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
         gen_all, prompt_all = sum(r["generated"] for r in rows), sum(r["prompt"] for r in rows)
         fracs = [r["decode_bytes"] / r["run_decode_s"] / 1e9 / hbm_peak_gbs for r in rows]
         return dict(
+            decode_window=window,
             requests=requests * (world if job == "weak" else 1), replicas=world, generated_tokens=gen_all,
             prompt_tokens=prompt_all, wall_s=wall, replica_wall_s=[round(r["wall_s"], 4) for r in rows],
             output_tokens_per_s=gen_all / wall, total_tokens_per_s=(gen_all + prompt_all) / wall,
@@ -357,14 +365,16 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
                workload=f"{requests} requests at t=0, prompts U[64,1024], outputs geometric(256) cap 1024, max 256 "
                         "seqs / 8192 tokens per step per replica, KV block 16",
                replicas=world, kv_pool_blocks=pool_blocks, engine_build_s=build_s,
-               cuda_graphs=bool(eng.model_runner.graphs), decode_window=decode_window)
-    fixed = run("fixed")
-    weak = run("weak") if world > 1 else None
+               cuda_graphs=bool(eng.model_runner.graphs))
+    fixed = run("fixed", 1)
+    fixed_window = run("fixed", decode_window)
+    weak = run("weak", decode_window) if world > 1 else None
     eng.exit()
     if rank != 0:
         return {}
     out["fixed"] = fixed
-    out["weak"] = weak if weak is not None else "one replica: the same job as fixed"
+    out["fixed_window"] = fixed_window
+    out["weak"] = weak if weak is not None else "one replica: the same job as fixed_window"
     return out
 
 
