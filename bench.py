@@ -259,6 +259,9 @@ def secondary_kernels(steps_scale: float = 1.0) -> dict:
     out["store"] = hbm_bound(clocked(microbench.store, steps=n(50), warmup=5))
     out["mla_decode"] = hbm_bound(clocked(microbench.mla_decode, steps=n(50), warmup=5))
     out["moe_experts"] = hbm_bound(clocked(microbench.moe_experts, steps=n(20), warmup=3))
+    out["lm_head"] = hbm_bound(clocked(microbench.lm_head, steps=n(50), warmup=5))
+    p64 = clocked(microbench.prefill64, steps=n(20), warmup=3)
+    out["prefill_d64"] = tensor_bound(p64, p64["tflops"])
     mp = clocked(microbench.mla_prefill, steps=n(20), warmup=3)
     out["mla_prefill"] = tensor_bound(mp, mp["tflops"])
     pf = clocked(microbench.prefill, steps=n(5), warmup=3)
@@ -279,7 +282,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg (profiling runs)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary kernels (profiling runs)")
     ap.add_argument("--no-engine", action="store_true", help="skip the engine job (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "mla_prefill", "store", "moe_experts", "engine", "engine_mla", "engine_step"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mla_decode", "prefill", "prefill64", "mla_prefill", "store", "moe_experts", "lm_head", "engine", "engine_mla", "engine_step"],
                     help="decode = the benchmark (paged GQA decode); the others time a secondary kernel on "
                          "its benchmark shape and print a short JSON line (single GPU, no reference arm)")
     ap.add_argument("--rate", type=float, default=0.0, help="engine workload: Poisson arrival rate (req/s); 0 = offline")
@@ -302,7 +305,8 @@ def main():
             kw["decode_window"] = args.decode_window
         if args.batch != BATCH:   # profiling cases: fewer sequences / tokens
             key = {"mla_decode": "batch", "engine": "batch", "prefill": "total", "store": "tokens",
-                   "moe_experts": "tokens", "engine_mla": "batch", "mla_prefill": "seqs", "engine_step": "batch"}[args.workload]
+                   "moe_experts": "tokens", "engine_mla": "batch", "mla_prefill": "seqs", "engine_step": "batch",
+                   "prefill64": "seqs", "lm_head": "rows"}[args.workload]
             kw[key] = args.batch
         res = fn(**kw)
         if not res:       # a non-zero rank of a multi-replica engine run

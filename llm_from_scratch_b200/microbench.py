@@ -118,6 +118,58 @@ def mla_prefill(steps: int = 10, warmup: int = 3, seqs: int = 16) -> dict:
                 tflops=flops / ms / 1e9, tile_rows=tile_rows, launches_per_call=2)
 
 
+def prefill64(steps: int = 20, warmup: int = 3, seqs: int = 120) -> dict:
+    """Prefill attention at the GQA+MoE decoder's shape (16 query heads / 4 KV heads, head_dim 64) on a batch of
+    the continuous-batching workload's prompts: ``seqs`` sequences with lengths uniform [64,1024] (seed 3), packed;
+    one call = the step's tile list + the attention of one layer (tcgen05, four heads of a KV head per CTA)."""
+    rng = np.random.default_rng(3)
+    lens = rng.integers(64, 1025, size=seqs)
+    T, Hq, Hkv, D = int(lens.sum()), 16, 4, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g, device="cuda", dtype=torch.bfloat16)   # fused projection output
+    q = qkv[:, :Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).cuda()
+    out = torch.empty(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    mx = int(lens.max())
+    rows = ops.prefill_tile_rows(Hq, Hkv, D, D, torch.bfloat16)
+
+    def call():
+        plan = ops.prefill_plan(cu, T, mx, rows)
+        ops.prefill_varlen(q, k, v, cu, cu, mx, mx, D ** -0.5, out=out, plan=plan)
+
+    ms = _time(call, steps, warmup)
+    ops.check_status()
+    flops = prefill_flops(lens, Hq, D, D)
+    return dict(workload=f"prefill attention, head_dim 64: {seqs} seqs U[64,1024], {T} tokens, 16/4 heads, bf16",
+                ms=ms, tokens=T, flops=flops, tflops=flops / ms / 1e9, tile_rows=rows, launches_per_call=2)
+
+
+def lm_head(steps: int = 50, warmup: int = 5, rows: int = 256) -> dict:
+    """Greedy head of the GQA+MoE decoder: ``rows`` hidden states x the [32000, 1024] head matrix (+ bias), argmax
+    per row, fused (the logits are never written).  Eight distinct head matrices are used in turn so that the
+    65.5 MB matrix is streamed from HBM on every call, as in a decode step (the other weights of a step evict it
+    from the 126 MB L2)."""
+    V, d = 32000, 1024
+    g = torch.Generator(device="cuda").manual_seed(7)
+    ws = [(torch.randn(V, d, generator=g, device="cuda") * d ** -0.5).bfloat16() for _ in range(8)]
+    b = (torch.randn(V, generator=g, device="cuda") * 0.1).bfloat16()
+    h = torch.randn(rows, d, generator=g, device="cuda").bfloat16()
+    out = torch.empty(rows, dtype=torch.int64, device="cuda")
+    state = {"i": 0}
+
+    def call():
+        ops.lm_head_argmax(h, ws[state["i"] % 8], b, out)
+        state["i"] += 1
+
+    ms = _time(call, steps, warmup)
+    ops.check_status()
+    nbytes = V * d * 2 + V * 2 + rows * d * 2 + rows * 8
+    return dict(workload=f"greedy head: {rows} rows x [32000, 1024] + bias -> argmax, bf16, fused",
+                ms=ms, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, launches_per_call=2)
+
+
 def store(steps: int = 50, warmup: int = 5, tokens: int = 262144) -> dict:
     """store_kvcache of the prefill stress batch: shuffled slot mapping (seed 2), 8 x 128 bf16 rows."""
     Hkv, D, bs = 8, 128, 16
