@@ -477,6 +477,11 @@ int launch(const GemmArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, dim3
 }
 
 }  // namespace
+
+int moe_gemm_rows_launch(const void* x, const void* w, const void* bias, void* out, const int32_t* expert_offsets,
+                         int64_t num_rows, int num_experts, int dense_rows, int n_out, int k_dim, int mode,
+                         int32_t* status, cudaStream_t s);
+
 }  // namespace b200
 
 extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* bias, void* out,
@@ -518,6 +523,10 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* b
     const dim3 grid(tiles, num_experts + (dense_rows + 63) / 64);
     return launch<64, 4>(a, tw, tx, grid, early, s);
   }
+  // many rows per expert: the compute-bound kernel (token rows as the MMA M side, persistent CTAs)
+  const int rc = moe_gemm_rows_launch(x, w, bias, out, expert_offsets, num_rows, num_experts, dense_rows, n_out, k_dim,
+                                      mode, status, s);
+  if (rc != B200_ERR_UNSUPPORTED) return rc;
   const dim3 grid(tiles, num_experts + (dense_rows + 255) / 256);
   return launch<256, 4>(a, tw, tx, grid, early, s);
 }

@@ -758,6 +758,8 @@ def _grouped_reference(x, w, offs, bias, swiglu):
     ([700, 90, 300, 10], 512, 192, True),                    # large batch: 256 rows per pass, several passes
     ([700, 90, 300, 10], 192, 520, False),
     ([0, 0, 5], 64, 64, False),
+    ([915, 1, 0, 1300, 128, 129, 127, 400], 1024, 704, True),    # compute-bound kernel: ragged row tiles, 5.5 column tiles
+    ([915, 1, 0, 1300, 128, 129, 127, 400], 704, 1024, False),
 ])
 def test_moe_grouped_gemm_matches_per_expert_matmuls(counts, k, n, swiglu):
     ops = _ops()
@@ -777,12 +779,15 @@ def test_moe_grouped_gemm_matches_per_expert_matmuls(counts, k, n, swiglu):
     assert torch.equal(again, ops.moe_grouped_gemm(x, w, offs, bias, swiglu=swiglu))
 
 
-@pytest.mark.parametrize("swiglu", [True, False])
-def test_moe_grouped_gemm_dense_tail_is_one_more_weight_set(swiglu):
+@pytest.mark.parametrize("swiglu,big", [(True, False), (False, False), (True, True), (False, True)])
+def test_moe_grouped_gemm_dense_tail_is_one_more_weight_set(swiglu, big):
     """Rows after the grouped ones that all use weight set E (a shared expert in the same launch), in
-    chunks of 64; 150 tail rows = two full chunks and a ragged one."""
+    chunks of 64; 150 tail rows = two full chunks and a ragged one.  ``big``: many rows per expert, served by
+    the compute-bound kernel, where the tail is one more group of row tiles."""
     ops = _ops()
     counts, tail, k, n = [12, 0, 31, 7, 16, 1, 60, 25], 150, 256, 192
+    if big:
+        counts, tail = [300, 0, 131, 700, 16, 1, 260, 425], 917
     E, R = len(counts), sum(counts)
     offs = torch.tensor(np.cumsum(counts), dtype=torch.int32, device="cuda")
     x = _randn((R + tail, k), 41, torch.bfloat16).cuda()
