@@ -1,21 +1,24 @@
 // Grouped GEMM for MoE inference at PREFILL sizes (hundreds of rows per expert), on the sm_100a tensor cores
 // (tcgen05): the compute-bound sibling of moe_gemm.cu, which serves the weight-streaming decode regime.
 // Same contract (the per-expert loop of MOE.moe_infer, model/architecture/moe.py:299-339; SwiGLU of
-// mlp.py:61-67 in mode 1), conventional orientation: 128 TOKEN rows are the M dimension of the MMA, 256
-// weight rows its N dimension, the accumulator [128 x 256] fp32 sits in tensor memory.
+// mlp.py:61-67 in mode 1), conventional orientation: TOKEN rows are the M dimension of the MMA, 256 weight rows
+// its N dimension.  A work item is a 256 x 256 tile computed as two M = 128 products on the same weight
+// operand (two accumulators of 256 tensor-memory columns): with 128 x 256 tiles every CTA pulls 48 KB from L2
+// per 64-wide k-step for 4.2 MFLOP and the kernel was bound by L2-to-SM bandwidth at ~1 us per k-step; the
+// square tile moves 64 KB for twice the arithmetic.
 //
 //   mode 0:  out[r, n0 .. n0+255]  = X[r] . W_e[n0 .. n0+255]^T (+ bias)
 //   mode 1:  a tile holds 128 rows of w1 and the matching 128 rows of w3 of the same features, so
 //            act[r, f0 .. f0+127] = silu(X[r] . W1^T + b1) * (X[r] . W3^T + b3) is formed in the epilogue and the
 //            [rows, 2 * d_ff] intermediate is never written
 //
-// Persistent CTAs (one per SM) walk the list of (group, 128-row tile, column tile) work items, column tile
+// Persistent CTAs (one per SM) walk the list of (group, 256-row tile, column tile) work items, column tile
 // fastest; groups are the experts' row ranges (read from expert_offsets on the device) plus, when
 // dense_rows > 0, one more group with weight set E (a shared expert over all tokens in the same launch).
-//   warp 0      TMA producer: one thread, ring of 4 stages of (A 16 KB | B 32 KB), 128-byte swizzle
-//   warp 1      tensor-memory owner; lane 0 issues tcgen05.mma (M 128, N 256, K 16), two accumulators
-//   warps 2-5   epilogue: thread = token row; tensor memory -> registers -> bias / rounding / SwiGLU -> global.
-// The epilogue of an item overlaps the MMAs of the next (double-buffered accumulator, 512 columns).
+//   warp 0      TMA producer: one thread, ring of 3 stages of (A 32 KB | B 32 KB), 128-byte swizzle
+//   warp 1      tensor-memory owner; lane 0 issues tcgen05.mma (M 128, N 256, K 16), one per row half
+//   warps 2-9   epilogue: thread = token row; tensor memory -> registers -> bias / rounding / SwiGLU -> global.
+// A tile whose group has at most 128 rows left skips its second half (no copy, no MMA).
 // Every wait is bounded; a timeout raises the CTA's abort flag, is reported (B200_ERR_TIMEOUT), copies in
 // flight are drained and the tensor memory is freed.
 #include <cuda.h>
@@ -26,15 +29,15 @@
 namespace b200 {
 namespace {
 
-constexpr int kThreads = 192;
-constexpr int BM = 128;                 // token rows per tile
+constexpr int kThreads = 320;
+constexpr int BM = 256;                 // token rows per tile (two M = 128 halves)
 constexpr int BN = 256;                 // weight rows per tile
 constexpr int BK = 64;                  // K elements per stage (128 bytes)
 constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
-constexpr int NST = 4;
+constexpr int NST = 3;
 constexpr int kMaxGroups = 66;          // 64 experts + a dense tail + sentinel
 constexpr int OFF_BAR = NST * STAGE;
-constexpr int FULL = 0, EMPTY = NST, ACC_FULL = 2 * NST, ACC_EMPTY = 2 * NST + 2, NUM_BARS = 2 * NST + 4;
+constexpr int FULL = 0, EMPTY = NST, ACC_FULL = 2 * NST, ACC_EMPTY = 2 * NST + 1, NUM_BARS = 2 * NST + 2;
 constexpr int OFF_TAB = OFF_BAR + NUM_BARS * 8 + 16;             // group table: first row, rows, first m-tile
 constexpr int SMEM = OFF_TAB + 3 * kMaxGroups * 4 + 1024;       // + slack to align the base to 1024 bytes
 
@@ -109,10 +112,8 @@ moe_gemm_rows_kernel(const RowsArgs a, const __grid_constant__ CUtensorMap tm_x,
       umma::mbar_init(bar(FULL + s), 1);
       umma::mbar_init(bar(EMPTY + s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      umma::mbar_init(bar(ACC_FULL + b), 1);
-      umma::mbar_init(bar(ACC_EMPTY + b), 128);
-    }
+    umma::mbar_init(bar(ACC_FULL), 1);
+    umma::mbar_init(bar(ACC_EMPTY), 256);
     *s_abort = 0;
     umma::mbar_init_fence();
   }
@@ -160,8 +161,10 @@ moe_gemm_rows_kernel(const RowsArgs a, const __grid_constant__ CUtensorMap tm_x,
             break;
           }
           const uint32_t dst = sb + st * STAGE;
-          umma::mbar_expect_tx(bar(FULL + st), STAGE);
+          const bool two = im.rows > 128;                  // the second row half holds rows of this group
+          umma::mbar_expect_tx(bar(FULL + st), two ? STAGE : STAGE - A_BYTES / 2);
           tma_2d(dst, &tm_x, ks * BK, im.row0, bar(FULL + st));
+          if (two) tma_2d(dst + A_BYTES / 2, &tm_x, ks * BK, im.row0 + 128, bar(FULL + st));
           if (swiglu) {
             tma_2d(dst + A_BYTES, &tm_w, ks * BK, wrow, bar(FULL + st));                          // 128 rows of w1
             tma_2d(dst + A_BYTES + B_BYTES / 2, &tm_w, ks * BK, wrow + a.n_out, bar(FULL + st));   // ... of w3
@@ -181,17 +184,17 @@ moe_gemm_rows_kernel(const RowsArgs a, const __grid_constant__ CUtensorMap tm_x,
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
     if (lane == 0) {
-      const uint32_t idesc = umma::instr_desc_bf16(BM, BN, false, false);
+      const uint32_t idesc = umma::instr_desc_bf16(128, BN, false, false);
       int it = 0, n_item = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x, ++n_item) {
-        const int buf = n_item & 1;
-        if (n_item >= 2 && !umma::mbar_wait(bar(ACC_EMPTY + buf), ((n_item >> 1) - 1) & 1, s_abort)) {
+        const Item im = item_of(w);
+        const bool two = im.rows > 128;
+        if (n_item >= 1 && !umma::mbar_wait(bar(ACC_EMPTY), (n_item - 1) & 1, s_abort)) {
           give_up();
           break;
         }
         umma::fence_after_sync();
-        const uint32_t acc = tmem + buf * BN;
         for (int ks = 0; ks < num_k; ++ks, ++it) {
           const int st = it % NST;
           if (!umma::mbar_wait(bar(FULL + st), (it / NST) & 1, s_abort)) {
@@ -201,31 +204,35 @@ moe_gemm_rows_kernel(const RowsArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           umma::fence_after_sync();
           const uint32_t sa = sb + st * STAGE;
-          const uint64_t adesc = umma::smem_desc(sa, 0, 1024);
+          const uint64_t adesc0 = umma::smem_desc(sa, 0, 1024);
+          const uint64_t adesc1 = umma::smem_desc(sa + A_BYTES / 2, 0, 1024);
           const uint64_t bdesc = umma::smem_desc(sa + A_BYTES, 0, 1024);
 #pragma unroll
-          for (int j = 0; j < BK / 16; ++j) umma::mma_ss(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (ks | j) != 0);
+          for (int j = 0; j < BK / 16; ++j) {
+            umma::mma_ss(tmem, adesc0 + 2 * j, bdesc + 2 * j, idesc, (ks | j) != 0);
+            if (two) umma::mma_ss(tmem + BN, adesc1 + 2 * j, bdesc + 2 * j, idesc, (ks | j) != 0);
+          }
           umma::commit(bar(EMPTY + st));
         }
-        if (ok) umma::commit(bar(ACC_FULL + buf));
+        if (ok) umma::commit(bar(ACC_FULL));
       }
     }
   } else {
-    // =============================== epilogue (4 warps, thread = token row) ===============================
+    // =============================== epilogue (8 warps, thread = token row) ===============================
     const int q = warp & 3;                          // tensor-memory lane quarter this warp may read
-    const int row = q * 32 + lane;
+    const int half = (warp - 2) >> 2;                // row half of the tile = accumulator
+    const int row = half * 128 + q * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     int n_item = 0;
     for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++n_item) {
       const Item im = item_of(w);
-      const int buf = n_item & 1;
       // tensor-memory loads are warp-collective: the whole warp continues or stops together
-      if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(ACC_FULL + buf), (n_item >> 1) & 1, s_abort))) {
+      if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(ACC_FULL), n_item & 1, s_abort))) {
         give_up();
         break;
       }
       umma::fence_after_sync();
-      const uint32_t acc = tmem + buf * BN + lane_sel;
+      const uint32_t acc = tmem + half * BN + lane_sel;
       const bool valid = row < im.rows;
       __nv_bfloat16* orow = a.out + (static_cast<int64_t>(im.row0) + row) * a.n_out + im.n0;
       if (swiglu) {
@@ -252,7 +259,8 @@ moe_gemm_rows_kernel(const RowsArgs a, const __grid_constant__ CUtensorMap tm_x,
                 gv = bf16r(gv + __bfloat162float(b1.b[x]));
                 uv = bf16r(uv + __bfloat162float(b3.b[x]));
               }
-              const float sv = bf16r(gv / (1.f + expf(-gv)));
+              // fast exponential and division: their ~1e-6 relative error disappears in the bf16 rounding of silu
+              const float sv = bf16r(__fdividef(gv, 1.f + __expf(-gv)));
               o.b[x] = __float2bfloat16(sv * uv);
             }
             *reinterpret_cast<uint4*>(orow + c + e8) = o.u;
@@ -283,7 +291,7 @@ moe_gemm_rows_kernel(const RowsArgs a, const __grid_constant__ CUtensorMap tm_x,
         }
       }
       umma::fence_before_sync();
-      umma::mbar_arrive(bar(ACC_EMPTY + buf));
+      umma::mbar_arrive(bar(ACC_EMPTY));
     }
   }
   umma::fence_before_sync();
@@ -318,7 +326,7 @@ bool rows_make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
   if (enc == nullptr || rows <= 0) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), 128};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), 128};   // halves of the A and B tiles
   const cuuint32_t estr[2] = {1, 1};
   return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

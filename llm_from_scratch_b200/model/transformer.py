@@ -117,7 +117,12 @@ class MoE(nn.Module):
 
     dense_max_tokens = 512
     use_grouped = True     # bf16: grouped GEMMs over tokens sorted by expert (no host sync)
-    own_gemm_max_rows_per_expert = 64   # average rows per expert up to which the weight-streaming kernel is used
+    # Average rows per expert up to which the grouped GEMMs of this package are used (weight-streaming kernel up to
+    # 64, compute-bound kernel above); larger batches go to the library grouped GEMM, which on the 7,300-token
+    # prefill steps of the benchmark engine is 11 % faster per step than the compute-bound kernel (both are bound by
+    # L2-to-SM traffic; the library overlaps its epilogue with the next tile).  At 2,048 tokens the own kernels win
+    # (122 against 163-195 us per layer, fewer launches: SwiGLU and the shared expert ride in the two GEMMs).
+    own_gemm_max_rows_per_expert = 256
     # Gate projection + routing (+ gather) as one launch (ops.moe_gate_route).  Off: measured on B200 inside a
     # CUDA graph the one launch takes 10.0 / 11.7 / 12.1 us at 1 / 64 / 256 tokens against 9.6 / 8.9 / 10.3 us for
     # the library GEMM + routing kernel + gather it replaces — each of those is a single memory round trip behind
