@@ -17,10 +17,20 @@
 // Tensor memory per problem (256 columns): two score buffers S 128 x 64 fp32 (bf16 P overwrites the first
 // 32 columns of its buffer and is the A operand of O += P.V) and O 128 x DV fp32.  Each issuing thread puts
 // the scores of tile j + 1 into the other buffer before it waits for the probabilities of tile j, so the
-// softmax warps (which set the pace: the tensor pipe needs less than half of an iteration) find their next
-// tile ready, and one problem's waits never hold up the other's instructions.  K/V tiles go through a ring
-// of NST stages that both problems release.  Rescaling of O is lazy as in prefill_umma.cu and waits for the
-// P.V product before it.  Every wait is bounded; a timeout aborts the CTA and is reported.
+// softmax warps find their next tile ready, and one problem's waits never hold up the other's instructions.
+// K/V tiles go through a ring of NST stages that both problems release.  Rescaling of O is lazy as in
+// prefill_umma.cu and waits for the P.V product before it.  Every wait is bounded; a timeout aborts the CTA
+// and is reported.
+//
+// What sets the pace, measured with clock counters in the warps: (1) the special-function unit — the 64
+// exponentials of a row tile occupy it for 512 clocks per warp, and the A and B warps of a scheduler, left
+// alone, run in step, share it during their exponentials (1,200 clocks each) and leave it idle during their
+// loads and maxima; their exponential phases therefore take turns (A(j), B(j), A(j + 1), ...; 650 clocks each),
+// and one warp's loads, maxima and waits run under the other's exponentials; (2) the issuing threads' own
+// instruction streams (each shares its scheduler with two softmax warps): descriptors are formed once and only
+// their address field advanced, and one tcgen05.commit per product serves every waiter (the barrier that frees a
+// K stage also announces the scores computed from it, the barrier that frees a V stage also announces the
+// product into O).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -43,11 +53,15 @@ struct Lay {
   static constexpr int NST = DQK >= 192 ? 3 : 4;
   static constexpr int OFF_QA = 0, OFF_QB = Q_BYTES, OFF_KV = 2 * Q_BYTES;
   static constexpr int OFF_BAR = OFF_KV + NST * STAGE;
-  // barriers: Q_FULL, then per stage K_FULL, V_FULL, K_EMPTY[problem], V_EMPTY[problem], then
-  // S_FULL[problem][score buffer], P_READY[problem], PV_DONE[problem], O_FINAL[problem]
-  static constexpr int Q_FULL = 0, K_FULL = 1, V_FULL = 1 + NST, K_EMPTY = 1 + 2 * NST, V_EMPTY = 1 + 4 * NST;
-  static constexpr int S_FULL = 1 + 6 * NST, P_READY = S_FULL + 4, PV_DONE = S_FULL + 6, O_FINAL = S_FULL + 8,
-                       NUM_BARS = S_FULL + 10;
+  // barriers: Q_FULL; per stage K_FULL, V_FULL; per stage and problem QK_DONE (the scores of the tile in this
+  // stage are in tensor memory, and the K stage is free for this problem) and PV_DONE (the product of the tile
+  // in this stage is in O, and the V stage is free for this problem); per problem and score buffer P_READY;
+  // per scheduler TURN_A, TURN_B (whose exponentials run next).
+  // P_READY is per buffer because the softmax warps may finish tile j + 1 before the issuing thread has looked at
+  // tile j (the scores of both were issued ahead); a single barrier would then have completed two phases and a
+  // wait by parity could not tell tile j from tile j + 2.  No other barrier can run two phases ahead of a waiter.
+  static constexpr int Q_FULL = 0, K_FULL = 1, V_FULL = 1 + NST, QK_DONE = 1 + 2 * NST, PV_DONE = 1 + 4 * NST,
+                       P_READY = 1 + 6 * NST, TURN = P_READY + 4, NUM_BARS = TURN + 8;
   static constexpr int SMEM = OFF_BAR + NUM_BARS * 8 + 32 + 1024;   // + slack to align the base to 1024 bytes
   static constexpr int TCOLS_USED = 2 * (128 + DV);   // per problem: two score buffers of 64 columns + O
   static constexpr int TCOLS = TCOLS_USED > 256 ? 512 : 256;
@@ -114,17 +128,12 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
       umma::mbar_init(bar(L::K_FULL + s), 1);
       umma::mbar_init(bar(L::V_FULL + s), 1);
       for (int x = 0; x < 2; ++x) {
-        umma::mbar_init(bar(L::K_EMPTY + 2 * s + x), 1);
-        umma::mbar_init(bar(L::V_EMPTY + 2 * s + x), 1);
+        umma::mbar_init(bar(L::QK_DONE + 2 * s + x), 1);
+        umma::mbar_init(bar(L::PV_DONE + 2 * s + x), 1);
       }
     }
-    for (int x = 0; x < 2; ++x) {
-      umma::mbar_init(bar(L::S_FULL + 2 * x), 1);
-      umma::mbar_init(bar(L::S_FULL + 2 * x + 1), 1);
-      umma::mbar_init(bar(L::PV_DONE + x), 1);
-      umma::mbar_init(bar(L::P_READY + x), 128);
-      umma::mbar_init(bar(L::O_FINAL + x), 1);
-    }
+    for (int i = 0; i < 4; ++i) umma::mbar_init(bar(L::P_READY + i), 128);
+    for (int i = 0; i < 8; ++i) umma::mbar_init(bar(L::TURN + i), 32);
     *s_abort = 0;
     umma::mbar_init_fence();
   }
@@ -133,8 +142,6 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = *s_tmem;
-  // problem x: score buffers at x * (128 + DV) + {0, 64}, output accumulator behind them
-  const uint32_t tS[2] = {tmem, tmem + 128 + DV}, tO[2] = {tmem + 128, tmem + 256 + DV};
 
   auto give_up = [&]() {
     *s_abort = 1;
@@ -157,7 +164,7 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
             umma::tma_load_3d(sb + (x ? L::OFF_QB : L::OFF_QA) + h * Q_SLAB, &tm_q, h * 64, head,
                               q0 + m0 + x * BM, bar(L::Q_FULL));
       }
-      const int full0 = is_k ? L::K_FULL : L::V_FULL, empty0 = is_k ? L::K_EMPTY : L::V_EMPTY;
+      const int full0 = is_k ? L::K_FULL : L::V_FULL, empty0 = is_k ? L::QK_DONE : L::PV_DONE;
       for (int j = 0; j < n; ++j) {
         const int st = j % NST;
         if (j >= NST) {   // both problems must have released the tile that occupied this stage
@@ -182,68 +189,73 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
     }
   } else if (warp < 4) {
     // =============================== MMA issuers ===============================
-    // One issuing thread per problem (warp 2: A, warp 3: B) and two score buffers per problem: the scores of
-    // tile j + 1 are issued before the thread waits for the probabilities of tile j, so a softmax warp finds
-    // its next tile ready, and neither problem's waits hold up the other's instructions.
     const int x = warp - 2;
     if (lane == 0 && nt[x] > 0) {
       const uint32_t idesc_qk = umma::instr_desc_bf16(BM, BN, false, false);
       const uint32_t idesc_pv = umma::instr_desc_bf16(BM, DV, false, true);
-      const uint32_t qbase = sb + (x ? L::OFF_QB : L::OFF_QA);
       const int nx = nt[x];
-      auto qk = [&](int j) {       // S[j & 1] = Q . K_j^T : contraction over d in steps of 16
-        const int st = j % NST;
-        const uint32_t kbase = sb + L::OFF_KV + st * L::STAGE;
+      const uint64_t qd = umma::smem_desc(sb + (x ? L::OFF_QB : L::OFF_QA), 0, 1024);
+      const uint64_t kd = umma::smem_desc(sb + L::OFF_KV, 0, 1024);
+      const uint64_t vd = umma::smem_desc(sb + L::OFF_KV + L::K_BYTES, K_SLAB, 1024);
+      const uint32_t tSx = tmem + x * (128 + DV), tOx = tSx + 128;
+      auto qk = [&](int st, int buf) {       // S[buf] = Q . K^T of the tile in stage st, contraction in steps of 16
+        const uint32_t so = st * (L::STAGE >> 4);
 #pragma unroll
-        for (int ks = 0; ks < DQK / 16; ++ks) {
-          const uint32_t oq = (ks >> 2) * Q_SLAB + (ks & 3) * 32, ok2 = (ks >> 2) * K_SLAB + (ks & 3) * 32;
-          umma::mma_ss(tS[x] + (j & 1) * 64, umma::smem_desc(qbase + oq, 0, 1024),
-                       umma::smem_desc(kbase + ok2, 0, 1024), idesc_qk, ks > 0);
-        }
-        umma::commit(bar(L::S_FULL + 2 * x + (j & 1)));
-        umma::commit(bar(L::K_EMPTY + 2 * st + x));
+        for (int ks = 0; ks < DQK / 16; ++ks)
+          umma::mma_ss(tSx + buf * 64, umma::desc_advance(qd, ((ks >> 2) * Q_SLAB + (ks & 3) * 32) >> 4),
+                       umma::desc_advance(kd, so + (((ks >> 2) * K_SLAB + (ks & 3) * 32) >> 4)), idesc_qk, ks > 0);
+        umma::commit(bar(L::QK_DONE + x) + st * 16);
       };
       bool ok = umma::mbar_wait(bar(L::Q_FULL), 0, s_abort) && umma::mbar_wait(bar(L::K_FULL + 0), 0, s_abort);
       if (!ok) give_up();
       if (ok) {
         umma::fence_after_sync();
-        qk(0);
+        qk(0, 0);
       }
+      int st = 0, ph = 0;                      // stage and phase of tile j
       for (int j = 0; ok && j < nx; ++j) {
-        const int st = j % NST, ph = (j / NST) & 1;
-        if (j + 1 < nx) {
-          WAIT_OR_ABORT(L::K_FULL + (j + 1) % NST, ((j + 1) / NST) & 1)
-          umma::fence_after_sync();
-          qk(j + 1);
+        int st1 = st + 1, ph1 = ph;
+        if (st1 == NST) {
+          st1 = 0;
+          ph1 ^= 1;
         }
-        WAIT_OR_ABORT(L::P_READY + x, j & 1)
+        if (j + 1 < nx) {
+          WAIT_OR_ABORT(L::K_FULL + st1, ph1)
+          umma::fence_after_sync();
+          qk(st1, (j + 1) & 1);
+        }
+        WAIT_OR_ABORT(L::P_READY + 2 * x + (j & 1), (j >> 1) & 1)
         WAIT_OR_ABORT(L::V_FULL + st, ph)
         umma::fence_after_sync();
-        const uint32_t vbase = sb + L::OFF_KV + st * L::STAGE + L::K_BYTES;
+        const uint32_t so = st * (L::STAGE >> 4);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)        // O += P[j & 1] . V_j : contraction over the 64 keys
-          umma::mma_ts(tO[x], tS[x] + (j & 1) * 64 + ks * 8, umma::smem_desc(vbase + ks * 2048, K_SLAB, 1024),
-                       idesc_pv, !(j == 0 && ks == 0));
-        umma::commit(bar(L::PV_DONE + x));
-        umma::commit(bar(L::V_EMPTY + 2 * st + x));
-        if (j == nx - 1) umma::commit(bar(L::O_FINAL + x));
+          umma::mma_ts(tOx, tSx + (j & 1) * 64 + ks * 8, umma::desc_advance(vd, so + ks * (2048 >> 4)), idesc_pv,
+                       !(j == 0 && ks == 0));
+        umma::commit(bar(L::PV_DONE + x) + st * 16);
+        st = st1;
+        ph = ph1;
       }
     }
-  } else if (warp >= 4) {
+  } else {
     // =============================== softmax / epilogue ===============================
     const int x = warp >= 8 ? 1 : 0;                        // problem A or B
     const int row = (warp & 3) * 32 + lane;                 // query row of the problem == tensor-memory lane
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS0 = tS[x] + lane_sel, tOx = tO[x] + lane_sel;
+    const uint32_t tS0 = tmem + x * (128 + DV) + lane_sel, tOx = tS0 + 128;
     const int qrow = m0 + x * BM + row;                     // index of the query inside its sequence
     const int lim = min(off + qrow, kmax[x] - 1);           // last visible key
     const int nx = nt[x];
+    const uint32_t qk_done = bar(L::QK_DONE + x), pv_done = bar(L::PV_DONE + x);
+    const uint32_t my_turn = bar(L::TURN + (x == 0 ? 0 : 4) + (warp & 3));
+    const uint32_t their_turn = bar(L::TURN + (x == 0 ? 4 : 0) + (warp & 3));
     float m_ref = -INFINITY, l = 0.f;
     bool alive = true;
+    int st = 0, ph = 0, stp = 0, php = 0;                   // stage and phase of tile j and of tile j - 1
     for (int j = 0; j < nx; ++j) {
       // tensor-memory loads / stores are warp-collective: the whole warp continues or stops together
       const uint32_t tSx = tS0 + (j & 1) * 64;                // score buffer of this tile
-      if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(L::S_FULL + 2 * x + (j & 1)), (j >> 1) & 1, s_abort))) {
+      if (!__all_sync(0xffffffffu, umma::mbar_wait(qk_done + st * 16, ph, s_abort))) {
         give_up();
         alive = false;
         break;
@@ -286,7 +298,7 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
         l *= alpha;
         if (j > 0) {
           // O still receives P(j-1).V(j-1): the scores of this tile were issued ahead of that product
-          if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(L::PV_DONE + x), (j - 1) & 1, s_abort))) {
+          if (!__all_sync(0xffffffffu, umma::mbar_wait(pv_done + stp * 16, php, s_abort))) {
             give_up();
             alive = false;
             break;
@@ -303,6 +315,14 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
           umma::tmem_wait_st();
         }
         m_ref = m_new;
+      }
+      // whose exponentials run now: A(j) follows B(j - 1), B(j) follows A(j) while A has tiles left
+      if (x == 0 ? (has_b && j >= 1) : (j < nt[0])) {
+        if (!__all_sync(0xffffffffu, umma::mbar_wait(my_turn, (x == 0 ? j - 1 : j) & 1, s_abort))) {
+          give_up();
+          alive = false;
+          break;
+        }
       }
       // P = 2^(s * scale - m_ref) as bf16 into the first 32 columns of S, row sum in fp32
       const float sub = m_ref == -INFINITY ? 0.f : m_ref;
@@ -325,6 +345,7 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
       };
       emit(ra, 0);
       emit(rb, 1);
+      umma::mbar_arrive(their_turn);
       {
         float la, lb;
         umma::unpack_f32x2(lsum2, la, lb);
@@ -332,10 +353,17 @@ prefill_umma2_kernel(const Args2 a, const __grid_constant__ CUtensorMap tm_q, co
       }
       umma::tmem_wait_st();
       umma::fence_before_sync();
-      umma::mbar_arrive(bar(L::P_READY + x));
+      umma::mbar_arrive(bar(L::P_READY + 2 * x + (j & 1)));
+      stp = st;
+      php = ph;
+      if (++st == NST) {
+        st = 0;
+        ph ^= 1;
+      }
     }
     if (nx > 0) {
-      if (alive && __all_sync(0xffffffffu, umma::mbar_wait(bar(L::O_FINAL + x), 0, s_abort))) {
+      // the last product: stp / php are the stage and phase of tile nx - 1
+      if (alive && __all_sync(0xffffffffu, umma::mbar_wait(pv_done + stp * 16, php, s_abort))) {
         umma::fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* op = a.out + (static_cast<int64_t>(q0 + qrow) * a.Hq + head) * DV;

@@ -27,6 +27,16 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// The same descriptor with its start address moved by `units16` units of 16 bytes (one 32-bit add: the address
+// field is the low 14 bits, and shared memory is far smaller than what they span).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t units16) {
+  uint32_t lo, hi;
+  asm("mov.b64 {%0, %1}, %2;\n" : "=r"(lo), "=r"(hi) : "l"(d));
+  lo += units16;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 __device__ __forceinline__ uint32_t instr_desc_bf16(int M, int N, bool a_mn_major, bool b_mn_major) {
   uint32_t d = 0;
@@ -138,6 +148,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 // ---- packed fp32x2 arithmetic (one instruction for two lanes of data) ---------------------------
+// Named barrier over `count` threads (a multiple of 32) of the CTA; id 0 is __syncthreads.
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+}
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t d;
   asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "f"(lo), "f"(hi));
