@@ -44,7 +44,8 @@ constexpr int OFF_Q = 0, OFF_KV = NP * Q_BYTES, OFF_BAR = OFF_KV + NST * STAGE;
 // barriers: Q_FULL, per stage K_FULL, V_FULL, K_EMPTY, V_EMPTY (NP arrivals each), per problem S_FULL, P_READY,
 // O_FINAL
 constexpr int Q_FULL = 0, K_FULL = 1, V_FULL = 1 + NST, K_EMPTY = 1 + 2 * NST, V_EMPTY = 1 + 3 * NST,
-              S_FULL = 1 + 4 * NST, P_READY = S_FULL + NP, O_FINAL = S_FULL + 2 * NP, NUM_BARS = S_FULL + 3 * NP;
+              S_FULL = 1 + 4 * NST, P_READY = S_FULL + NP, O_FINAL = S_FULL + 2 * NP, TURN = S_FULL + 3 * NP,
+              NUM_BARS = TURN + 8;   // TURN[softmax group][scheduler]: whose exponentials run next
 constexpr int SMEM = OFF_BAR + NUM_BARS * 8 + 32 + 1024;   // + slack to align the base to 1024 bytes
 constexpr int TCOLS = 512;
 
@@ -106,6 +107,7 @@ prefill_umma4_kernel(const Args4 a, const __grid_constant__ CUtensorMap tm_q, co
       umma::mbar_init(bar(P_READY + x), 128);
       umma::mbar_init(bar(O_FINAL + x), 1);
     }
+    for (int i = 0; i < 8; ++i) umma::mbar_init(bar(TURN + i), 32);
     *s_abort = 0;
     umma::mbar_init_fence();
   }
@@ -252,6 +254,22 @@ prefill_umma4_kernel(const Args4 a, const __grid_constant__ CUtensorMap tm_q, co
           }
           m_ref[pp] = m_new;
         }
+        // The exponentials of the two softmax warps of a scheduler (this row quarter of either group) take turns:
+        // group 0's k-th tile, group 1's k-th, group 0's (k + 1)-th, ...  Left alone the two warps run in step,
+        // share the special-function unit during their exponentials (64 per row and tile: 512 clocks per warp,
+        // more than the tensor pipe needs for the tile at this head dimension) and leave it idle during their
+        // loads and maxima; in turns one warp's loads, maxima and waits run under the other's exponentials.
+        {
+          const int k = 2 * j + pp;
+          if (grp == 0 ? k >= 1 : true) {
+            if (!__all_sync(0xffffffffu, umma::mbar_wait(bar(TURN + grp * 4 + (warp & 3)), (grp == 0 ? k - 1 : k) & 1,
+                                                         s_abort))) {
+              give_up();
+              alive = false;
+              break;
+            }
+          }
+        }
         // P = 2^(s * scale - m_ref) as bf16 into the first 32 columns of S, row sum in fp32
         const float sub = m_ref[pp] == -INFINITY ? 0.f : m_ref[pp];
         const uint64_t scale2 = umma::pack_f32x2(a.scale_log2, a.scale_log2);
@@ -273,6 +291,7 @@ prefill_umma4_kernel(const Args4 a, const __grid_constant__ CUtensorMap tm_q, co
         };
         emit(ra, 0);
         emit(rb, 1);
+        umma::mbar_arrive(bar(TURN + (grp ^ 1) * 4 + (warp & 3)));   // the other group's turn
         {
           float la, lb;
           umma::unpack_f32x2(lsum2, la, lb);
