@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory by running the REFERENCE's own code.
 
-Run in the build container only (needs /root/reference; the GPU box does not have it):
+Needs a checkout of the reference project (the tests themselves never do); give its path:
 
-    python tests/golden/make_golden.py
+    B200_REFERENCE=<reference checkout> python tests/golden/make_golden.py
 
 Host path: the reference's Sequence / BlockManager / Scheduler (engine/*.py) are imported with a
 seven-line ``sampling_parameters`` shim (the module they import is missing from the reference), and
@@ -29,7 +29,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("B200_REFERENCE", "/root/reference"))
+REF = Path(os.environ["B200_REFERENCE"])
 sys.path.insert(0, str(HERE))
 import scenarios as sc  # noqa: E402
 
