@@ -458,8 +458,9 @@ int launch2(const Args2& a, const CUtensorMap& tq, const CUtensorMap& tk, const 
 // Query rows per CTA of this kernel for a shape it serves, else 0.
 int prefill_umma2_tile_rows(int Hq, int Hkv, int Dqk, int Dv) {
   if (Hkv <= 0 || Hq % Hkv != 0) return 0;
-  // head_dim 64 is left to the mma.sync kernel: measured on 7,300-token batches of ~540-token sequences it
-  // takes 56 us per layer there against 76 us here (one 384-thread CTA per SM, too little work per CTA)
+  // head_dim 64 has a kernel of its own (prefill_umma4.cu, four heads of a KV head per CTA): one head per CTA
+  // leaves a CTA too little work on short sequences (76 us per layer here on 7,300-token batches of ~540-token
+  // sequences against 36 us there)
   const bool ok = (Dqk == 192 && Dv == 128) || (Dqk == 128 && Dv == 128);
   return ok ? ROWS : 0;
 }
