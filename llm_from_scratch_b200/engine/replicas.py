@@ -39,6 +39,11 @@ class ReplicaReport:
     decode_tokens: int = 0
     steps: int = 0
     timing: dict = field(default_factory=dict)        # the engine's per-component wall times for this shard
+    # online runs only, one entry per request of the shard (seconds from the start of the run): when it arrived,
+    # when the step that produced its first token ended, when the step that finished it ended
+    arrival_s: list = field(default_factory=list)
+    first_token_s: list = field(default_factory=list)
+    finish_s: list = field(default_factory=list)
 
 
 def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaReport:
@@ -57,11 +62,17 @@ def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaRep
         pending = 0
     else:
         seqs, pending = [], 0
+        rep.arrival_s = [float(a) for a in arrivals[:len(shard)]]
+        rep.first_token_s = [0.0] * len(shard)
+        rep.finish_s = [0.0] * len(shard)
+    index_of = {}             # seq_id -> position in the shard (online runs)
+    unstarted = 0             # requests before this position have their first token (admission is first come, first served)
     while pending < (len(shard) if arrivals is not None else 0) or not engine.is_finished():
         if arrivals is not None:
             now = time.perf_counter() - t0
             while pending < len(shard) and arrivals[pending] <= now:
                 seqs.append(engine.add_request(*shard[pending]))
+                index_of[seqs[-1].seq_id] = pending
                 pending += 1
             if engine.is_finished():
                 if pending < len(shard):
@@ -75,6 +86,14 @@ def serve_shard(engine, shard: list, rank: int = 0, arrivals=None) -> ReplicaRep
             rep.prefill_tokens += n
         else:
             rep.decode_tokens += n
+        if arrivals is not None:
+            now = time.perf_counter() - t0
+            if is_prefill:
+                while unstarted < len(seqs) and seqs[unstarted].num_tokens > seqs[unstarted].num_prompt_tokens:
+                    rep.first_token_s[unstarted] = now
+                    unstarted += 1
+            for seq_id, _ in outputs:
+                rep.finish_s[index_of[seq_id]] = now
     rep.wall_s = time.perf_counter() - t0
     rep.timing = {k: v - before.get(k, 0) for k, v in getattr(engine, "timing", {}).items()}
     rep.token_ids = [s.completion_token_ids for s in seqs]

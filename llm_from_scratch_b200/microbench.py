@@ -286,14 +286,33 @@ def engine(steps: int = 0, warmup: int = 0, batch: int = 512, rate: float | None
     assert gen == int(outs.sum()), (gen, int(outs.sum()))
     wall = max(r.wall_s for r in reports)
     prompt_tokens = int(sum(len(p) for p in prompts))
-    return dict(workload=f"continuous batching GQA+MoE bf16: {batch} requests "
-                         f"({'all at t=0' if rate is None else f'Poisson {rate}/s'}), prompts U[64,1024], outputs "
-                         "geometric(256) cap 1024, max 256 seqs / 8192 tokens per step per replica",
-                replicas=world, requests=batch, generated_tokens=gen, prompt_tokens=prompt_tokens, wall_s=wall,
-                replica_wall_s=[r.wall_s for r in reports], steps=[r.steps for r in reports],
-                output_tokens_per_s=gen / wall, total_tokens_per_s=(gen + prompt_tokens) / wall,
-                engine_build_s=built["build_s"], cuda_graphs=graphs, kv_pool_blocks=pool_blocks,
-                decode_window=decode_window, rank0_timing=timing)
+    out = dict(workload=f"continuous batching GQA+MoE bf16: {batch} requests "
+                        f"({'all at t=0' if rate is None else f'Poisson {rate}/s'}), prompts U[64,1024], outputs "
+                        "geometric(256) cap 1024, max 256 seqs / 8192 tokens per step per replica",
+               replicas=world, requests=batch, generated_tokens=gen, prompt_tokens=prompt_tokens, wall_s=wall,
+               replica_wall_s=[r.wall_s for r in reports], steps=[r.steps for r in reports],
+               output_tokens_per_s=gen / wall, total_tokens_per_s=(gen + prompt_tokens) / wall,
+               engine_build_s=built["build_s"], cuda_graphs=graphs, kv_pool_blocks=pool_blocks,
+               decode_window=decode_window, rank0_timing=timing)
+    if rate is not None:
+        out["latency"] = request_latencies(reports)
+    return out
+
+
+def request_latencies(reports) -> dict:
+    """Per-request latencies of an online run over all replicas: time to the first token (arrival -> end of the
+    step that produced it), time per output token after the first, and arrival -> completion."""
+    ttft, tpot, e2e = [], [], []
+    for r in reports:
+        for a, f, d, toks in zip(r.arrival_s, r.first_token_s, r.finish_s, r.token_ids):
+            ttft.append(f - a)
+            e2e.append(d - a)
+            if len(toks) > 1:
+                tpot.append((d - f) / (len(toks) - 1))
+    q = lambda v, p: float(np.percentile(v, p)) if v else None
+    return dict(ttft_ms={"p50": q(ttft, 50) * 1e3, "p90": q(ttft, 90) * 1e3, "p99": q(ttft, 99) * 1e3},
+                ms_per_output_token={"mean": float(np.mean(tpot)) * 1e3, "p50": q(tpot, 50) * 1e3, "p99": q(tpot, 99) * 1e3},
+                request_s={"p50": q(e2e, 50), "p99": q(e2e, 99)})
 
 
 def decode_step_bytes(model: dict, seq_steps: int, ctx_tokens: int, steps: int, itemsize: int = 2) -> float:
@@ -324,7 +343,7 @@ def decode_step_bytes(model: dict, seq_steps: int, ctx_tokens: int, steps: int, 
 
 
 def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: int = 8,
-                hbm_peak_gbs: float = 6542.1) -> dict:
+                hbm_peak_gbs: float = 6542.1, online_rate: float = 256.0) -> dict:
     """The continuous-batching benchmark through the engine (GQA+MoE decoder of ``C3_MODEL``, bf16, random init
     seed 0, KV block 16, at most 256 sequences and 8192 batched tokens per step, all requests present at
     t = 0), as the two jobs a multi-GPU run can mean.  Every rank of the process group is an independent
@@ -337,7 +356,14 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
     ``fixed_window``, with ``decode_window`` decode graph replays per decision (same token streams; the sampled
     token of one step feeds the next on the device); ``weak`` runs with the window.
     With one replica fixed and weak are the same job.  Rates are tokens of all replicas over the
-    slowest replica's wall time.  Returns {} on ranks other than 0."""
+    slowest replica's wall time.
+
+    * ``online``: the fixed job's requests arriving as a Poisson process of ``online_rate`` requests/s in total (the
+      other arrival pattern of the configuration; 0 skips it), one decode step per scheduling decision: the load
+      is below what the engine sustains, so the record is about latency — time to the first token, time per
+      output token, arrival to completion — not throughput.
+
+    Returns {} on ranks other than 0."""
     import itertools
     import os
     import time
@@ -361,14 +387,17 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
     eng = LLMEngine(cfg)
     build_s = time.perf_counter() - t0
 
-    def run(job: str, window: int):
+    def run(job: str, window: int, rate: float | None = None):
         eng.decode_window = window
         # a fresh block pool: a job must not find the previous job's prompts in the prefix cache
         bm = eng.scheduler.block_manager
         eng.scheduler.block_manager = type(bm)(eng.model_runner.num_kv_blocks, bm.block_size)
+        arrivals = None
         if job == "fixed":
-            prompts, outs, _ = c3_requests(requests, seed=3)
+            prompts, outs, arr = c3_requests(requests, seed=3, rate=rate)
             shard = shard_requests(list(zip(prompts, outs)), world, rank)
+            if rate is not None:
+                arrivals = shard_requests(arr.tolist(), world, rank)
         else:
             prompts, outs, _ = c3_requests(requests, seed=1000 + rank)
             shard = list(zip(prompts, outs))
@@ -376,7 +405,7 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
         torch.cuda.synchronize()
         if distributed:
             dist.barrier()                      # replicas start the job together
-        rep = serve_shard(eng, reqs, rank)
+        rep = serve_shard(eng, reqs, rank, arrivals)
         torch.cuda.synchronize()
         ops.check_status()
         gen = sum(len(t) for t in rep.token_ids)
@@ -388,12 +417,22 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
                     run_prefill_s=t["run_prefill_s"], schedule_s=t["schedule_s"], postprocess_s=t["postprocess_s"],
                     decode_seq_steps=t["decode_seq_steps"], decode_ctx_tokens=t["decode_ctx_tokens"],
                     decode_bytes=nbytes)
+        if rate is not None:
+            mine["report"] = rep
         rows = [mine]
         if distributed:
             rows = [None] * world if rank == 0 else None
             dist.gather_object(mine, rows, dst=0)
         if rank != 0:
             return None
+        if rate is not None:
+            lat = request_latencies([r["report"] for r in rows])
+            wall = max(r["wall_s"] for r in rows)
+            gen_all = sum(r["generated"] for r in rows)
+            return dict(decode_window=window, requests=requests, replicas=world, arrivals=f"Poisson, {rate:g} requests/s "
+                        "over all replicas (seed 3), request i to replica i mod N", wall_s=wall,
+                        output_tokens_per_s=gen_all / wall, latency=lat,
+                        mean_decode_batch=sum(r["decode_seq_steps"] for r in rows) / max(sum(r["decode_steps"] for r in rows), 1))
         wall = max(r["wall_s"] for r in rows)
         gen_all, prompt_all = sum(r["generated"] for r in rows), sum(r["prompt"] for r in rows)
         fracs = [r["decode_bytes"] / r["run_decode_s"] / 1e9 / hbm_peak_gbs for r in rows]
@@ -422,12 +461,15 @@ def engine_jobs(pool_blocks: int = 110000, requests: int = 2048, decode_window: 
     fixed = run("fixed", 1)
     fixed_window = run("fixed", decode_window)
     weak = run("weak", decode_window) if world > 1 else None
+    online = run("fixed", 1, rate=online_rate) if online_rate else None
     eng.exit()
     if rank != 0:
         return {}
     out["fixed"] = fixed
     out["fixed_window"] = fixed_window
     out["weak"] = weak if weak is not None else "one replica: the same job as fixed_window"
+    if online is not None:
+        out["online"] = online
     return out
 
 

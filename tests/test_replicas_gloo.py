@@ -97,3 +97,12 @@ def test_online_arrivals_give_the_same_streams_as_offline():
     online = serve_shard(_make_engine(0), reqs, arrivals=arrivals)
     assert online.token_ids == offline
     assert online.wall_s >= 0.05
+    # per-request clock: arrival <= first token <= completion <= end of the run, one entry per request
+    assert online.arrival_s == arrivals and len(online.first_token_s) == len(online.finish_s) == len(reqs)
+    for a, f, d, toks in zip(online.arrival_s, online.first_token_s, online.finish_s, online.token_ids):
+        assert a <= f <= d <= online.wall_s and f > 0.0
+        assert len(toks) > 1 or f == d                     # a one-token request finishes in its prefill step
+    from llm_from_scratch_b200.microbench import request_latencies
+    lat = request_latencies([online])
+    assert 0.0 <= lat["ttft_ms"]["p50"] <= lat["ttft_ms"]["p99"] <= 1e3 * online.wall_s
+    assert lat["request_s"]["p99"] <= online.wall_s and lat["ms_per_output_token"]["mean"] > 0.0
