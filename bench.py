@@ -488,6 +488,10 @@ def main():
     if not args.no_engine:
         from llm_from_scratch_b200 import microbench
         engine = microbench.engine_jobs(hbm_peak_gbs=hbm_peak()[0])
+        if n_gpus == 1:
+            # the MLA+MoE decoder's mixed step (16 prefills + 240 decodes per step pair) through the engine
+            torch.cuda.empty_cache()
+            engine["mla_mixed_step"] = microbench.engine_mla(steps=5, warmup=2)
 
     if rank != 0:
         if dist is not None:
